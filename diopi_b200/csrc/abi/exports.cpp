@@ -1,0 +1,416 @@
+// The exported C entry points of libdiopi_impl.so: argument validation, then one launch on the
+// stream of the caller's context. No host synchronisation, no per-request host loop; lengths,
+// start offsets and slot tables are read on the device.
+#include <cmath>
+#include <cstring>
+
+#include "../kernels/kernels.hpp"
+#include "common.hpp"
+
+namespace b200 {
+const char* last_error_cstr();
+}
+
+using namespace b200;  // NOLINT
+
+namespace {
+
+k::Dt float_dt(const TensorView& t, const char* name, bool allow_f64) {
+    switch (t.dtype) {
+        case diopi_dtype_float16: return k::Dt::F16;
+        case diopi_dtype_bfloat16: return k::Dt::BF16;
+        case diopi_dtype_float32: return k::Dt::F32;
+        case diopi_dtype_float64:
+            if (allow_f64) return k::Dt::F64;
+            break;
+        default: break;
+    }
+    fail(diopiDtypeNotSupported, "'%s' has dtype %s; supported: float16, bfloat16, float32%s", name, dtype_name(t.dtype), allow_f64 ? ", float64" : "");
+}
+
+k::IndexArg index_arg(const TensorView& t, const char* name, int ndim) {
+    if (!is_index_dtype(t.dtype)) fail(diopiDtypeNotSupported, "'%s' has dtype %s; index tensors must be int32 or int64", name, dtype_name(t.dtype));
+    B200_REQUIRE(t.ndim == ndim, "'%s' must have %d dim(s), got %d", name, ndim, t.ndim);
+    k::IndexArg a;
+    a.ptr = t.data;
+    a.s0 = t.stride[0];
+    a.s1 = ndim > 1 ? t.stride[1] : 0;
+    a.is64 = t.dtype == diopi_dtype_int64;
+    return a;
+}
+
+void same_dtype(const TensorView& a, const char* an, const TensorView& b, const char* bn) {
+    B200_REQUIRE(a.dtype == b.dtype, "'%s' (%s) and '%s' (%s) must share a dtype", an, dtype_name(a.dtype), bn, dtype_name(b.dtype));
+}
+
+// Common checks and argument packing of the three decode entry points.
+void run_decode(diopiContextHandle_t ctx, k::DecodeMode mode, const TensorView* out, const TensorView* att, const TensorView* q, const TensorView* kmat,
+                const TensorView* vmat, const TensorView& b_loc, const TensorView& b_start, const TensorView& b_len, int max_input_len) {
+    k::DecodeArgs a{};
+    a.mode = mode;
+    const TensorView& pool = kmat ? *kmat : *vmat;
+    a.dt = float_dt(pool, kmat ? "k" : "v", false);
+    B200_REQUIRE(pool.ndim == 3, "the K/V pool must be [slots, head_num, head_dim], got %d dims", pool.ndim);
+    a.H = static_cast<int>(pool.shape[1]);
+    a.D = static_cast<int>(pool.shape[2]);
+    a.slots = pool.shape[0];
+    B200_REQUIRE(b_loc.ndim == 2, "'b_loc' must be [batch, N], got %d dims", b_loc.ndim);
+    a.B = static_cast<int>(b_loc.shape[0]);
+    B200_REQUIRE(max_input_len >= 0, "max_input_len must not be negative (got %d)", max_input_len);
+    B200_REQUIRE(b_loc.shape[1] >= max_input_len, "'b_loc' has %ld columns, fewer than max_input_len = %d", (long)b_loc.shape[1], max_input_len);
+    a.max_input_len = max_input_len;
+    a.b_loc = index_arg(b_loc, "b_loc", 2);
+    a.b_start = index_arg(b_start, "b_start_loc", 1);
+    a.b_len = index_arg(b_len, "b_seq_len", 1);
+    B200_REQUIRE(b_start.shape[0] == a.B && b_len.shape[0] == a.B, "'b_start_loc' and 'b_seq_len' must have batch = %d entries", a.B);
+    B200_REQUIRE(a.D <= 512, "head_dim %d is beyond the supported maximum of 512", a.D);
+
+    if (q) {
+        same_dtype(*q, "q", pool, "k");
+        B200_REQUIRE(q->ndim == 3 && q->shape[0] == a.B && q->shape[1] == a.H && q->shape[2] == a.D, "'q' must be [%d, %d, %d]", a.B, a.H, a.D);
+        a.q = q->data;
+        a.q_s0 = q->stride[0];
+        a.q_s1 = q->stride[1];
+        a.q_s2 = q->stride[2];
+    }
+    if (kmat) {
+        a.kmat = kmat->data;
+        a.k_s0 = kmat->stride[0];
+        a.k_s1 = kmat->stride[1];
+        a.k_s2 = kmat->stride[2];
+    }
+    if (vmat) {
+        same_dtype(*vmat, "v", pool, "k");
+        B200_REQUIRE(vmat->ndim == 3 && vmat->shape[1] == a.H && vmat->shape[2] == a.D, "'v' must be [slots, %d, %d]", a.H, a.D);
+        if (kmat) B200_REQUIRE(vmat->shape[0] == kmat->shape[0], "'k' and 'v' pools differ in slot count");
+        a.vmat = vmat->data;
+        a.v_s0 = vmat->stride[0];
+        a.v_s1 = vmat->stride[1];
+        a.v_s2 = vmat->stride[2];
+    }
+    if (att) {
+        same_dtype(*att, "logits", pool, "k/v");
+        B200_REQUIRE(att->ndim == 2 && att->shape[0] == a.H, "the logits tensor must be [head_num = %d, sum of lengths]", a.H);
+        a.att = att->data;
+        a.att_s0 = att->stride[0];
+        a.att_s1 = att->stride[1];
+        a.att_cols = att->shape[1];
+    }
+    if (out) {
+        same_dtype(*out, "out", pool, "k/v");
+        B200_REQUIRE(out->ndim == 3 && out->shape[0] == a.B && out->shape[1] == a.H && out->shape[2] == a.D, "'out' must be [%d, %d, %d]", a.B, a.H, a.D);
+        a.out = out->data;
+        a.out_s0 = out->stride[0];
+        a.out_s1 = out->stride[1];
+        a.out_s2 = out->stride[2];
+    }
+    if (a.B == 0 || a.H == 0 || a.D == 0) return;
+    B200_REQUIRE(a.slots > 0 || max_input_len == 0, "the K/V pool has no slots");
+    cudaStream_t st = stream_of(ctx);
+    if (max_input_len == 0 || a.slots == 0) {
+        // Every request is empty: no logits to write, zeros for the attention output.
+        if (out && out->numel > 0) {
+            B200_REQUIRE(out->contiguous(), "'out' must be contiguous when every request is empty");
+            B200_CUDA(cudaMemsetAsync(out->data, 0, static_cast<size_t>(out->numel * out->elem_size()), st));
+        }
+        return;
+    }
+    const DeviceInfo& di = device_info();
+    a.status = async_status_device_ptr();
+    const int64_t ws_bytes = k::decode_workspace_bytes(a, di.sm_count, di.max_smem_optin);
+    void* ws = ws_bytes > 0 ? workspace(ctx, ws_bytes) : nullptr;
+    logf("decode mode=%d B=%d H=%d D=%d max_input_len=%d scratch=%ld bytes (%s path)", static_cast<int>(mode), a.B, a.H, a.D, max_input_len, (long)ws_bytes,
+         (ws_bytes > 0 || mode == k::DecodeMode::QK) ? "split or plain" : "plain");
+    k::launch_decode(a, ws, di.sm_count, di.max_smem_optin, st);
+    B200_CUDA(cudaGetLastError());
+}
+
+}  // namespace
+
+// ---------------------------------------------------------------------------------------------
+B200_EXPORT const char* diopiGetVendorName() { return "B200Device"; }
+B200_EXPORT const char* diopiGetImplVersion() {
+    static char buf[160];
+    static bool once = [] {
+        std::snprintf(buf, sizeof(buf), "diopi_b200 0.1.0 (sm_100a, CUDA runtime %d.%d)", CUDART_VERSION / 1000, (CUDART_VERSION % 1000) / 10);
+        return true;
+    }();
+    (void)once;
+    return buf;
+}
+B200_EXPORT const char* diopiGetLastErrorString() { return last_error_cstr(); }
+
+// ---------------------------------------------------------------------------------------------
+B200_EXPORT diopiError_t diopiDestIndexCopyKV(diopiContextHandle_t ctx, diopiTensorHandle_t out, diopiConstTensorHandle_t kh, diopiConstTensorHandle_t dest_loc) {
+    return guard("diopiDestIndexCopyKV", [&] {
+        TensorView o = view_of(out, "out"), src = view_of(kh, "k"), d = view_of(dest_loc, "dest_loc");
+        same_dtype(o, "out", src, "k");
+        B200_REQUIRE(dtype_size(src.dtype) > 0, "'k' has an unsupported dtype");
+        B200_REQUIRE(src.ndim == 3 && o.ndim == 3, "'k' and 'out' must be [tokens, head_num, head_dim]");
+        B200_REQUIRE(src.shape[1] == o.shape[1] && src.shape[2] == o.shape[2], "'k' is [*, %ld, %ld] but 'out' is [*, %ld, %ld]", (long)src.shape[1],
+                     (long)src.shape[2], (long)o.shape[1], (long)o.shape[2]);
+        k::CopyKVArgs a{};
+        a.dest = index_arg(d, "dest_loc", 1);
+        B200_REQUIRE(d.shape[0] == src.shape[0], "'dest_loc' has %ld entries for %ld rows of 'k'", (long)d.shape[0], (long)src.shape[0]);
+        a.src = src.data;
+        a.dst = o.data;
+        a.T = src.shape[0];
+        a.H = src.shape[1];
+        a.D = src.shape[2];
+        a.slots = o.shape[0];
+        a.src_s0 = src.stride[0];
+        a.src_s1 = src.stride[1];
+        a.src_s2 = src.stride[2];
+        a.dst_s0 = o.stride[0];
+        a.dst_s1 = o.stride[1];
+        a.dst_s2 = o.stride[2];
+        a.elem_bytes = static_cast<int>(dtype_size(src.dtype));
+        if (src.numel == 0) return;
+        B200_REQUIRE(a.slots > 0, "'out' has no slots");
+        cudaStream_t st = stream_of(ctx);
+        a.status = async_status_device_ptr();
+        k::launch_dest_index_copy(a, st);
+        B200_CUDA(cudaGetLastError());
+    });
+}
+
+B200_EXPORT diopiError_t diopiTokenAttentionInference(diopiContextHandle_t ctx, diopiTensorHandle_t token_attention_out, diopiConstTensorHandle_t q,
+                                                      diopiConstTensorHandle_t kh, diopiConstTensorHandle_t b_loc, diopiConstTensorHandle_t b_start_loc,
+                                                      diopiConstTensorHandle_t b_seq_len, int max_input_len) {
+    return guard("diopiTokenAttentionInference", [&] {
+        TensorView att = view_of(token_attention_out, "token_attention_out"), qv = view_of(q, "q"), kv = view_of(kh, "k");
+        TensorView bl = view_of(b_loc, "b_loc"), bs = view_of(b_start_loc, "b_start_loc"), bn = view_of(b_seq_len, "b_seq_len");
+        run_decode(ctx, k::DecodeMode::QK, nullptr, &att, &qv, &kv, nullptr, bl, bs, bn, max_input_len);
+    });
+}
+
+B200_EXPORT diopiError_t diopiTokenSoftmaxReduceVInference(diopiContextHandle_t ctx, diopiTensorHandle_t out, diopiConstTensorHandle_t logics,
+                                                           diopiConstTensorHandle_t v, diopiConstTensorHandle_t b_loc, diopiConstTensorHandle_t b_start_loc,
+                                                           diopiConstTensorHandle_t b_seq_len, int max_input_len, int /*other_kv_index*/) {
+    return guard("diopiTokenSoftmaxReduceVInference", [&] {
+        TensorView o = view_of(out, "out"), att = view_of(logics, "logics"), vv = view_of(v, "v");
+        TensorView bl = view_of(b_loc, "b_loc"), bs = view_of(b_start_loc, "b_start_loc"), bn = view_of(b_seq_len, "b_seq_len");
+        run_decode(ctx, k::DecodeMode::PV, &o, &att, nullptr, nullptr, &vv, bl, bs, bn, max_input_len);
+    });
+}
+
+B200_EXPORT diopiError_t diopiTokenDecodeAttentionInference(diopiContextHandle_t ctx, diopiTensorHandle_t out, diopiConstTensorHandle_t q,
+                                                            diopiConstTensorHandle_t kh, diopiConstTensorHandle_t v, diopiConstTensorHandle_t b_loc,
+                                                            diopiConstTensorHandle_t b_start_loc, diopiConstTensorHandle_t b_seq_len, int max_input_len) {
+    return guard("diopiTokenDecodeAttentionInference", [&] {
+        TensorView o = view_of(out, "out"), qv = view_of(q, "q"), kv = view_of(kh, "k"), vv = view_of(v, "v");
+        TensorView bl = view_of(b_loc, "b_loc"), bs = view_of(b_start_loc, "b_start_loc"), bn = view_of(b_seq_len, "b_seq_len");
+        run_decode(ctx, k::DecodeMode::FUSED, &o, nullptr, &qv, &kv, &vv, bl, bs, bn, max_input_len);
+    });
+}
+
+B200_EXPORT diopiError_t diopiContextAttentionInference(diopiContextHandle_t ctx, diopiTensorHandle_t context_attention_out, diopiConstTensorHandle_t q,
+                                                        diopiConstTensorHandle_t kh, diopiConstTensorHandle_t v, diopiConstTensorHandle_t b_start_loc,
+                                                        diopiConstTensorHandle_t b_seq_len, int max_input_len) {
+    return guard("diopiContextAttentionInference", [&] {
+        TensorView o = view_of(context_attention_out, "context_attention_out"), qv = view_of(q, "q"), kv = view_of(kh, "k"), vv = view_of(v, "v");
+        TensorView bs = view_of(b_start_loc, "b_start_loc"), bn = view_of(b_seq_len, "b_seq_len");
+        k::PrefillArgs a{};
+        a.dt = float_dt(qv, "q", false);
+        same_dtype(kv, "k", qv, "q");
+        same_dtype(vv, "v", qv, "q");
+        same_dtype(o, "context_attention_out", qv, "q");
+        B200_REQUIRE(qv.ndim == 3, "'q' must be [sum of lengths, head_num, head_dim]");
+        for (const TensorView* t : {&kv, &vv, &o}) {
+            B200_REQUIRE(t->ndim == 3 && t->shape[0] == qv.shape[0] && t->shape[1] == qv.shape[1] && t->shape[2] == qv.shape[2],
+                         "q, k, v and out must share the shape [%ld, %ld, %ld]", (long)qv.shape[0], (long)qv.shape[1], (long)qv.shape[2]);
+            B200_REQUIRE(t->shape[2] == 1 || t->stride[2] == 1, "the last dim of q, k, v and out must be dense");
+        }
+        B200_REQUIRE(qv.shape[2] == 1 || qv.stride[2] == 1, "the last dim of q, k, v and out must be dense");
+        a.total_rows = qv.shape[0];
+        a.H = static_cast<int>(qv.shape[1]);
+        a.D = static_cast<int>(qv.shape[2]);
+        B200_REQUIRE(a.D <= 256, "head_dim %d is beyond the supported maximum of 256", a.D);
+        a.b_start = index_arg(bs, "b_start_loc", 1);
+        a.b_len = index_arg(bn, "b_seq_len", 1);
+        a.B = static_cast<int>(bs.shape[0]);
+        B200_REQUIRE(bn.shape[0] == a.B, "'b_start_loc' and 'b_seq_len' differ in length");
+        a.max_input_len = max_input_len;
+        a.q = qv.data;
+        a.kmat = kv.data;
+        a.vmat = vv.data;
+        a.out = o.data;
+        a.q_s0 = qv.stride[0];
+        a.q_s1 = qv.stride[1];
+        a.k_s0 = kv.stride[0];
+        a.k_s1 = kv.stride[1];
+        a.v_s0 = vv.stride[0];
+        a.v_s1 = vv.stride[1];
+        a.o_s0 = o.stride[0];
+        a.o_s1 = o.stride[1];
+        if (qv.numel == 0 || a.B == 0) return;
+        cudaStream_t st = stream_of(ctx);
+        const DeviceInfo& di = device_info();
+        k::launch_prefill(a, di.sm_count, di.max_smem_optin, st);
+        B200_CUDA(cudaGetLastError());
+    });
+}
+
+B200_EXPORT diopiError_t diopiApplyPenalty(diopiContextHandle_t ctx, diopiTensorHandle_t logits, diopiConstTensorHandle_t presence_penalty,
+                                           diopiConstTensorHandle_t frequency_penalty, diopiConstTensorHandle_t p_token_ids,
+                                           diopiConstTensorHandle_t p_token_counts, diopiConstTensorHandle_t p_cumsum_seq_len, int /*p_max_len_in_batch*/) {
+    return guard("diopiApplyPenalty", [&] {
+        TensorView lg = view_of(logits, "logits"), pp = view_of(presence_penalty, "presence_penalty"), fp = view_of(frequency_penalty, "frequency_penalty");
+        TensorView ids = view_of(p_token_ids, "p_token_ids"), cnt = view_of(p_token_counts, "p_token_counts"), cum = view_of(p_cumsum_seq_len, "p_cumsum_seq_len");
+        k::PenaltyArgs a{};
+        a.dt = float_dt(lg, "logits", true);
+        same_dtype(pp, "presence_penalty", lg, "logits");
+        same_dtype(fp, "frequency_penalty", lg, "logits");
+        B200_REQUIRE(lg.ndim == 2, "'logits' must be [batch, vocab], got %d dims", lg.ndim);
+        a.B = lg.shape[0];
+        a.V = lg.shape[1];
+        B200_REQUIRE(pp.ndim == 1 && fp.ndim == 1 && pp.shape[0] == a.B && fp.shape[0] == a.B, "the penalties must be [batch = %ld]", (long)a.B);
+        a.ids = index_arg(ids, "p_token_ids", 1);
+        a.counts = index_arg(cnt, "p_token_counts", 1);
+        a.cum = index_arg(cum, "p_cumsum_seq_len", 1);
+        B200_REQUIRE(ids.shape[0] == cnt.shape[0], "'p_token_ids' and 'p_token_counts' differ in length");
+        B200_REQUIRE(cum.shape[0] == a.B + 1, "'p_cumsum_seq_len' must have batch + 1 = %ld entries, got %ld", (long)(a.B + 1), (long)cum.shape[0]);
+        a.E = ids.shape[0];
+        a.logits = lg.data;
+        a.l_s0 = lg.stride[0];
+        a.l_s1 = lg.stride[1];
+        a.presence = pp.data;
+        a.p_s = pp.stride[0];
+        a.frequency = fp.data;
+        a.f_s = fp.stride[0];
+        if (a.E == 0 || a.B == 0 || a.V == 0) return;
+        cudaStream_t st = stream_of(ctx);
+        a.status = async_status_device_ptr();
+        k::launch_apply_penalty(a, st);
+        B200_CUDA(cudaGetLastError());
+    });
+}
+
+B200_EXPORT diopiError_t diopiRotaryEmbedding(diopiContextHandle_t ctx, diopiTensorHandle_t out, diopiConstTensorHandle_t x, diopiConstTensorHandle_t cos,
+                                              diopiConstTensorHandle_t sin, const bool conj, const bool interleaved) {
+    return guard("diopiRotaryEmbedding", [&] {
+        if (interleaved) fail(diopiNoImplement, "interleaved rotary embedding is not implemented (nor is it in the reference's CUDA backend)");
+        TensorView o = view_of(out, "out"), xv = view_of(x, "x"), cv = view_of(cos, "cos"), sv = view_of(sin, "sin");
+        k::RopeArgs a{};
+        a.dt = float_dt(xv, "x", true);
+        same_dtype(o, "out", xv, "x");
+        same_dtype(cv, "cos", xv, "x");
+        same_dtype(sv, "sin", xv, "x");
+        B200_REQUIRE(xv.ndim >= 1, "'x' must have at least one dim");
+        B200_REQUIRE(o.ndim == xv.ndim, "'out' must have the shape of 'x'");
+        for (int i = 0; i < xv.ndim; ++i) B200_REQUIRE(o.shape[i] == xv.shape[i], "'out' must have the shape of 'x'");
+        const int64_t D = xv.shape[xv.ndim - 1];
+        B200_REQUIRE(D % 2 == 0, "the last dim of 'x' (%ld) must be even", (long)D);
+        a.half = D / 2;
+        B200_REQUIRE(cv.ndim >= 1 && sv.ndim >= 1 && cv.ndim <= xv.ndim && sv.ndim <= xv.ndim, "'cos'/'sin' must have between 1 and %d dims", xv.ndim);
+        B200_REQUIRE(cv.shape[cv.ndim - 1] == a.half && sv.shape[sv.ndim - 1] == a.half, "the last dim of 'cos'/'sin' must be %ld", (long)a.half);
+        if (xv.numel == 0) return;
+        // Leading dims of x, with the matching (right-aligned) stride of cos/sin, 0 where they broadcast.
+        const int nl = xv.ndim - 1;
+        int64_t size[kMaxDims], xs[kMaxDims], os[kMaxDims], cs[kMaxDims], ss[kMaxDims];
+        for (int i = 0; i < nl; ++i) {
+            size[i] = xv.shape[i];
+            xs[i] = xv.stride[i];
+            os[i] = o.stride[i];
+            auto bstride = [&](const TensorView& t, const char* name) -> int64_t {
+                const int ti = i - (xv.ndim - t.ndim);
+                if (ti < 0) return 0;
+                if (t.shape[ti] == 1) return 0;
+                B200_REQUIRE(t.shape[ti] == xv.shape[i], "'%s' dim %d (%ld) does not broadcast against 'x' dim %d (%ld)", name, ti, (long)t.shape[ti], i,
+                             (long)xv.shape[i]);
+                return t.stride[ti];
+            };
+            cs[i] = bstride(cv, "cos");
+            ss[i] = bstride(sv, "sin");
+        }
+        // Collapse neighbouring dims that walk memory uniformly in all four tensors; drop dims of extent 1.
+        int nd = 0;
+        for (int i = 0; i < nl; ++i) {
+            if (size[i] == 1) continue;
+            if (nd > 0 && xs[nd - 1] == size[i] * xs[i] && os[nd - 1] == size[i] * os[i] && cs[nd - 1] == size[i] * cs[i] && ss[nd - 1] == size[i] * ss[i]) {
+                size[nd - 1] *= size[i];
+                xs[nd - 1] = xs[i];
+                os[nd - 1] = os[i];
+                cs[nd - 1] = cs[i];
+                ss[nd - 1] = ss[i];
+            } else {
+                size[nd] = size[i];
+                xs[nd] = xs[i];
+                os[nd] = os[i];
+                cs[nd] = cs[i];
+                ss[nd] = ss[i];
+                ++nd;
+            }
+        }
+        B200_REQUIRE(nd <= k::kRopeMaxDims, "'x' needs %d independent leading dims; at most %d are supported", nd, k::kRopeMaxDims);
+        a.nd = nd;
+        a.n_lead = 1;
+        for (int i = 0; i < nd; ++i) {
+            a.size[i] = size[i];
+            a.xs[i] = xs[i];
+            a.os[i] = os[i];
+            a.cs[i] = cs[i];
+            a.ss[i] = ss[i];
+            a.n_lead *= size[i];
+        }
+        a.x = xv.data;
+        a.out = o.data;
+        a.cos = cv.data;
+        a.sin = sv.data;
+        a.x_ls = xv.stride[xv.ndim - 1];
+        a.o_ls = o.stride[o.ndim - 1];
+        a.c_ls = cv.stride[cv.ndim - 1];
+        a.s_ls = sv.stride[sv.ndim - 1];
+        a.conj = conj;
+        cudaStream_t st = stream_of(ctx);
+        k::launch_rope(a, st);
+        B200_CUDA(cudaGetLastError());
+    });
+}
+
+B200_EXPORT diopiError_t diopiRMSNorm(diopiContextHandle_t ctx, diopiTensorHandle_t out, diopiTensorHandle_t inv_rms, diopiConstTensorHandle_t input,
+                                      diopiSize_t normalized_shape, diopiConstTensorHandle_t weight, diopiConstTensorHandle_t bias, double eps) {
+    return guard("diopiRMSNorm", [&] {
+        TensorView o = view_of(out, "out"), iv = view_of(inv_rms, "inv_rms"), xv = view_of(input, "input"), wv = view_of(weight, "weight");
+        TensorView bv = view_of(bias, "bias", /*optional=*/true);
+        k::RmsNormArgs a{};
+        a.dt = float_dt(xv, "input", true);
+        same_dtype(o, "out", xv, "input");
+        same_dtype(wv, "weight", xv, "input");
+        if (bv.defined) same_dtype(bv, "bias", xv, "input");
+        B200_REQUIRE(normalized_shape.len >= 1 && normalized_shape.len <= xv.ndim && normalized_shape.data != nullptr,
+                     "normalized_shape must name between 1 and %d trailing dims", xv.ndim);
+        int64_t n2 = 1;
+        for (int64_t i = 0; i < normalized_shape.len; ++i) {
+            const int64_t want = normalized_shape.data[i];
+            const int64_t have = xv.shape[xv.ndim - normalized_shape.len + i];
+            B200_REQUIRE(want == have, "normalized_shape[%ld] = %ld does not match the input's trailing dim %ld", (long)i, (long)want, (long)have);
+            n2 *= want;
+        }
+        a.n2 = n2;
+        a.n1 = n2 > 0 ? xv.numel / n2 : 0;
+        B200_REQUIRE(o.numel == xv.numel, "'out' must have the shape of 'input'");
+        B200_REQUIRE(wv.numel == n2, "'weight' must have %ld elements (normalized_shape), got %ld", (long)n2, (long)wv.numel);
+        if (bv.defined) B200_REQUIRE(bv.numel == n2, "'bias' must have %ld elements (normalized_shape), got %ld", (long)n2, (long)bv.numel);
+        if (xv.numel == 0) return;
+        B200_REQUIRE(iv.numel == a.n1, "'inv_rms' must have one element per normalised row (%ld), got %ld", (long)a.n1, (long)iv.numel);
+        B200_REQUIRE(xv.contiguous() && o.contiguous() && wv.contiguous() && iv.contiguous() && (!bv.defined || bv.contiguous()),
+                     "input, out, weight, bias and inv_rms must be contiguous");
+        if (iv.dtype == diopi_dtype_float32)
+            a.inv_dt = k::Dt::F32;
+        else if (iv.dtype == xv.dtype)
+            a.inv_dt = a.dt;
+        else
+            fail(diopiDtypeNotSupported, "'inv_rms' has dtype %s; expected float32 or the input's dtype (%s)", dtype_name(iv.dtype), dtype_name(xv.dtype));
+        a.x = xv.data;
+        a.weight = wv.data;
+        a.bias = bv.defined ? bv.data : nullptr;
+        a.out = o.data;
+        a.inv_rms = iv.data;
+        a.eps = eps;
+        cudaStream_t st = stream_of(ctx);
+        const DeviceInfo& di = device_info();
+        k::launch_rms_norm(a, di.sm_count, st);
+        B200_CUDA(cudaGetLastError());
+    });
+}

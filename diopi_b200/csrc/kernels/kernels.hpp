@@ -1,0 +1,113 @@
+// Launch interfaces between the exported ops (plain C++) and the CUDA kernels.
+// Everything crosses as raw pointers, element strides and sizes.
+#pragma once
+
+#include <cuda_runtime_api.h>
+
+#include <cstdint>
+
+namespace b200 {
+namespace k {
+
+enum class Dt : int { F16 = 0, BF16 = 1, F32 = 2, F64 = 3 };
+
+// A 1-D or 2-D tensor of int32/int64 indices read on the device.
+struct IndexArg {
+    const void* ptr = nullptr;
+    int64_t s0 = 0;  // stride of dim 0, in elements
+    int64_t s1 = 0;  // stride of dim 1 (2-D only)
+    int is64 = 0;
+};
+
+// ---- DestIndexCopyKV -------------------------------------------------------
+struct CopyKVArgs {
+    const void* src;  // [T, H, D]
+    void* dst;        // [slots, H, D]
+    IndexArg dest;    // [T]
+    int64_t T, H, D, slots;
+    int64_t src_s0, src_s1, src_s2;
+    int64_t dst_s0, dst_s1, dst_s2;
+    int elem_bytes;
+    int* status;
+};
+void launch_dest_index_copy(const CopyKVArgs& a, cudaStream_t st);
+
+// ---- decode attention over the paged pool -----------------------------------
+enum class DecodeMode : int { QK = 0, PV = 1, FUSED = 2 };
+
+struct DecodeArgs {
+    DecodeMode mode;
+    Dt dt;
+    const void* q;   int64_t q_s0, q_s1, q_s2;          // [B,H,D]          (QK, FUSED)
+    const void* kmat; int64_t k_s0, k_s1, k_s2;         // [slots,H,D]      (QK, FUSED)
+    const void* vmat; int64_t v_s0, v_s1, v_s2;         // [slots,H,D]      (PV, FUSED)
+    void* att;       int64_t att_s0, att_s1;            // [H,sumL] logits: written by QK, read by PV
+    void* out;       int64_t out_s0, out_s1, out_s2;    // [B,H,D]          (PV, FUSED)
+    IndexArg b_loc, b_start, b_len;
+    int B, H, D, max_input_len;
+    int64_t slots;       // extent of dim 0 of the pool (bounds check)
+    int64_t att_cols;    // extent of dim 1 of att (bounds check)
+    int* status;
+};
+
+// Size in bytes of the scratch the split-KV path needs for these arguments, 0 if the
+// arguments take the plain (no scratch) path.
+int64_t decode_workspace_bytes(const DecodeArgs& a, int sm_count, int max_smem);
+// `ws` must hold decode_workspace_bytes(); ignored by the plain path.
+void launch_decode(const DecodeArgs& a, void* ws, int sm_count, int max_smem, cudaStream_t st);
+
+// ---- RMSNorm ----------------------------------------------------------------
+struct RmsNormArgs {
+    Dt dt;
+    const void* x;      // [n1, n2] dense
+    const void* weight; // [n2]
+    const void* bias;   // [n2] or null
+    void* out;          // [n1, n2]
+    void* inv_rms;      // [n1]
+    Dt inv_dt;          // F32, F64, or the input's half type
+    int64_t n1, n2;
+    double eps;
+};
+void launch_rms_norm(const RmsNormArgs& a, int sm_count, cudaStream_t st);
+
+// ---- rotary embedding -------------------------------------------------------
+constexpr int kRopeMaxDims = 6;
+struct RopeArgs {
+    Dt dt;
+    const void* x; void* out; const void* cos; const void* sin;
+    int nd;                          // number of leading (collapsed) dims
+    int64_t size[kRopeMaxDims];
+    int64_t xs[kRopeMaxDims], os[kRopeMaxDims], cs[kRopeMaxDims], ss[kRopeMaxDims];
+    int64_t x_ls, o_ls, c_ls, s_ls;  // stride of the last dim
+    int64_t half;                    // D / 2
+    int64_t n_lead;                  // product of size[]
+    bool conj;
+};
+void launch_rope(const RopeArgs& a, cudaStream_t st);
+
+// ---- ApplyPenalty -----------------------------------------------------------
+struct PenaltyArgs {
+    Dt dt;
+    void* logits; int64_t l_s0, l_s1; int64_t B, V;
+    const void* presence; int64_t p_s;
+    const void* frequency; int64_t f_s;
+    IndexArg ids, counts, cum;
+    int64_t E;
+    int* status;
+};
+void launch_apply_penalty(const PenaltyArgs& a, cudaStream_t st);
+
+// ---- causal prefill ---------------------------------------------------------
+struct PrefillArgs {
+    Dt dt;
+    const void* q; const void* kmat; const void* vmat; void* out;   // [sumL, H, D]
+    int64_t q_s0, q_s1, k_s0, k_s1, v_s0, v_s1, o_s0, o_s1;          // last dim dense
+    IndexArg b_start, b_len;
+    int B, H, D;
+    int64_t total_rows;
+    int max_input_len;
+};
+void launch_prefill(const PrefillArgs& a, int sm_count, int max_smem, cudaStream_t st);
+
+}  // namespace k
+}  // namespace b200

@@ -1,0 +1,157 @@
+// Rotary embedding on the two halves (x1, x2) of the last dimension:
+//   forward:  o1 = x1*cos - x2*sin,  o2 = x1*sin + x2*cos
+//   conj:     o1 = x1*cos + x2*sin,  o2 = -x1*sin + x2*cos
+// Replaces the TensorIterator kernel of impl/torch/functions/functions_ext/rotary.cu:14-46; the
+// arithmetic (fp32, each product and the sum rounded on its own, one final rounding to the storage
+// type) follows diopi_test/python/conformance/customized_test.py:374-390.
+//
+// HBM-bound: 2*numel(x)*e bytes + the cos/sin tables (re-read from L2 for every head).
+// cos/sin broadcast over x's leading dims; the host turns that into one stride per collapsed leading
+// dim (0 where broadcast), so the kernel only does a short div/mod chain per vector.
+#include "dev_util.cuh"
+
+namespace b200 {
+namespace k {
+
+namespace {
+
+struct Offsets {
+    int64_t x, o, c, s;
+};
+
+__device__ __forceinline__ Offsets lead_offsets(const RopeArgs& a, int64_t lead) {
+    Offsets r{0, 0, 0, 0};
+#pragma unroll
+    for (int d = kRopeMaxDims - 1; d >= 0; --d) {
+        if (d < a.nd) {
+            const int64_t q = lead / a.size[d];
+            const int64_t i = lead - q * a.size[d];
+            lead = q;
+            r.x += i * a.xs[d];
+            r.o += i * a.os[d];
+            r.c += i * a.cs[d];
+            r.s += i * a.ss[d];
+        }
+    }
+    return r;
+}
+
+__device__ __forceinline__ void rotate(float x1, float x2, float c, float s, bool conj, float& o1, float& o2) {
+    const float a = __fmul_rn(x1, c), b = __fmul_rn(x2, s), d = __fmul_rn(x1, s), e = __fmul_rn(x2, c);
+    if (!conj) {
+        o1 = __fsub_rn(a, b);
+        o2 = __fadd_rn(d, e);
+    } else {
+        o1 = __fadd_rn(a, b);
+        o2 = __fadd_rn(-d, e);
+    }
+}
+
+// One thread per 16-byte vector of x1 (and the matching vector of x2). Last dims dense and aligned.
+template <typename T>
+__global__ void __launch_bounds__(256) rope_vec_kernel(RopeArgs a, int vec_per_half, int64_t total_vec) {
+    constexpr int N = Vec16<T>::N;
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total_vec; i += stride) {
+        const int64_t lead = i / vec_per_half;
+        const int v = static_cast<int>(i - lead * vec_per_half);
+        const Offsets of = lead_offsets(a, lead);
+        const T* x = static_cast<const T*>(a.x) + of.x;
+        T* o = static_cast<T*>(a.out) + of.o;
+        const uint4 r1 = __ldcs(reinterpret_cast<const uint4*>(x) + v);
+        const uint4 r2 = __ldcs(reinterpret_cast<const uint4*>(x + a.half) + v);
+        const uint4 rc = __ldg(reinterpret_cast<const uint4*>(static_cast<const T*>(a.cos) + of.c) + v);
+        const uint4 rs = __ldg(reinterpret_cast<const uint4*>(static_cast<const T*>(a.sin) + of.s) + v);
+        float x1[N], x2[N], c[N], s[N], o1[N], o2[N];
+        unpack16<T>(r1, x1);
+        unpack16<T>(r2, x2);
+        unpack16<T>(rc, c);
+        unpack16<T>(rs, s);
+#pragma unroll
+        for (int e = 0; e < N; ++e) rotate(x1[e], x2[e], c[e], s[e], a.conj, o1[e], o2[e]);
+        __stcs(reinterpret_cast<uint4*>(o) + v, pack16<T>(o1));
+        __stcs(reinterpret_cast<uint4*>(o + a.half) + v, pack16<T>(o2));
+    }
+}
+
+template <typename T>
+struct Io {
+    static __device__ __forceinline__ float ld(const T* p) { return Cvt<T>::to_f(*p); }
+    static __device__ __forceinline__ void st(T* p, float v) { *p = Cvt<T>::from_f(v); }
+};
+
+// One thread per (x1, x2) pair; any strides.
+template <typename T>
+__global__ void __launch_bounds__(256) rope_scalar_kernel(RopeArgs a, int64_t total) {
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+        const int64_t lead = i / a.half;
+        const int64_t j = i - lead * a.half;
+        const Offsets of = lead_offsets(a, lead);
+        const T* x = static_cast<const T*>(a.x) + of.x;
+        T* o = static_cast<T*>(a.out) + of.o;
+        const float c = Io<T>::ld(static_cast<const T*>(a.cos) + of.c + j * a.c_ls);
+        const float s = Io<T>::ld(static_cast<const T*>(a.sin) + of.s + j * a.s_ls);
+        float o1, o2;
+        rotate(Io<T>::ld(x + j * a.x_ls), Io<T>::ld(x + (j + a.half) * a.x_ls), c, s, a.conj, o1, o2);
+        Io<T>::st(o + j * a.o_ls, o1);
+        Io<T>::st(o + (j + a.half) * a.o_ls, o2);
+    }
+}
+
+__global__ void __launch_bounds__(256) rope_scalar_f64_kernel(RopeArgs a, int64_t total) {
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+        const int64_t lead = i / a.half;
+        const int64_t j = i - lead * a.half;
+        const Offsets of = lead_offsets(a, lead);
+        const double* x = static_cast<const double*>(a.x) + of.x;
+        double* o = static_cast<double*>(a.out) + of.o;
+        const double c = static_cast<const double*>(a.cos)[of.c + j * a.c_ls];
+        const double s = static_cast<const double*>(a.sin)[of.s + j * a.s_ls];
+        const double x1 = x[j * a.x_ls], x2 = x[(j + a.half) * a.x_ls];
+        const double p = __dmul_rn(x1, c), q = __dmul_rn(x2, s), r = __dmul_rn(x1, s), t = __dmul_rn(x2, c);
+        o[j * a.o_ls] = a.conj ? __dadd_rn(p, q) : __dsub_rn(p, q);
+        o[(j + a.half) * a.o_ls] = a.conj ? __dadd_rn(-r, t) : __dadd_rn(r, t);
+    }
+}
+
+template <typename T>
+void launch_typed(const RopeArgs& a, cudaStream_t st) {
+    constexpr int N = Vec16<T>::N;
+    const int e = static_cast<int>(sizeof(T));
+    auto al = [&](const void* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; };
+    bool vec = a.half % N == 0 && a.x_ls == 1 && a.o_ls == 1 && a.c_ls == 1 && a.s_ls == 1 && al(a.x) && al(a.out) && al(a.cos) && al(a.sin);
+    for (int d = 0; d < a.nd && vec; ++d)
+        vec = (a.xs[d] * e) % 16 == 0 && (a.os[d] * e) % 16 == 0 && (a.cs[d] * e) % 16 == 0 && (a.ss[d] * e) % 16 == 0;
+    if (vec) {
+        const int vph = static_cast<int>(a.half / N);
+        const int64_t total = a.n_lead * vph;
+        const unsigned blocks = static_cast<unsigned>(std::min<int64_t>((total + 255) / 256, 148ll * 64));
+        rope_vec_kernel<T><<<blocks, 256, 0, st>>>(a, vph, total);
+    } else {
+        const int64_t total = a.n_lead * a.half;
+        const unsigned blocks = static_cast<unsigned>(std::min<int64_t>((total + 255) / 256, 148ll * 64));
+        rope_scalar_kernel<T><<<blocks, 256, 0, st>>>(a, total);
+    }
+}
+
+}  // namespace
+
+void launch_rope(const RopeArgs& a, cudaStream_t st) {
+    if (a.n_lead == 0 || a.half == 0) return;
+    switch (a.dt) {
+        case Dt::F16: launch_typed<__half>(a, st); break;
+        case Dt::BF16: launch_typed<__nv_bfloat16>(a, st); break;
+        case Dt::F32: launch_typed<float>(a, st); break;
+        case Dt::F64: {
+            const int64_t total = a.n_lead * a.half;
+            const unsigned blocks = static_cast<unsigned>(std::min<int64_t>((total + 255) / 256, 148ll * 64));
+            rope_scalar_f64_kernel<<<blocks, 256, 0, st>>>(a, total);
+            break;
+        }
+    }
+}
+
+}  // namespace k
+}  // namespace b200

@@ -1,0 +1,801 @@
+// Paged-KV decode attention: one query token per request against the K/V rows that
+// b_loc names in the pool.
+//
+//   QK    mode = diopiTokenAttentionInference       (functions_lightllm.cpp:53-80)
+//   PV    mode = diopiTokenSoftmaxReduceVInference  (functions_lightllm.cpp:82-107)
+//   FUSED mode = both in one pass; the logits stay in registers.
+//
+// The reference walks the requests on the host, copies each request's rows out of
+// the pool and calls a batched GEMV. Here everything is read on the device and each
+// K/V byte is read once.
+//
+// Split path (the fast one). The (request, token) pairs are flattened in request
+// order and cut into equal ranges, one per CTA, so every CTA streams the same number of
+// bytes whatever the mix of request lengths. Inside a CTA one producer warp looks up the
+// pool slots and issues one bulk asynchronous copy (cp.async.bulk, completion on an
+// mbarrier) per row: the row of a token is contiguous over heads, H*D*e bytes (8 KB at
+// 32 x 128 x fp16). Rows land in a ring of shared-memory stages; 16 consumer warps
+// take 16 bytes of every row each, so one head is spread over D*e/16 neighbouring lanes,
+// the dot product finishes with warp shuffles, and max/sum/accumulator of the online
+// softmax stay in fp32 registers. A CTA writes one partial (m, l, acc[D]) per request
+// it touched into scratch; a second small kernel merges the partials of a request.
+// Scratch slot of (CTA c, request i) is c + i: both only grow along the flattened
+// order, so the sum is unique and at most n_cta + B slots are needed.
+//
+// Algorithmic bytes, fused: 2*sumL*H*D*e (K and V) + 2*B*H*D*e (q, out) + index loads.
+// The scratch traffic, (n_cta + B)*H*(D+2)*4 bytes written and read once, is overhead.
+//
+// Plain path: one CTA per (request, head), any strides, any D up to 512. Used when the
+// rows are not 16-byte aligned/dense or D*e/16 is not 8, 16 or 32.
+#include <cfloat>
+#include <cstdlib>
+
+#include "dev_util.cuh"
+
+namespace b200 {
+namespace k {
+
+namespace {
+
+constexpr int kConsumerWarps = 16;
+constexpr int kConsumerThreads = kConsumerWarps * 32;
+constexpr int kThreads = kConsumerThreads + 32;  // + one producer warp
+constexpr int kMaxB = 2048;                      // request prefix sums live in shared memory
+constexpr int kMaxG = 32;                        // token groups per CTA
+constexpr int kMaxStages = 8;
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // a wait longer than this is given up
+
+struct SplitPlan {
+    int lph;          // lanes (16-byte chunks) per head
+    int hg;           // heads per CTA
+    int n_hg;         // CTAs along the head axis
+    int C;            // chunks per row for a full head group = hg * lph
+    int G;            // token groups: consumer thread = g * C + chunk
+    int TT;           // tokens per stage = G * tpg
+    int tpg;          // tokens per group per stage
+    int nmat;         // matrices streamed: 2 when fused
+    int stage_bytes;  // TT * C * 16 * nmat
+    int nstages;
+    int n_cta;        // CTAs along the flattened token axis
+    int smem_bytes;
+    int off_bars, off_pre, off_red, off_flag;
+};
+
+// ---------------------------------------------------------------------------
+// PTX wrappers: mbarrier + bulk copy.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) { asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory"); }
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+// Waits for the phase with the given parity. Gives up after kWaitLimitNs or as soon as another
+// thread of the CTA has given up; returns false then.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* give_up) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const unsigned long long t0 = global_ns();
+    uint32_t spins = 0;
+    while (!mbar_try_wait(bar, parity)) {
+        if ((++spins & 0xffu) == 0) {
+            if (*give_up) return false;
+            if (global_ns() - t0 > kWaitLimitNs) {
+                *give_up = 1;
+                return false;
+            }
+        }
+    }
+    return true;
+}
+// One contiguous global -> shared copy; both addresses 16-byte aligned, bytes a multiple of 16.
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+                 "l"(__cvta_generic_to_global(src)), "r"(bytes), "r"(bar)
+                 : "memory");
+}
+
+// ---------------------------------------------------------------------------
+// Walks the stages of one CTA's token range. Producer and consumers run the same
+// walk, so nothing but the data itself has to be handed over.
+// ---------------------------------------------------------------------------
+struct StageWalk {
+    const int* pre;  // pre[i] = first flattened token of request i; pre[B] = total
+    int t, t1, i;
+
+    __device__ void init(const int* pre_, int B, int t0_, int t1_) {
+        pre = pre_;
+        t = t0_;
+        t1 = t1_;
+        int lo = 0, hi = B;  // smallest i with pre[i+1] > t
+        while (lo < hi) {
+            const int mid = (lo + hi) >> 1;
+            if (pre[mid + 1] > t)
+                hi = mid;
+            else
+                lo = mid + 1;
+        }
+        i = lo;
+    }
+    // Next stage: tokens [j0, j0+cnt) of request req; last = the request's part in this CTA ends here.
+    __device__ bool next(int TT, int& req, int& j0, int& cnt, bool& last) {
+        if (t >= t1) return false;
+        const int req_end = min(pre[i + 1], t1);
+        cnt = min(TT, req_end - t);
+        req = i;
+        j0 = t - pre[i];
+        t += cnt;
+        last = (t == req_end);
+        if (t == pre[i + 1] && t < t1) {
+            do {
+                ++i;
+            } while (pre[i + 1] == t);
+        }
+        return true;
+    }
+};
+
+// Clamped request length: never negative, never beyond the window b_loc holds.
+__device__ __forceinline__ int request_len(const DecodeArgs& a, int i) {
+    int64_t L = load_index(a.b_len, i);
+    L = L < 0 ? 0 : L;
+    L = L > a.max_input_len ? a.max_input_len : L;
+    return static_cast<int>(L);
+}
+
+template <typename T, int LPH, int MODE, int TPG>
+__global__ void __launch_bounds__(kThreads, 1) decode_split_kernel(const DecodeArgs a, const SplitPlan p, float* __restrict__ ws_acc,
+                                                                    float* __restrict__ ws_ml) {
+    constexpr int EPC = Vec16<T>::N;  // elements per 16-byte chunk
+    constexpr bool kHasK = (MODE != static_cast<int>(DecodeMode::PV));
+    constexpr bool kHasV = (MODE != static_cast<int>(DecodeMode::QK));
+    constexpr bool kFused = (MODE == static_cast<int>(DecodeMode::FUSED));
+
+    extern __shared__ __align__(128) unsigned char smem[];
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + p.off_bars);  // full[nstages], empty[nstages], red[2]
+    int* pre = reinterpret_cast<int*>(smem + p.off_pre);
+    float* red = reinterpret_cast<float*>(smem + p.off_red);
+    volatile int* give_up = reinterpret_cast<volatile int*>(smem + p.off_flag);
+
+    const int tid = threadIdx.x;
+    const int warp = tid >> 5;
+    const int lane = tid & 31;
+    const int cta = blockIdx.x;
+    const int hg0 = blockIdx.y * p.hg;               // first head of this CTA
+    const int heads_here = min(p.hg, a.H - hg0);
+    const int C_eff = heads_here * LPH;               // chunks per row actually copied
+    const uint32_t row_bytes = static_cast<uint32_t>(C_eff) * 16u;
+
+    // ---- set-up: barriers and the prefix sums of the request lengths -------------
+    if (tid == 0) {
+        for (int s = 0; s < p.nstages; ++s) {
+            mbar_init(smem_u32(&bars[s]), 1);                            // full: the producer's arrive + bytes
+            mbar_init(smem_u32(&bars[p.nstages + s]), kConsumerWarps);   // empty: one arrive per consumer warp
+        }
+        mbar_init(smem_u32(&bars[2 * p.nstages]), kConsumerWarps);
+        mbar_init(smem_u32(&bars[2 * p.nstages + 1]), kConsumerWarps);
+        *give_up = 0;
+        pre[0] = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    for (int i = tid; i < a.B; i += kThreads) pre[i + 1] = request_len(a, i);
+    __syncthreads();
+    if (warp == 0) {
+        int carry = 0;
+        for (int base = 0; base < a.B; base += 32) {
+            const int idx = base + lane;
+            int v = idx < a.B ? pre[idx + 1] : 0;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int u = __shfl_up_sync(0xffffffffu, v, o);
+                if (lane >= o) v += u;
+            }
+            if (idx < a.B) pre[idx + 1] = v + carry;
+            carry += __shfl_sync(0xffffffffu, v, 31);
+        }
+    }
+    __syncthreads();
+
+    const int total = pre[a.B];
+    const int t0 = static_cast<int>(static_cast<int64_t>(total) * cta / p.n_cta);
+    const int t1 = static_cast<int>(static_cast<int64_t>(total) * (cta + 1) / p.n_cta);
+    const int TT = p.TT;
+
+    if (warp == kConsumerWarps) {
+        // =========================== producer warp ===============================
+        const char* kbase = kHasK ? static_cast<const char*>(a.kmat) + static_cast<int64_t>(hg0) * a.k_s1 * sizeof(T) : nullptr;
+        const char* vbase = kHasV ? static_cast<const char*>(a.vmat) + static_cast<int64_t>(hg0) * a.v_s1 * sizeof(T) : nullptr;
+        const int64_t k_row = a.k_s0 * static_cast<int64_t>(sizeof(T));
+        const int64_t v_row = a.v_s0 * static_cast<int64_t>(sizeof(T));
+        const uint32_t v_off = kFused ? static_cast<uint32_t>(TT) * static_cast<uint32_t>(p.C) * 16u : 0u;
+
+        StageWalk walk;
+        walk.init(pre, a.B, t0, t1);
+        int req, j0, cnt;
+        bool last;
+        bool have = walk.next(TT, req, j0, cnt, last);
+        int64_t slot[TPG];
+        auto fetch_slots = [&](int r, int j, int n, int64_t (&out)[TPG]) {
+            const int L = pre[r + 1] - pre[r];
+            const int64_t col0 = static_cast<int64_t>(a.max_input_len) - L + j;
+#pragma unroll
+            for (int u = 0; u < TPG; ++u) {
+                const int t = lane + 32 * u;
+                out[u] = 0;
+                if (t < n) {
+                    int64_t s = load_index(a.b_loc, r, col0 + t);
+                    if (s < 0 || s >= a.slots) {
+                        report_status(a.status, 1);
+                        s = 0;  // keep the byte count of the stage intact
+                    }
+                    out[u] = s;
+                }
+            }
+        };
+        if (have) fetch_slots(req, j0, cnt, slot);
+        int n = 0;
+        while (have) {
+            const int cur_cnt = cnt;
+            int64_t cur_slot[TPG];
+#pragma unroll
+            for (int u = 0; u < TPG; ++u) cur_slot[u] = slot[u];
+            // Look up the next stage's slots before blocking, so that load overlaps the wait.
+            have = walk.next(TT, req, j0, cnt, last);
+            if (have) fetch_slots(req, j0, cnt, slot);
+
+            const int s = n % p.nstages;
+            const uint32_t parity = static_cast<uint32_t>((n / p.nstages) & 1);
+            if (!mbar_wait(smem_u32(&bars[p.nstages + s]), parity ^ 1u, give_up)) break;
+            const uint32_t full = smem_u32(&bars[s]);
+            if (lane == 0) mbar_arrive_expect_tx(full, static_cast<uint32_t>(cur_cnt) * row_bytes * static_cast<uint32_t>(p.nmat));
+            __syncwarp();
+            const uint32_t stage = smem_u32(smem + static_cast<size_t>(s) * p.stage_bytes);
+#pragma unroll
+            for (int u = 0; u < TPG; ++u) {
+                const int t = lane + 32 * u;
+                if (t < cur_cnt) {
+                    if (kHasK) bulk_g2s(stage + static_cast<uint32_t>(t) * row_bytes, kbase + cur_slot[u] * k_row, row_bytes, full);
+                    if (kHasV) bulk_g2s(stage + v_off + static_cast<uint32_t>(t) * row_bytes, vbase + cur_slot[u] * v_row, row_bytes, full);
+                }
+            }
+            ++n;
+        }
+    } else {
+        // =========================== consumer warps ==============================
+        const int GC = p.G * p.C;
+        int g = tid / p.C;
+        int c = tid - g * p.C;
+        const bool real = (tid < GC) && (c < C_eff);
+        if (!real) {  // shadow threads mirror group 0 so that shuffles stay full-warp; they never store
+            g = 0;
+            c = c % LPH;
+        }
+        const int hl = c / LPH;    // head within this CTA's group
+        const int lih = c % LPH;   // lane within the head
+        const int h = hg0 + hl;
+        const uint32_t v_off = kFused ? static_cast<uint32_t>(TT) * static_cast<uint32_t>(p.C) * 16u : 0u;
+        const float sqrt_d = sqrtf(static_cast<float>(a.D));
+        const float qscale = kLog2e / sqrt_d;  // softmax runs in base 2
+
+        float qreg[EPC];
+        float acc[EPC];
+        float m = -INFINITY, l = 0.f;
+        int cur_req = -1;
+        int64_t att_col0 = 0;
+        uint32_t red_phase = 0;
+
+        StageWalk walk;
+        walk.init(pre, a.B, t0, t1);
+        int req, j0, cnt;
+        bool last;
+        int n = 0;
+        while (walk.next(TT, req, j0, cnt, last)) {
+            if (req != cur_req) {
+                cur_req = req;
+                m = -INFINITY;
+                l = 0.f;
+#pragma unroll
+                for (int e = 0; e < EPC; ++e) acc[e] = 0.f;
+                if (kHasK) {
+                    const T* qp = static_cast<const T*>(a.q) + static_cast<int64_t>(req) * a.q_s0 + static_cast<int64_t>(h) * a.q_s1 + lih * EPC;
+                    if (MODE == static_cast<int>(DecodeMode::QK)) {
+                        // The reference divides the finished dot product by sqrt(D); do the same at the store.
+#pragma unroll
+                        for (int e = 0; e < EPC; ++e) qreg[e] = Cvt<T>::to_f(qp[e]);
+                    } else {
+#pragma unroll
+                        for (int e = 0; e < EPC; ++e) qreg[e] = Cvt<T>::to_f(qp[e]) * qscale;
+                    }
+                }
+                if (!kFused) att_col0 = load_index(a.b_start, req);
+            }
+            const int s = n % p.nstages;
+            const uint32_t parity = static_cast<uint32_t>((n / p.nstages) & 1);
+
+            float sc[TPG];
+            if (!kHasK) {
+                // Stored logits: fetch them before blocking on the V rows.
+#pragma unroll
+                for (int u = 0; u < TPG; ++u) {
+                    const int t = g + u * p.G;
+                    const int64_t col = att_col0 + j0 + t;
+                    sc[u] = -INFINITY;
+                    if (t < cnt && col >= 0 && col < a.att_cols)
+                        sc[u] = Cvt<T>::to_f(static_cast<const T*>(a.att)[static_cast<int64_t>(h) * a.att_s0 + col * a.att_s1]) * kLog2e;
+                }
+            }
+            if (!mbar_wait(smem_u32(&bars[s]), parity, give_up)) break;
+            const unsigned char* stage = smem + static_cast<size_t>(s) * p.stage_bytes;
+
+            if (kHasK) {
+#pragma unroll
+                for (int u = 0; u < TPG; ++u) {
+                    const int t = g + u * p.G;
+                    float part = 0.f;
+                    if (t < cnt) {
+                        const uint4 kv = *reinterpret_cast<const uint4*>(stage + static_cast<uint32_t>(t) * row_bytes + c * 16);
+                        float f[EPC];
+                        unpack16<T>(kv, f);
+#pragma unroll
+                        for (int e = 0; e < EPC; ++e) part = fmaf(qreg[e], f[e], part);
+                    }
+#pragma unroll
+                    for (int o = LPH / 2; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+                    sc[u] = (t < cnt) ? part : -INFINITY;
+                }
+            }
+            if (MODE == static_cast<int>(DecodeMode::QK)) {
+                if (real && lih == 0) {
+#pragma unroll
+                    for (int u = 0; u < TPG; ++u) {
+                        const int t = g + u * p.G;
+                        const int64_t col = att_col0 + j0 + t;
+                        if (t < cnt && col >= 0 && col < a.att_cols)
+                            static_cast<T*>(a.att)[static_cast<int64_t>(h) * a.att_s0 + col * a.att_s1] = Cvt<T>::from_f(sc[u] / sqrt_d);
+                    }
+                }
+            } else {
+                float m_new = m;
+#pragma unroll
+                for (int u = 0; u < TPG; ++u) m_new = fmaxf(m_new, sc[u]);
+                const float m_ref = (m_new == -INFINITY) ? 0.f : m_new;
+                const float alpha = exp2f(m - m_ref);
+                l *= alpha;
+#pragma unroll
+                for (int e = 0; e < EPC; ++e) acc[e] *= alpha;
+#pragma unroll
+                for (int u = 0; u < TPG; ++u) {
+                    const int t = g + u * p.G;
+                    if (t < cnt) {
+                        const float pr = exp2f(sc[u] - m_ref);
+                        l += pr;
+                        const uint4 vv = *reinterpret_cast<const uint4*>(stage + v_off + static_cast<uint32_t>(t) * row_bytes + c * 16);
+                        float f[EPC];
+                        unpack16<T>(vv, f);
+#pragma unroll
+                        for (int e = 0; e < EPC; ++e) acc[e] = fmaf(pr, f[e], acc[e]);
+                    }
+                }
+                m = m_new;
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&bars[p.nstages + s]));
+            ++n;
+
+            if (last && kHasV) {
+                // The request's part in this CTA is done: merge the token groups, then store the partial.
+                if (p.G > 1) {
+                    if (tid < GC) {
+                        red[tid * (EPC + 2) + 0] = m;
+                        red[tid * (EPC + 2) + 1] = l;
+#pragma unroll
+                        for (int e = 0; e < EPC; ++e) red[tid * (EPC + 2) + 2 + e] = acc[e];
+                    }
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(smem_u32(&bars[2 * p.nstages]));
+                    if (!mbar_wait(smem_u32(&bars[2 * p.nstages]), red_phase, give_up)) break;
+                    if (real && g == 0) {
+                        float M = m;
+                        for (int gg = 1; gg < p.G; ++gg) M = fmaxf(M, red[(gg * p.C + c) * (EPC + 2)]);
+                        const float Mr = (M == -INFINITY) ? 0.f : M;
+                        const float w0 = exp2f(m - Mr);
+                        l *= w0;
+#pragma unroll
+                        for (int e = 0; e < EPC; ++e) acc[e] *= w0;
+                        for (int gg = 1; gg < p.G; ++gg) {
+                            const float* r = &red[(gg * p.C + c) * (EPC + 2)];
+                            const float w = exp2f(r[0] - Mr);
+                            l = fmaf(r[1], w, l);
+#pragma unroll
+                            for (int e = 0; e < EPC; ++e) acc[e] = fmaf(r[2 + e], w, acc[e]);
+                        }
+                        m = M;
+                    }
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(smem_u32(&bars[2 * p.nstages + 1]));
+                    if (!mbar_wait(smem_u32(&bars[2 * p.nstages + 1]), red_phase, give_up)) break;
+                    red_phase ^= 1u;
+                }
+                if (real && g == 0) {
+                    const int64_t slot_id = static_cast<int64_t>(cta) + req;
+                    float* dst = ws_acc + (slot_id * a.H + h) * a.D + lih * EPC;
+#pragma unroll
+                    for (int e = 0; e < EPC; e += 4) *reinterpret_cast<float4*>(dst + e) = make_float4(acc[e], acc[e + 1], acc[e + 2], acc[e + 3]);
+                    if (lih == 0) *reinterpret_cast<float2*>(ws_ml + (slot_id * a.H + h) * 2) = make_float2(m, l);
+                }
+            }
+        }
+    }
+
+    // A thread that gave up a wait reports it; copies that might still be in flight get time to land
+    // before the shared memory of the CTA is released.
+    if (*give_up) {
+        if (lane == 0) report_status(a.status, 3);
+        const unsigned long long t_begin = global_ns();
+        while (global_ns() - t_begin < 2000000ull) __nanosleep(1000);
+    }
+}
+
+// Merges the partials of one (request, head) and writes out[i,h,:]. One warp each.
+template <typename T>
+__global__ void __launch_bounds__(128) decode_combine_kernel(const DecodeArgs a, int n_cta, const float* __restrict__ ws_acc,
+                                                              const float* __restrict__ ws_ml) {
+    __shared__ int s_part[4][2];
+    const int i = blockIdx.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // start = sum of the lengths before request i, total = sum of all lengths
+    int before = 0, all = 0;
+    for (int r = threadIdx.x; r < a.B; r += blockDim.x) {
+        const int L = request_len(a, r);
+        all += L;
+        if (r < i) before += L;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        before += __shfl_xor_sync(0xffffffffu, before, o);
+        all += __shfl_xor_sync(0xffffffffu, all, o);
+    }
+    if (lane == 0) {
+        s_part[warp][0] = before;
+        s_part[warp][1] = all;
+    }
+    __syncthreads();
+    before = s_part[0][0] + s_part[1][0] + s_part[2][0] + s_part[3][0];
+    all = s_part[0][1] + s_part[1][1] + s_part[2][1] + s_part[3][1];
+
+    const int h = blockIdx.y * 4 + warp;
+    if (h >= a.H) return;
+    const int L = request_len(a, i);
+    constexpr int R = 8;  // D <= 256 on this path
+    float acc[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) acc[r] = 0.f;
+    float M = -INFINITY, Lsum = 0.f;
+    if (L > 0) {
+        auto first_token = [&](int c) { return static_cast<int>(static_cast<int64_t>(all) * c / n_cta); };
+        auto cta_of = [&](int t) {  // largest c with first_token(c) <= t
+            int lo = 0, hi = n_cta - 1;
+            while (lo < hi) {
+                const int mid = (lo + hi + 1) >> 1;
+                if (first_token(mid) <= t)
+                    lo = mid;
+                else
+                    hi = mid - 1;
+            }
+            return lo;
+        };
+        const int c_first = cta_of(before), c_last = cta_of(before + L - 1);
+        for (int c = c_first; c <= c_last; ++c) {
+            if (first_token(c) == first_token(c + 1)) continue;  // an empty range wrote nothing
+            const int64_t slot_id = static_cast<int64_t>(c) + i;
+            const float2 ml = *reinterpret_cast<const float2*>(ws_ml + (slot_id * a.H + h) * 2);
+            if (ml.x == -INFINITY) continue;
+            const float Mn = fmaxf(M, ml.x);
+            const float wo = exp2f(M - Mn), wn = exp2f(ml.x - Mn);
+            Lsum = Lsum * wo + ml.y * wn;
+            const float* src = ws_acc + (slot_id * a.H + h) * a.D;
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+                const int d = lane + 32 * r;
+                if (d < a.D) acc[r] = acc[r] * wo + src[d] * wn;
+            }
+            M = Mn;
+        }
+    }
+    const float inv = Lsum > 0.f ? 1.f / Lsum : 0.f;
+    T* o = static_cast<T*>(a.out) + static_cast<int64_t>(i) * a.out_s0 + static_cast<int64_t>(h) * a.out_s1;
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+        const int d = lane + 32 * r;
+        if (d < a.D) o[d * a.out_s2] = Cvt<T>::from_f(acc[r] * inv);
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Plain path: one CTA of 4 warps per (request, head); warps stride over the tokens,
+// lanes over D. No scratch, any strides.
+// ---------------------------------------------------------------------------
+template <typename T, int MODE>
+__global__ void __launch_bounds__(128) decode_plain_kernel(const DecodeArgs a) {
+    constexpr int R = 16;  // D <= 512
+    constexpr bool kHasK = (MODE != static_cast<int>(DecodeMode::PV));
+    constexpr bool kHasV = (MODE != static_cast<int>(DecodeMode::QK));
+    __shared__ float s_m[4], s_l[4];
+    __shared__ float s_acc[4][512];
+    const int i = blockIdx.x, h = blockIdx.y;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int L = request_len(a, i);
+    const int64_t col0 = load_index(a.b_start, i);
+    const float inv_sqrt_d = 1.0f / sqrtf(static_cast<float>(a.D));
+
+    float qf[R], acc[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+        acc[r] = 0.f;
+        qf[r] = 0.f;
+        const int d = lane + 32 * r;
+        if (kHasK && d < a.D) qf[r] = Cvt<T>::to_f(static_cast<const T*>(a.q)[static_cast<int64_t>(i) * a.q_s0 + static_cast<int64_t>(h) * a.q_s1 + d * a.q_s2]);
+    }
+    float m = -INFINITY, l = 0.f;
+    for (int j = warp; j < L; j += 4) {
+        int64_t slot = load_index(a.b_loc, i, static_cast<int64_t>(a.max_input_len) - L + j);
+        if (slot < 0 || slot >= a.slots) {
+            if (lane == 0) report_status(a.status, 1);
+            continue;
+        }
+        const int64_t col = col0 + j;
+        float sc;
+        if (kHasK) {
+            const T* kp = static_cast<const T*>(a.kmat) + slot * a.k_s0 + static_cast<int64_t>(h) * a.k_s1;
+            float part = 0.f;
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+                const int d = lane + 32 * r;
+                if (d < a.D) part = fmaf(qf[r], Cvt<T>::to_f(kp[d * a.k_s2]), part);
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+            sc = part * inv_sqrt_d;
+            if (MODE == static_cast<int>(DecodeMode::QK)) {
+                if (lane == 0 && col >= 0 && col < a.att_cols) static_cast<T*>(a.att)[static_cast<int64_t>(h) * a.att_s0 + col * a.att_s1] = Cvt<T>::from_f(sc);
+                continue;
+            }
+        } else {
+            if (col < 0 || col >= a.att_cols) continue;
+            sc = Cvt<T>::to_f(static_cast<const T*>(a.att)[static_cast<int64_t>(h) * a.att_s0 + col * a.att_s1]);
+        }
+        if (kHasV) {
+            sc *= kLog2e;
+            const float m_new = fmaxf(m, sc);
+            const float alpha = exp2f(m - m_new), pr = exp2f(sc - m_new);
+            l = l * alpha + pr;
+            const T* vp = static_cast<const T*>(a.vmat) + slot * a.v_s0 + static_cast<int64_t>(h) * a.v_s1;
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+                const int d = lane + 32 * r;
+                if (d < a.D) acc[r] = fmaf(pr, Cvt<T>::to_f(vp[d * a.v_s2]), acc[r] * alpha);
+            }
+            m = m_new;
+        }
+    }
+    if (!kHasV) return;
+    if (lane == 0) {
+        s_m[warp] = m;
+        s_l[warp] = l;
+    }
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+        const int d = lane + 32 * r;
+        if (d < a.D) s_acc[warp][d] = acc[r];
+    }
+    __syncthreads();
+    if (warp == 0) {
+        const float M = fmaxf(fmaxf(s_m[0], s_m[1]), fmaxf(s_m[2], s_m[3]));
+        const float Mr = (M == -INFINITY) ? 0.f : M;
+        float w[4], Ls = 0.f;
+#pragma unroll
+        for (int x = 0; x < 4; ++x) {
+            w[x] = exp2f(s_m[x] - Mr);
+            Ls += s_l[x] * w[x];
+        }
+        const float inv = Ls > 0.f ? 1.f / Ls : 0.f;
+        T* o = static_cast<T*>(a.out) + static_cast<int64_t>(i) * a.out_s0 + static_cast<int64_t>(h) * a.out_s1;
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            const int d = lane + 32 * r;
+            if (d < a.D) {
+                const float v = s_acc[0][d] * w[0] + s_acc[1][d] * w[1] + s_acc[2][d] * w[2] + s_acc[3][d] * w[3];
+                o[d * a.out_s2] = Cvt<T>::from_f(v * inv);
+            }
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Host side: path choice and launch.
+// ---------------------------------------------------------------------------
+int elem_bytes(Dt dt) { return dt == Dt::F32 ? 4 : 2; }
+
+int env_int(const char* name, int dflt) {
+    const char* v = std::getenv(name);
+    if (!v || !*v) return dflt;
+    return std::atoi(v);
+}
+
+// Fills `p` when the arguments qualify for the split path.
+bool make_split_plan(const DecodeArgs& a, int sm_count, int max_smem, SplitPlan& p) {
+    if (a.dt == Dt::F64) return false;
+    if (env_int("DIOPI_B200_DECODE_PLAIN", 0)) return false;
+    const int e = elem_bytes(a.dt);
+    const bool has_k = a.mode != DecodeMode::PV, has_v = a.mode != DecodeMode::QK;
+    if ((a.D * e) % 16 != 0) return false;
+    const int lph = a.D * e / 16;
+    if (lph != 8 && lph != 16 && lph != 32) return false;
+    if (a.B > kMaxB || a.B <= 0) return false;
+    if (static_cast<int64_t>(a.B) * a.max_input_len >= (1ll << 31)) return false;
+    auto rows_ok = [&](const void* ptr, int64_t s0, int64_t s1, int64_t s2) {
+        return (a.D == 1 || s2 == 1) && (a.H == 1 || s1 == a.D) && (s0 * e) % 16 == 0 && reinterpret_cast<uintptr_t>(ptr) % 16 == 0;
+    };
+    if (has_k && !rows_ok(a.kmat, a.k_s0, a.k_s1, a.k_s2)) return false;
+    if (has_v && !rows_ok(a.vmat, a.v_s0, a.v_s1, a.v_s2)) return false;
+    if (has_k && a.q_s2 != 1 && a.D != 1) return false;
+
+    p.lph = lph;
+    p.hg = std::min(a.H, kConsumerThreads / lph);
+    p.n_hg = (a.H + p.hg - 1) / p.hg;
+    p.C = p.hg * lph;
+    p.G = std::min(kConsumerThreads / p.C, kMaxG);
+    p.tpg = (a.mode == DecodeMode::FUSED) ? env_int("DIOPI_B200_DECODE_TPG", 4) : 4;
+    if (p.tpg != 2 && p.tpg != 4) p.tpg = 4;
+    p.TT = p.G * p.tpg;
+    p.nmat = (has_k && has_v) ? 2 : 1;
+    p.stage_bytes = p.TT * p.C * 16 * p.nmat;
+    const int ctas_per_sm = std::max(1, std::min(2, env_int("DIOPI_B200_DECODE_CTAS_PER_SM", 1)));
+
+    const int red_bytes = (p.G > 1 && has_v) ? kConsumerThreads * (16 / e + 2) * 4 : 0;
+    int off = 0;
+    auto take = [&](int bytes, int align) {
+        off = (off + align - 1) / align * align;
+        const int at = off;
+        off += bytes;
+        return at;
+    };
+    const int budget = max_smem / ctas_per_sm - (ctas_per_sm > 1 ? 1024 : 0);
+    // everything but the stages
+    int fixed = 0;
+    {
+        off = 0;
+        take((2 * kMaxStages + 2) * 8, 8);
+        take((a.B + 1) * 4, 4);
+        take(red_bytes, 16);
+        take(4, 4);
+        fixed = off + 128;
+    }
+    int nst = (budget - fixed) / p.stage_bytes;
+    nst = std::min(nst, std::min(kMaxStages, std::max(2, env_int("DIOPI_B200_DECODE_STAGES", kMaxStages))));
+    if (nst < 2) return false;
+    p.nstages = nst;
+    off = nst * p.stage_bytes;
+    p.off_bars = take((2 * kMaxStages + 2) * 8, 8);
+    p.off_pre = take((a.B + 1) * 4, 4);
+    p.off_red = take(red_bytes, 16);
+    p.off_flag = take(4, 4);
+    p.smem_bytes = off;
+
+    // One CTA per SM (times ctas_per_sm) over the head groups, but no more CTAs than there can be work for.
+    int n_cta = std::max(1, sm_count * ctas_per_sm / p.n_hg);
+    const int64_t max_tokens = static_cast<int64_t>(a.B) * a.max_input_len;
+    const int64_t useful = std::max<int64_t>(1, (max_tokens + 2 * p.TT - 1) / (2 * p.TT));
+    n_cta = static_cast<int>(std::min<int64_t>(n_cta, useful));
+    p.n_cta = n_cta;
+    return true;
+}
+
+template <typename T, int LPH, int MODE>
+void launch_split_t(const DecodeArgs& a, const SplitPlan& p, float* ws_acc, float* ws_ml, cudaStream_t st) {
+    dim3 grid(p.n_cta, p.n_hg);
+    if (p.tpg == 2 && MODE == static_cast<int>(DecodeMode::FUSED)) {
+        auto kern = decode_split_kernel<T, LPH, MODE, (MODE == static_cast<int>(DecodeMode::FUSED) ? 2 : 4)>;
+        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, p.smem_bytes);
+        kern<<<grid, kThreads, p.smem_bytes, st>>>(a, p, ws_acc, ws_ml);
+    } else {
+        auto kern = decode_split_kernel<T, LPH, MODE, 4>;
+        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, p.smem_bytes);
+        kern<<<grid, kThreads, p.smem_bytes, st>>>(a, p, ws_acc, ws_ml);
+    }
+    if (MODE != static_cast<int>(DecodeMode::QK)) {
+        dim3 cgrid(a.B, (a.H + 3) / 4);
+        decode_combine_kernel<T><<<cgrid, 128, 0, st>>>(a, p.n_cta, ws_acc, ws_ml);
+    }
+}
+
+template <typename T, int MODE>
+void launch_split_lph(const DecodeArgs& a, const SplitPlan& p, float* ws_acc, float* ws_ml, cudaStream_t st) {
+    switch (p.lph) {
+        case 8: launch_split_t<T, 8, MODE>(a, p, ws_acc, ws_ml, st); break;
+        case 16: launch_split_t<T, 16, MODE>(a, p, ws_acc, ws_ml, st); break;
+        default: launch_split_t<T, 32, MODE>(a, p, ws_acc, ws_ml, st); break;
+    }
+}
+
+template <typename T>
+void launch_split_mode(const DecodeArgs& a, const SplitPlan& p, float* ws_acc, float* ws_ml, cudaStream_t st) {
+    switch (a.mode) {
+        case DecodeMode::QK: launch_split_lph<T, 0>(a, p, ws_acc, ws_ml, st); break;
+        case DecodeMode::PV: launch_split_lph<T, 1>(a, p, ws_acc, ws_ml, st); break;
+        default: launch_split_lph<T, 2>(a, p, ws_acc, ws_ml, st); break;
+    }
+}
+
+template <typename T>
+void launch_plain_mode(const DecodeArgs& a, cudaStream_t st) {
+    dim3 grid(a.B, a.H);
+    switch (a.mode) {
+        case DecodeMode::QK: decode_plain_kernel<T, 0><<<grid, 128, 0, st>>>(a); break;
+        case DecodeMode::PV: decode_plain_kernel<T, 1><<<grid, 128, 0, st>>>(a); break;
+        default: decode_plain_kernel<T, 2><<<grid, 128, 0, st>>>(a); break;
+    }
+}
+
+int64_t split_ws_floats_acc(const DecodeArgs& a, const SplitPlan& p) { return static_cast<int64_t>(p.n_cta + a.B) * a.H * a.D; }
+int64_t split_ws_floats_ml(const DecodeArgs& a, const SplitPlan& p) { return static_cast<int64_t>(p.n_cta + a.B) * a.H * 2; }
+
+}  // namespace
+
+int64_t decode_workspace_bytes(const DecodeArgs& a, int sm_count, int max_smem) {
+    SplitPlan p;
+    if (a.mode == DecodeMode::QK) return 0;
+    if (!make_split_plan(a, sm_count, max_smem, p)) return 0;
+    return (split_ws_floats_acc(a, p) + split_ws_floats_ml(a, p)) * 4 + 256;
+}
+
+void launch_decode(const DecodeArgs& a, void* ws, int sm_count, int max_smem, cudaStream_t st) {
+    if (a.B <= 0 || a.H <= 0 || a.D <= 0) return;
+    SplitPlan p;
+    if (make_split_plan(a, sm_count, max_smem, p)) {
+        float* ws_acc = nullptr;
+        float* ws_ml = nullptr;
+        if (a.mode != DecodeMode::QK) {
+            // 256-byte aligned start, acc block first (its size is a multiple of 16 bytes)
+            uintptr_t base = (reinterpret_cast<uintptr_t>(ws) + 255) & ~static_cast<uintptr_t>(255);
+            ws_acc = reinterpret_cast<float*>(base);
+            ws_ml = ws_acc + split_ws_floats_acc(a, p);
+        }
+        switch (a.dt) {
+            case Dt::F16: launch_split_mode<__half>(a, p, ws_acc, ws_ml, st); break;
+            case Dt::BF16: launch_split_mode<__nv_bfloat16>(a, p, ws_acc, ws_ml, st); break;
+            default: launch_split_mode<float>(a, p, ws_acc, ws_ml, st); break;
+        }
+        return;
+    }
+    switch (a.dt) {
+        case Dt::F16: launch_plain_mode<__half>(a, st); break;
+        case Dt::BF16: launch_plain_mode<__nv_bfloat16>(a, st); break;
+        case Dt::F32: launch_plain_mode<float>(a, st); break;
+        default: break;  // fp64 is refused by the caller
+    }
+}
+
+}  // namespace k
+}  // namespace b200

@@ -1,0 +1,108 @@
+"""Python call forms of the ops, with the names and argument order of the reference's
+wrappers (diopi_test/python/conformance/diopi_functions.py: rotary_emb 7030, rms_norm 7040,
+apply_penalty 7851, destindex_copy_kv 7896, token_attention 7905, token_softmax_reducev 7914,
+context_attention 7942). Each takes torch CUDA tensors, wraps them as DIOPI handles and makes
+exactly one call through the C ABI of libdiopi_impl.so on torch's current stream.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _lib
+from .runtime import Context, Sizes, Tensor, check_returncode, default_context
+
+
+def _impl():
+    return _lib.load().impl
+
+
+def _t(x, as_device=None):
+    if x is None or isinstance(x, Tensor):
+        return x
+    return Tensor(x, as_device=as_device)
+
+
+def _h(x):
+    return None if x is None else x.handle
+
+
+def _call(name: str, ctx: Context | None, *args):
+    ctx = ctx or default_context()
+    rc = getattr(_impl(), name)(ctx.handle, *args)
+    check_returncode(name, rc)
+
+
+def vendor_name() -> str:
+    return _impl().diopiGetVendorName().decode()
+
+
+def impl_version() -> str:
+    return _impl().diopiGetImplVersion().decode()
+
+
+def last_error() -> str:
+    return _impl().diopiGetLastErrorString().decode(errors="replace")
+
+
+def destindex_copy_kv(k, dest_loc, out, *, ctx=None, as_device=None):
+    """out[dest_loc] = k; returns out."""
+    tk, td, to = _t(k, as_device), _t(dest_loc, as_device), _t(out, as_device)
+    _call("diopiDestIndexCopyKV", ctx, _h(to), _h(tk), _h(td))
+    return out
+
+
+def token_attention(q, k, out, b_loc, b_start_loc, b_seq_len, max_input_len, *, ctx=None, as_device=None):
+    """Decode logits into out [H, sum(L)]; returns out."""
+    ts = [_t(x, as_device) for x in (out, q, k, b_loc, b_start_loc, b_seq_len)]
+    _call("diopiTokenAttentionInference", ctx, *[_h(t) for t in ts], int(max_input_len))
+    return out
+
+
+def token_softmax_reducev(logics, v, out, b_loc, b_start_loc, b_seq_len, max_input_len, other_kv_index, *, ctx=None, as_device=None):
+    """softmax(logics) @ v per request into out [B, H, D]; returns out."""
+    ts = [_t(x, as_device) for x in (out, logics, v, b_loc, b_start_loc, b_seq_len)]
+    _call("diopiTokenSoftmaxReduceVInference", ctx, *[_h(t) for t in ts], int(max_input_len), int(other_kv_index))
+    return out
+
+
+def token_decode_attention(q, k, v, out, b_loc, b_start_loc, b_seq_len, max_input_len, *, ctx=None, as_device=None):
+    """The fused decode step (token_attention then token_softmax_reducev in one pass); returns out."""
+    ts = [_t(x, as_device) for x in (out, q, k, v, b_loc, b_start_loc, b_seq_len)]
+    _call("diopiTokenDecodeAttentionInference", ctx, *[_h(t) for t in ts], int(max_input_len))
+    return out
+
+
+def context_attention(q, k, v, out, b_start_loc, b_seq_len, max_input_len, *, ctx=None, as_device=None):
+    """Causal prefill over the packed ragged batch; returns out."""
+    ts = [_t(x, as_device) for x in (out, q, k, v, b_start_loc, b_seq_len)]
+    _call("diopiContextAttentionInference", ctx, *[_h(t) for t in ts], int(max_input_len))
+    return out
+
+
+def apply_penalty(logits, presence_penalty, frequency_penalty, p_token_ids, p_token_counts, p_cumsum_seq_len,
+                  p_max_len_in_batch, *, ctx=None, as_device=None):
+    """In-place presence/frequency penalty; returns logits."""
+    ts = [_t(x, as_device) for x in (logits, presence_penalty, frequency_penalty, p_token_ids, p_token_counts, p_cumsum_seq_len)]
+    _call("diopiApplyPenalty", ctx, *[_h(t) for t in ts], int(p_max_len_in_batch))
+    return logits
+
+
+def rotary_emb(input, cos, sin, conj, interleaved, *, out=None, ctx=None, as_device=None):
+    """Returns a new tensor like input (or fills `out`)."""
+    if out is None:
+        out = torch.empty_like(input)
+    ts = [_t(x, as_device) for x in (out, input, cos, sin)]
+    _call("diopiRotaryEmbedding", ctx, *[_h(t) for t in ts], bool(conj), bool(interleaved))
+    return out
+
+
+def rms_norm(input, normalized_shape, weight, bias, eps, *, return_inv_rms=False, ctx=None, as_device=None):
+    """Returns out (and inv_rms when asked). inv_rms is fp32 for fp16/bf16/fp32 input, fp64 for fp64."""
+    out = torch.empty_like(input)
+    n = len(normalized_shape)
+    inv_dtype = torch.float64 if input.dtype == torch.float64 else torch.float32
+    inv_rms = torch.empty(tuple(input.shape[: input.dim() - n]), dtype=inv_dtype, device=input.device)
+    ts = [_t(x, as_device) for x in (out, inv_rms, input)]
+    tw, tb = _t(weight, as_device), _t(bias, as_device)
+    _call("diopiRMSNorm", ctx, _h(ts[0]), _h(ts[1]), _h(ts[2]), Sizes(normalized_shape), _h(tw), _h(tb), float(eps))
+    return (out, inv_rms) if return_inv_rms else out

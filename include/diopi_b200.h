@@ -1,0 +1,198 @@
+/*
+ * diopi_b200.h — the C ABI of the B200 backend (libdiopi_impl.so).
+ *
+ * The library is a drop-in DIOPI backend for the LLM-inference hot path. A DIOPI
+ * consumer owns tensors, contexts and streams and hands them over as opaque
+ * handles; the backend reads them only through the run-time accessors declared
+ * in the first half of this file (the consumer defines those), launches its
+ * kernels on the stream of the context it was given, and returns without
+ * synchronising.
+ *
+ * Every enum value, struct layout and prototype here is ABI-identical to the
+ * DIOPI interface headers it stands in for (proto/include/diopi/diopirt.h,
+ * proto/include/diopi/functions.h, proto/include/diopi/functions_ext.h). When the
+ * consumer has already included the original diopirt.h, the type block below is
+ * skipped and only the prototypes are (re)declared, so a translation unit may
+ * include both; a mismatch then fails to compile.
+ */
+#ifndef DIOPI_B200_H_
+#define DIOPI_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+#if !defined(__cplusplus)
+#include <stdbool.h>
+#endif
+
+#if defined(__cplusplus)
+extern "C" {
+#endif
+
+/* ------------------------------------------------------------------------- */
+/* Run-time types (stand in for proto/include/diopi/diopirt.h:27-112).        */
+/* ------------------------------------------------------------------------- */
+#ifndef _PROJECT_DIOPERATOR_INTERFACE_RT_H_
+
+/* A borrowed array of int64: shapes, strides, normalized_shape. Passed by value. */
+typedef struct {
+    const int64_t* data;
+    int64_t len;
+} diopiSize_t;
+
+/* Return codes. Only the four values the backend can return are spelled out
+ * with their own names; the numeric gaps belong to the consumer-side run time. */
+typedef enum {
+    diopiSuccess = 0,
+    diopiErrorOccurred = 1,
+    diopiNotInited = 2,
+    diopiNoRegisteredStreamCreateFunction = 3,
+    diopiNoRegisteredStreamDestoryFunction = 4,
+    diopiNoRegisteredStreamSyncFunction = 5,
+    diopiNoRegisteredDeviceMemoryMallocFunction = 6,
+    diopiNoRegisteredDeviceMemoryFreeFunction = 7,
+    diopiNoRegisteredDevice2DdeviceMemoryCopyFunction = 8,
+    diopiNoRegisteredDevice2HostMemoryCopyFunction = 9,
+    diopiNoRegisteredHost2DeviceMemoryCopyFunction = 10,
+    diopiNoRegisteredGetLastErrorFunction = 11,
+    diopi5DNotSupported = 12,
+    diopiNoImplement = 13,
+    diopiForceFallbackToCPU = 14,
+    diopiDtypeNotSupported = 1000
+} diopiError_t;
+
+typedef enum { diopi_host = 0, diopi_device = 1 } diopiDevice_t;
+
+typedef int8_t diopiDeviceIndex_t;
+
+typedef enum {
+    diopi_dtype_int8 = 0,
+    diopi_dtype_uint8 = 1,
+    diopi_dtype_int16 = 2,
+    diopi_dtype_uint16 = 3,
+    diopi_dtype_int32 = 4,
+    diopi_dtype_uint32 = 5,
+    diopi_dtype_int64 = 6,
+    diopi_dtype_uint64 = 7,
+    diopi_dtype_float16 = 8,
+    diopi_dtype_float32 = 9,
+    diopi_dtype_float64 = 10,
+    diopi_dtype_bool = 11,
+    diopi_dtype_bfloat16 = 12,
+    diopi_dtype_tfloat32 = 13,
+    diopi_dtype_complex32 = 14,
+    diopi_dtype_complex64 = 15,
+    diopi_dtype_complex128 = 16,
+    diopi_dtype_unsupported = 255
+} diopiDtype_t;
+
+/* Opaque handles: the backend never looks inside them. */
+struct diopiContext;
+typedef struct diopiContext* diopiContextHandle_t;
+struct diopiTensor;
+typedef struct diopiTensor* diopiTensorHandle_t;
+typedef const struct diopiTensor* diopiConstTensorHandle_t;
+typedef void* diopiStreamHandle_t; /* a cudaStream_t for this backend */
+
+#define DIOPI_B200_OWN_RT_TYPES 1
+#endif /* _PROJECT_DIOPERATOR_INTERFACE_RT_H_ */
+
+#define DIOPI_B200_WEAK __attribute__((weak))
+
+/* ------------------------------------------------------------------------- */
+/* Run-time accessors the library IMPORTS (the consumer defines them).        */
+/* Strong ones (diopirt.h:122-126,129,145,147) must exist; weak ones           */
+/* (diopirt.h:127,130,140,149) are used only when the loader resolved them.    */
+/* ------------------------------------------------------------------------- */
+extern diopiError_t diopiGetTensorData(diopiTensorHandle_t th, void** data);
+extern diopiError_t diopiGetTensorDataConst(diopiConstTensorHandle_t th, const void** data);
+extern diopiError_t diopiGetTensorShape(diopiConstTensorHandle_t th, diopiSize_t* size);
+extern diopiError_t diopiGetTensorStride(diopiConstTensorHandle_t th, diopiSize_t* stride);
+extern diopiError_t diopiGetTensorDtype(diopiConstTensorHandle_t th, diopiDtype_t* dtype);
+extern diopiError_t diopiGetTensorNumel(diopiConstTensorHandle_t th, int64_t* numel);
+extern diopiError_t diopiGetStream(diopiContextHandle_t ctx, diopiStreamHandle_t* stream);
+extern diopiError_t diopiRequireTensor(diopiContextHandle_t ctx, diopiTensorHandle_t* tensor, const diopiSize_t* size, const diopiSize_t* stride,
+                                       const diopiDtype_t dtype, const diopiDevice_t device);
+extern DIOPI_B200_WEAK diopiError_t diopiGetTensorDevice(diopiConstTensorHandle_t th, diopiDevice_t* device);
+extern DIOPI_B200_WEAK diopiError_t diopiGetTensorElemSize(diopiConstTensorHandle_t th, int64_t* itemsize);
+extern DIOPI_B200_WEAK diopiError_t diopiGetCurrentDeviceIndex(diopiDeviceIndex_t* pDevIndex);
+extern DIOPI_B200_WEAK diopiError_t diopiRequireBuffer(diopiContextHandle_t ctx, diopiTensorHandle_t* tensor, int64_t num_bytes, diopiDevice_t device);
+extern DIOPI_B200_WEAK diopiError_t diopiRecordStart(const char* record_name, void** record);
+extern DIOPI_B200_WEAK diopiError_t diopiRecordEnd(void** record);
+
+/* ------------------------------------------------------------------------- */
+/* Symbols the library EXPORTS.                                               */
+/* ------------------------------------------------------------------------- */
+
+/* Backend identification and the text of the most recent failure on any thread.
+ * Replace proto/include/diopi/functions.h:19-21. The vendor name contains the
+ * substring "Device", which the reference's device-info test looks for. */
+const char* diopiGetVendorName();
+const char* diopiGetImplVersion();
+const char* diopiGetLastErrorString();
+
+/* out[dest_loc[t], :, :] = k[t, :, :] — writes new tokens' K (or V) rows into the
+ * paged pool. k [T,H,D]; dest_loc [T] int32/int64; out [slots,H,D], same dtype as k.
+ * Bit-exact byte copy. Replaces proto/include/diopi/functions_ext.h:563. */
+diopiError_t diopiDestIndexCopyKV(diopiContextHandle_t ctx, diopiTensorHandle_t out, diopiConstTensorHandle_t k, diopiConstTensorHandle_t dest_loc);
+
+/* Decode logits: for request i and j in [0, L_i):
+ *   slot = b_loc[i, max_input_len - L_i + j]
+ *   token_attention_out[h, b_start_loc[i] + j] = dot(q[i,h,:], k[slot,h,:]) / sqrt(D)
+ * q [B,H,D]; k [slots,H,D]; b_loc [B,N>=max_input_len]; b_start_loc, b_seq_len [B];
+ * token_attention_out [H, sum(L)]. Replaces functions_ext.h:579-581. */
+diopiError_t diopiTokenAttentionInference(diopiContextHandle_t ctx, diopiTensorHandle_t token_attention_out, diopiConstTensorHandle_t q,
+                                          diopiConstTensorHandle_t k, diopiConstTensorHandle_t b_loc, diopiConstTensorHandle_t b_start_loc,
+                                          diopiConstTensorHandle_t b_seq_len, int max_input_len);
+
+/* Decode output: P = softmax(logics[:, start_i : start_i + L_i]) per head,
+ * out[i,h,:] = sum_j P[h,j] * v[slot(i,j),h,:]. A request of length 0 gets zeros.
+ * other_kv_index is accepted and ignored, as in the reference.
+ * Replaces functions_ext.h:597-599. */
+diopiError_t diopiTokenSoftmaxReduceVInference(diopiContextHandle_t ctx, diopiTensorHandle_t out, diopiConstTensorHandle_t logics,
+                                               diopiConstTensorHandle_t v, diopiConstTensorHandle_t b_loc, diopiConstTensorHandle_t b_start_loc,
+                                               diopiConstTensorHandle_t b_seq_len, int max_input_len, int other_kv_index);
+
+/* Causal prefill over a packed ragged batch: for request i on rows
+ * [b_start_loc[i], b_start_loc[i] + b_seq_len[i]) of q/k/v/out [sum(L),H,D]:
+ * out = softmax(q k^T / sqrt(D) + causal mask) v, per head.
+ * Replaces functions_ext.h:634-636. */
+diopiError_t diopiContextAttentionInference(diopiContextHandle_t ctx, diopiTensorHandle_t context_attention_out, diopiConstTensorHandle_t q,
+                                            diopiConstTensorHandle_t k, diopiConstTensorHandle_t v, diopiConstTensorHandle_t b_start_loc,
+                                            diopiConstTensorHandle_t b_seq_len, int max_input_len);
+
+/* In-place sampling penalty: for request i and entries e in
+ * [p_cumsum_seq_len[i], p_cumsum_seq_len[i+1]):
+ *   logits[i, p_token_ids[e]] -= p_token_counts[e] * frequency_penalty[i] + presence_penalty[i]
+ * evaluated as three separately rounded operations in the dtype of logits.
+ * Replaces functions_ext.h:527-529. */
+diopiError_t diopiApplyPenalty(diopiContextHandle_t ctx, diopiTensorHandle_t logits, diopiConstTensorHandle_t presence_penalty,
+                               diopiConstTensorHandle_t frequency_penalty, diopiConstTensorHandle_t p_token_ids, diopiConstTensorHandle_t p_token_counts,
+                               diopiConstTensorHandle_t p_cumsum_seq_len, int p_max_len_in_batch);
+
+/* Rotary embedding on the two halves of the last dimension; cos/sin broadcast
+ * against x's leading dimensions. interleaved=true returns diopiNoImplement, as the
+ * reference's NVIDIA backend does. Replaces functions_ext.h:31-32. */
+diopiError_t diopiRotaryEmbedding(diopiContextHandle_t ctx, diopiTensorHandle_t out, diopiConstTensorHandle_t x, diopiConstTensorHandle_t cos,
+                                  diopiConstTensorHandle_t sin, const bool conj, const bool interleaved);
+
+/* RMS normalisation over the trailing normalized_shape dims:
+ * inv_rms = rsqrt(mean(x^2) + eps) (fp32; fp64 for fp64 input),
+ * out = weight * (x * inv_rms) (+ bias), one rounding at the end.
+ * Replaces functions_ext.h:45-46. */
+diopiError_t diopiRMSNorm(diopiContextHandle_t ctx, diopiTensorHandle_t out, diopiTensorHandle_t inv_rms, diopiConstTensorHandle_t input,
+                          diopiSize_t normalized_shape, diopiConstTensorHandle_t weight, diopiConstTensorHandle_t bias, double eps);
+
+/* Extension (not in the DIOPI headers): the fused decode step. Equivalent to
+ * diopiTokenAttentionInference followed by diopiTokenSoftmaxReduceVInference on
+ * the same index tensors, but the logits never reach memory: one pass over the
+ * gathered K and V rows with an online softmax, fp32 accumulation.
+ * It is the composition of functions_ext.h:579-581 and :597-599; out [B,H,D]. */
+diopiError_t diopiTokenDecodeAttentionInference(diopiContextHandle_t ctx, diopiTensorHandle_t out, diopiConstTensorHandle_t q, diopiConstTensorHandle_t k,
+                                                diopiConstTensorHandle_t v, diopiConstTensorHandle_t b_loc, diopiConstTensorHandle_t b_start_loc,
+                                                diopiConstTensorHandle_t b_seq_len, int max_input_len);
+
+#if defined(__cplusplus)
+}
+#endif
+
+#endif /* DIOPI_B200_H_ */

@@ -1,0 +1,154 @@
+"""Generates tests/golden/*.npz from the reference's own golden functions.
+
+Run in a container where the reference tree is mounted:
+    python tests/golden/make_fixtures.py [/path/to/reference]
+It imports diopi_test/python/conformance/customized_test.py unmodified and evaluates
+CustomizedTest.<fn> on CPU for (a) the literal known-answer cases of
+diopi_test/python/configs/diopi_configs.py (index tensors, shapes and values typed in from
+lines 9053-9078, 9137-9337, 9339-9381, 9517-9610; some head counts and leading extents are cut down so
+that the files stay small) with seeded random float data where the config draws random data, and (b) small seeded cases of the benchmark's shapes.
+context_attention calls ``.cuda()`` on its mask (customized_test.py:16); there is no GPU here, so
+``torch.Tensor.cuda`` is patched to the identity for the duration of this script — the function
+body itself runs unchanged, on CPU.
+bfloat16 tensors are stored as their uint16 bit patterns (numpy has no bfloat16).
+"""
+import sys
+from pathlib import Path
+
+import numpy as np
+import torch
+
+REF = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+sys.path.insert(0, str(REF / "diopi_test" / "python" / "conformance"))
+torch.Tensor.cuda = lambda self, *a, **k: self  # see the module docstring
+from customized_test import CustomizedTest as G  # noqa: E402
+
+OUT = Path(__file__).resolve().parent
+gen = torch.Generator().manual_seed(20240607)
+
+
+def randn(*shape, dtype=torch.float32, scale=1.0):
+    return (torch.randn(*shape, generator=gen) * scale).to(dtype)
+
+
+def to_np(t):
+    if isinstance(t, torch.Tensor):
+        if t.dtype == torch.bfloat16:
+            return t.view(torch.int16).numpy().view(np.uint16)
+        return t.numpy()
+    return np.asarray(t)
+
+
+def save(name, **arrays):
+    np.savez_compressed(OUT / f"{name}.npz", **{k: to_np(v) for k, v in arrays.items() if v is not None})
+    print("wrote", name, {k: tuple(np.shape(to_np(v))) for k, v in arrays.items() if v is not None})
+
+
+DT = {"f32": torch.float32, "f16": torch.float16}
+
+# ---- apply_penalty: literal values of diopi_configs.py:9265-9312 ------------------------------
+for tag, dt in DT.items():
+    logits = torch.tensor([[0.1, 0.5, 0.4, 0.3, 0.5], [0.2, 0.4, 0.0, 0.0, 0.0], [0.3, 0.4, 0.5, 0.3, 0.0]], dtype=dt)
+    pres = torch.tensor([0.1, 0.8, 1.0], dtype=dt)
+    freq = torch.tensor([0.3, 0.5, 0.4], dtype=dt)
+    ids = torch.tensor([0, 1, 2, 3, 4, 0, 1, 0, 1, 2, 3], dtype=torch.int32)
+    cnt = torch.tensor([3, 3, 2, 2, 1, 3, 3, 3, 3, 2, 2], dtype=torch.int32)
+    cum = torch.tensor([0, 5, 7, 11], dtype=torch.int32)
+    out = G.apply_penalty(logits.clone(), pres, freq, ids, cnt, cum, 5)
+    save(f"apply_penalty_config_{tag}", logits=logits, presence=pres, frequency=freq, ids=ids, counts=cnt, cum=cum, out=out)
+
+# ---- apply_penalty: seeded, ids without repetition inside a request ----------------------------
+for tag, dt in DT.items():
+    B, V = 6, 997
+    logits = randn(B, V, dtype=dt, scale=2.0)
+    pres = torch.rand(B, generator=gen).to(dt)
+    freq = torch.rand(B, generator=gen).to(dt)
+    lens = torch.randint(0, 40, (B,), generator=gen)
+    lens[2] = 0
+    ids = torch.cat([torch.randperm(V, generator=gen)[: int(n)] for n in lens]).to(torch.int32)
+    cnt = torch.randint(1, 9, (int(lens.sum()),), generator=gen).to(torch.int32)
+    cum = torch.cat([torch.zeros(1, dtype=torch.int64), lens.cumsum(0)]).to(torch.int32)
+    out = G.apply_penalty(logits.clone(), pres, freq, ids, cnt, cum, int(lens.max()))
+    save(f"apply_penalty_seeded_{tag}", logits=logits, presence=pres, frequency=freq, ids=ids, counts=cnt, cum=cum, out=out)
+
+# ---- destindex_copy_kv: diopi_configs.py:9314-9337 (heads cut from 32 to 2 to keep the file small)
+for tag, dt in DT.items():
+    for case, (T, dest) in enumerate([(5, (0, 1, 2, 3, 4)), (4, (14, 15, 16, 17))]):
+        k = randn(T, 2, 128, dtype=dt)
+        base = randn(120, 2, 128, dtype=dt).round()  # integers compress well; the copy is bit-exact anyway
+        d = torch.tensor(dest, dtype=torch.int32)
+        out = G.destindex_copy_kv(k, d, base.clone())
+        save(f"destindex_copy_kv_config{case}_{tag}", k=k, dest_loc=d, out_before=base, out=out)
+
+# ---- token_attention / token_softmax_reducev: index tensors of diopi_configs.py:9517-9610 ------
+b_loc = torch.tensor([[0, 0, 1, 2, 10] + [0] * 10, [3, 4, 5, 6, 11] + [0] * 10, [0, 7, 8, 9, 12] + [0] * 10], dtype=torch.int32)
+b_start = torch.tensor([0, 4, 9], dtype=torch.int32)
+b_len = torch.tensor([4, 5, 4], dtype=torch.int32)
+for tag, dt in DT.items():
+    H, D = 8, 128  # heads cut from 32 to 8 to keep the file small
+    q = randn(3, H, D, dtype=dt)
+    k = randn(100, H, D, dtype=dt)
+    v = randn(100, H, D, dtype=dt)
+    att = G.token_attention(q, k, torch.zeros(H, 13, dtype=dt), b_loc, b_start, b_len, 5)
+    logics = randn(H, 13, dtype=dt)
+    red = G.token_softmax_reducev(logics, v, torch.zeros(3, H, D, dtype=dt), b_loc, b_start, b_len, 5, 10)
+    fused = G.token_softmax_reducev(att, v, torch.zeros(3, H, D, dtype=dt), b_loc, b_start, b_len, 5, 10)
+    # keep only the 13 pool rows that are referenced, at their slots (the rest of the pool is never read)
+    used = sorted(set(b_loc[:, :5].flatten().tolist()))
+    save(f"token_attention_config_{tag}", q=q, k_rows=k[used], v_rows=v[used], used=np.array(used), pool=np.array(100), b_loc=b_loc,
+         b_start_loc=b_start, b_seq_len=b_len, max_input_len=np.array(5), att=att, logics=logics, reducev=red, fused=fused)
+
+# ---- decode, seeded, shape of the CPU-runnable benchmark config (B4 H8 D64, lens in [16,128]) --
+for tag, dt in DT.items():
+    B, H, D = 4, 8, 64
+    lens = torch.randint(8, 49, (B,), generator=gen)  # the benchmark config draws from [16,128]
+    lens[1] = 0 if tag == "f32" else lens[1]  # one empty request in the fp32 case
+    pool = int(lens.sum()) + 16  # the benchmark config adds 64 spare slots; 16 keep the file small
+    k = randn(pool, H, D, dtype=dt)
+    v = randn(pool, H, D, dtype=dt)
+    q = randn(B, H, D, dtype=dt)
+    perm = torch.randperm(pool, generator=gen)
+    mx = int(lens.max())
+    bl = torch.zeros(B, mx + 3, dtype=torch.int32)
+    st = torch.zeros(B, dtype=torch.int32)
+    acc = 0
+    for i in range(B):
+        L = int(lens[i])
+        bl[i, mx - L:mx] = perm[acc:acc + L].to(torch.int32)
+        st[i] = acc
+        acc += L
+    bn = lens.to(torch.int32)
+    att = G.token_attention(q, k, torch.zeros(H, acc, dtype=dt), bl, st, bn, mx)
+    out = G.token_softmax_reducev(att, v, torch.zeros(B, H, D, dtype=dt), bl, st, bn, mx, 0)
+    save(f"decode_seeded_{tag}", q=q, k=k, v=v, b_loc=bl, b_start_loc=st, b_seq_len=bn, max_input_len=np.array(mx), att=att, out=out)
+
+# ---- context_attention: ragged layouts of diopi_configs.py:9339-9381 ---------------------------
+# heads cut from 32/32/32/64 to 4/4/4/1 to keep the files small
+layouts = [((4, 4, 64), (0,), (4,), 4), ((17, 4, 128), (0, 5), (5, 12), 12), ((64, 4, 128), (0, 16, 48), (16, 32, 16), 32),
+           ((128, 1, 256), (0, 32, 64), (32, 32, 64), 64)]  # last layout halved as well
+for tag, dt in DT.items():
+    for case, (shape, starts, lens, mx) in enumerate(layouts):
+        q, k, v = (randn(*shape, dtype=dt) for _ in range(3))
+        st = torch.tensor(starts, dtype=torch.int32)
+        bn = torch.tensor(lens, dtype=torch.int32)
+        out = G.context_attention(q, k, v, torch.zeros(shape, dtype=dt), st, bn, mx)
+        save(f"context_attention_config{case}_{tag}", q=q, k=k, v=v, b_start_loc=st, b_seq_len=bn, max_input_len=np.array(mx), out=out)
+
+# ---- rotary_emb: shape/broadcast/conj combinations of diopi_configs.py:9053-9078 ---------------
+rot = [((12,), (6,), True), ((64,), (32,), False), ((2, 128), (2, 64), False), ((3, 8, 256), (3, 1, 128), False), ((1, 64), (1, 32), True),
+       ((3, 5, 12), (3, 5, 6), True), ((1, 25, 4, 64), (25, 1, 32), False), ((2, 16, 4, 32), (16, 1, 16), False), ((3, 20, 2, 64), (20, 1, 32), True)]
+for tag, dt in {**DT, "f64": torch.float64}.items():
+    for case, (xs, cs, conj) in enumerate(rot):
+        x, c, s = randn(*xs, dtype=dt), randn(*cs, dtype=dt), randn(*cs, dtype=dt)
+        out = G.rotary_emb(x, c, s, conj, False)
+        save(f"rotary_emb_config{case}_{tag}", x=x, cos=c, sin=s, conj=np.array(conj), out=out)
+
+# ---- rms_norm: diopi_configs.py:9137-9263 -------------------------------------------------------
+rms = [((16,), (16,), 1e-4, False), ((5, 5), (5,), 1e-6, False), ((7, 25, 32), (32,), 1e-6, True), ((3, 64, 64), (64, 64), 1e-6, False),
+       ((1, 8, 8, 64), (8, 64), 1e-6, True), ((3, 2, 4, 7, 8), (7, 8), 1e-2, True), ((5, 5), (5, 5), 1e-4, True), ((3, 4096), (4096,), 1e-6, False)]
+for tag, dt in {**DT, "f64": torch.float64, "bf16": torch.bfloat16}.items():
+    for case, (xs, ns, eps, with_bias) in enumerate(rms):
+        x, w = randn(*xs, dtype=dt), (1 + 0.1 * torch.randn(*ns, generator=gen)).to(dt)
+        b = randn(*ns, dtype=dt) if with_bias else None
+        out = G.rms_norm(x, ns, w, b, eps)
+        save(f"rms_norm_config{case}_{tag}", x=x, weight=w, bias=b, eps=np.array(eps), normalized_shape=np.array(ns), out=out)

@@ -1,0 +1,99 @@
+"""The drop-in boundary without a GPU: the library loads, exports exactly the symbols the header
+declares, imports only run-time accessors, and its header is ABI-compatible with the reference's."""
+import re
+import subprocess
+from pathlib import Path
+
+import pytest
+
+ROOT = Path(__file__).resolve().parent.parent
+HEADER = ROOT / "include" / "diopi_b200.h"
+REFERENCE = Path("/root/reference/proto/include")
+
+
+def declared_exports():
+    text = HEADER.read_text().split("Symbols the library EXPORTS")[1]
+    return sorted(set(re.findall(r"\b(diopi[A-Z]\w+)\s*\(", text)))
+
+
+def declared_imports():
+    text = HEADER.read_text().split("Symbols the library EXPORTS")[0]
+    return sorted(set(re.findall(r"\b(diopi[A-Z]\w+)\s*\(", text)))
+
+
+def nm(lib, flag):
+    out = subprocess.run(["nm", "-D", flag, str(lib)], capture_output=True, text=True, check=True).stdout
+    return [line.split() for line in out.splitlines() if line.strip()]
+
+
+def test_header_lists_the_hot_path():
+    want = {"diopiDestIndexCopyKV", "diopiTokenAttentionInference", "diopiTokenSoftmaxReduceVInference", "diopiRMSNorm", "diopiRotaryEmbedding",
+            "diopiApplyPenalty", "diopiContextAttentionInference", "diopiGetVendorName", "diopiGetImplVersion", "diopiGetLastErrorString"}
+    assert want <= set(declared_exports())
+
+
+def test_library_exports_exactly_the_declared_symbols(built_libs):
+    lib = ROOT / "diopi_b200" / "lib" / "libdiopi_impl.so"
+    defined = sorted(f[-1] for f in nm(lib, "--defined-only"))
+    assert defined == declared_exports(), "exported symbols and include/diopi_b200.h disagree"
+    # every export is a plain C name, reachable by dlsym (the reference's dyn-load shim binds by name)
+    for name in declared_exports():
+        assert getattr(built_libs.impl, name) is not None
+
+
+def test_library_imports_only_runtime_accessors(built_libs):
+    lib = ROOT / "diopi_b200" / "lib" / "libdiopi_impl.so"
+    undefined = [f for f in nm(lib, "--undefined-only") if f[-1].startswith("diopi")]
+    names = {f[-1] for f in undefined}
+    assert names <= set(declared_imports()), names - set(declared_imports())
+    weak = {f[-1] for f in undefined if f[0] in ("w", "v")}
+    # optional accessors must stay weak so that a consumer without them can still load the library
+    assert {"diopiRequireBuffer", "diopiGetTensorDevice", "diopiRecordStart", "diopiRecordEnd"} <= weak
+    strong = names - weak
+    assert {"diopiGetTensorData", "diopiGetStream", "diopiRequireTensor", "diopiGetTensorShape"} <= strong
+    # no torch, no cudart shared object: the CUDA run time is linked statically
+    needed = subprocess.run(["readelf", "-d", str(lib)], capture_output=True, text=True, check=True).stdout
+    assert "torch" not in needed and "libcudart" not in needed
+
+
+def test_info_exports(built_libs):
+    from diopi_b200 import functions as F
+    assert "Device" in F.vendor_name()          # diopi_test/python/tests/diopi/test_device_info.py:13
+    assert "sm_100a" in F.impl_version()
+    assert isinstance(F.last_error(), str)
+
+
+def test_enum_values_match_the_interface():
+    text = HEADER.read_text()
+    for name, value in [("diopiSuccess", 0), ("diopiErrorOccurred", 1), ("diopiNoImplement", 13), ("diopiDtypeNotSupported", 1000),
+                        ("diopi_dtype_int32", 4), ("diopi_dtype_int64", 6), ("diopi_dtype_float16", 8), ("diopi_dtype_float32", 9),
+                        ("diopi_dtype_float64", 10), ("diopi_dtype_bfloat16", 12), ("diopi_host", 0), ("diopi_device", 1)]:
+        assert re.search(rf"\b{name}\s*=\s*{value}\b", text), name
+
+
+@pytest.mark.skipif(not REFERENCE.exists(), reason="the reference interface headers are not mounted")
+def test_prototypes_compile_against_the_reference_headers(tmp_path):
+    """One translation unit includes the reference's diopirt.h/functions.h/functions_ext.h and then this
+    repository's header: any prototype that differs is a conflicting redeclaration and fails to compile.
+    A second unit includes only our header and checks type sizes and enum values."""
+    tu = tmp_path / "both.cpp"
+    tu.write_text(
+        '#include <diopi/diopirt.h>\n#include <diopi/functions.h>\n#include <diopi/functions_ext.h>\n'
+        '#include "diopi_b200.h"\n#ifdef DIOPI_B200_OWN_RT_TYPES\n#error "own types must be skipped when diopirt.h came first"\n#endif\n'
+        'int main() { return 0; }\n')
+    r = subprocess.run(["g++", "-std=c++17", "-fsyntax-only", f"-I{REFERENCE}", f"-I{ROOT / 'include'}", str(tu)], capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+    own = tmp_path / "own.cpp"
+    own.write_text(
+        '#include "diopi_b200.h"\n#include <cstddef>\n'
+        'static_assert(sizeof(diopiSize_t) == 16 && offsetof(diopiSize_t, len) == 8, "diopiSize_t layout");\n'
+        'static_assert(sizeof(diopiDeviceIndex_t) == 1, "device index");\n'
+        'static_assert(diopi_dtype_bfloat16 == 12 && diopi_dtype_float16 == 8 && diopiNoImplement == 13, "enum values");\n'
+        'int main() { return 0; }\n')
+    r = subprocess.run(["g++", "-std=c++17", "-fsyntax-only", f"-I{ROOT / 'include'}", str(own)], capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+    # and as C
+    cfile = tmp_path / "own.c"
+    cfile.write_text('#include "diopi_b200.h"\nint main(void) { return (int)diopiSuccess; }\n')
+    r = subprocess.run(["gcc", "-std=c11", "-fsyntax-only", f"-I{ROOT / 'include'}", str(cfile)], capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr

@@ -1,0 +1,504 @@
+"""Parity of the CUDA path, called through the C ABI of libdiopi_impl.so, against the reference's
+outputs (tests/golden) and the CPU oracle on the same seeded inputs.
+
+Tolerances (stated by the task): bit-exact for DestIndexCopyKV and ApplyPenalty; rtol=atol=1e-3 for
+fp32; rtol=atol=1e-2 for fp16/bf16 against the oracle evaluated with fp32 accumulation."""
+import threading
+
+import pytest
+import torch
+
+from conftest import fixture_names, load_fixture
+from oracle import golden
+
+pytestmark = pytest.mark.gpu
+
+TOL32 = dict(rtol=1e-3, atol=1e-3)
+TOL16 = dict(rtol=1e-2, atol=1e-2)
+
+
+def tol(dtype):
+    return TOL32 if dtype in (torch.float32, torch.float64) else TOL16
+
+
+def close(got, want, dtype=None):
+    torch.testing.assert_close(got.detach().cpu().double(), want.detach().cpu().double(), **tol(dtype or want.dtype))
+
+
+@pytest.fixture(scope="module")
+def F(built_libs):
+    assert torch.cuda.is_available(), "these tests need a CUDA device"
+    from diopi_b200 import functions
+    return functions
+
+
+def cuda(*ts):
+    return [t.cuda() if isinstance(t, torch.Tensor) else t for t in ts]
+
+
+def full_pool(f, key):
+    rows = f[key]
+    pool = torch.zeros((f["pool"],) + tuple(rows.shape[1:]), dtype=rows.dtype)
+    pool[f["used"].long()] = rows
+    return pool
+
+
+# ------------------------------------------------------------------ DestIndexCopyKV
+@pytest.mark.parametrize("name", fixture_names("destindex_copy_kv"))
+def test_destindex_copy_kv_fixture(F, name):
+    f = load_fixture(name)
+    k, d, out = cuda(f["k"], f["dest_loc"], f["out_before"].clone())
+    k0, d0 = k.clone(), d.clone()
+    F.destindex_copy_kv(k, d, out)
+    assert torch.equal(out.cpu(), f["out"])
+    assert torch.equal(k, k0) and torch.equal(d, d0)  # inputs untouched
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32, torch.float64])
+@pytest.mark.parametrize("idx_dtype", [torch.int32, torch.int64])
+def test_destindex_copy_kv_layouts(F, dtype, idx_dtype):
+    g = torch.Generator().manual_seed(5)
+    T, H, D, slots = 37, 5, 24, 211   # odd sizes: rows of 240/480/960 bytes
+    k = torch.randn(T, H, D, generator=g).to(dtype)
+    base = torch.randn(slots, H, D, generator=g).to(dtype)
+    dest = torch.randperm(slots, generator=g)[:T].to(idx_dtype)
+    dest[3] = dest[3] - slots  # a negative index counts from the end, as index_put_ does
+    want = golden.destindex_copy_kv(k, dest, base.clone())
+    out = base.clone().cuda()
+    F.destindex_copy_kv(k.cuda(), dest.cuda(), out)
+    assert torch.equal(out.cpu(), want)
+    # strided views: a head shard of a wider pool and every other source row (element path)
+    wide = torch.randn(slots, 2 * H, D, generator=g).to(dtype).cuda()
+    view = wide[:, H:, :]
+    src = torch.randn(2 * T, H, D, generator=g).to(dtype).cuda()[::2]
+    want2 = golden.destindex_copy_kv(src.cpu(), dest, view.cpu().clone())
+    F.destindex_copy_kv(src, dest.cuda(), view)
+    assert torch.equal(view.cpu(), want2)
+    # 1-byte rows / empty input
+    F.destindex_copy_kv(k.cuda()[:0], dest.cuda()[:0], out)
+    assert torch.equal(out.cpu(), want)
+
+
+# ------------------------------------------------------------------ decode: fixtures
+@pytest.mark.parametrize("name", fixture_names("token_attention_config"))
+def test_token_attention_config(F, name):
+    f = load_fixture(name)
+    k, v = full_pool(f, "k_rows"), full_pool(f, "v_rows")
+    q, bl, bs, bn = f["q"], f["b_loc"], f["b_start_loc"], f["b_seq_len"]
+    mx = f["max_input_len"]
+    att = torch.zeros_like(f["att"]).cuda()
+    F.token_attention(q.cuda(), k.cuda(), att, bl.cuda(), bs.cuda(), bn.cuda(), mx)
+    close(att, f["att"])
+    red = torch.zeros_like(f["reducev"]).cuda()
+    F.token_softmax_reducev(f["logics"].cuda(), v.cuda(), red, bl.cuda(), bs.cuda(), bn.cuda(), mx, 10)
+    close(red, f["reducev"])
+    fused = torch.zeros_like(f["fused"]).cuda()
+    F.token_decode_attention(q.cuda(), k.cuda(), v.cuda(), fused, bl.cuda(), bs.cuda(), bn.cuda(), mx)
+    close(fused, f["fused"])
+
+
+@pytest.mark.parametrize("name", fixture_names("decode_seeded"))
+def test_decode_seeded_fixture(F, name):
+    f = load_fixture(name)
+    q, k, v, bl, bs, bn = cuda(f["q"], f["k"], f["v"], f["b_loc"], f["b_start_loc"], f["b_seq_len"])
+    mx = f["max_input_len"]
+    att = torch.zeros_like(f["att"]).cuda()
+    F.token_attention(q, k, att, bl, bs, bn, mx)
+    close(att, f["att"])
+    out = torch.full_like(f["out"], 7.0).cuda()
+    F.token_softmax_reducev(f["att"].cuda(), v, out, bl, bs, bn, mx, 0)
+    close(out, f["out"])
+    fused = torch.full_like(f["out"], 7.0).cuda()
+    F.token_decode_attention(q, k, v, fused, bl, bs, bn, mx)
+    close(fused, f["out"])
+    for i in (f["b_seq_len"] == 0).nonzero().flatten().tolist():
+        assert torch.count_nonzero(fused[i]) == 0 and torch.count_nonzero(out[i]) == 0
+
+
+# ------------------------------------------------------------------ decode: the CPU-runnable config, whole step
+def test_decode_cfg1_step(F):
+    from diopi_b200 import workloads
+    w = workloads.decode("cfg1", device="cuda")
+    # oracle on CPU copies of the same inputs
+    kc, vc = w.k_pool.cpu().clone(), w.v_pool.cpu().clone()
+    golden.destindex_copy_kv(w.k_new.cpu(), w.dest_loc.cpu(), kc)
+    golden.destindex_copy_kv(w.v_new.cpu(), w.dest_loc.cpu(), vc)
+    H = w.q.shape[1]
+    att_ref = golden.token_attention(w.q.cpu(), kc, torch.zeros(H, w.sum_len), w.b_loc.cpu(), w.b_start_loc.cpu(), w.b_seq_len.cpu(), w.max_input_len)
+    out_ref = golden.token_softmax_reducev(att_ref, vc, torch.zeros_like(w.q.cpu()), w.b_loc.cpu(), w.b_start_loc.cpu(), w.b_seq_len.cpu(), w.max_input_len)
+    # device path
+    F.destindex_copy_kv(w.k_new, w.dest_loc, w.k_pool)
+    F.destindex_copy_kv(w.v_new, w.dest_loc, w.v_pool)
+    assert torch.equal(w.k_pool.cpu(), kc) and torch.equal(w.v_pool.cpu(), vc)
+    att = torch.zeros(H, w.sum_len, device="cuda")
+    F.token_attention(w.q, w.k_pool, att, w.b_loc, w.b_start_loc, w.b_seq_len, w.max_input_len)
+    close(att, att_ref)
+    out = torch.empty_like(w.q)
+    F.token_softmax_reducev(att, w.v_pool, out, w.b_loc, w.b_start_loc, w.b_seq_len, w.max_input_len, int(w.b_loc[0, -1]))
+    close(out, out_ref)
+    fused = torch.empty_like(w.q)
+    F.token_decode_attention(w.q, w.k_pool, w.v_pool, fused, w.b_loc, w.b_start_loc, w.b_seq_len, w.max_input_len)
+    close(fused, out_ref)
+
+
+def make_decode_case(B, H, D, dtype, lens, idx_dtype=torch.int32, extra_cols=0, seed=0, pool_extra=17):
+    g = torch.Generator().manual_seed(seed)
+    lens = torch.tensor(lens)
+    total = int(lens.sum())
+    slots = total + pool_extra
+    k = (torch.randn(slots, H, D, generator=g) * 0.7).to(dtype)
+    v = torch.randn(slots, H, D, generator=g).to(dtype)
+    q = torch.randn(B, H, D, generator=g).to(dtype)
+    perm = torch.randperm(slots, generator=g)
+    mx = int(lens.max()) if B else 0
+    bl = torch.zeros(B, mx + extra_cols, dtype=idx_dtype)
+    st = torch.zeros(B, dtype=idx_dtype)
+    acc = 0
+    for i in range(B):
+        L = int(lens[i])
+        bl[i, mx - L:mx] = perm[acc:acc + L].to(idx_dtype)
+        st[i] = acc
+        acc += L
+    return dict(q=q, k=k, v=v, b_loc=bl, b_start_loc=st, b_seq_len=lens.to(idx_dtype), max_input_len=mx, total=total)
+
+
+def check_decode_case(F, c, k_dev=None, v_dev=None):
+    dtype = c["q"].dtype
+    H = c["q"].shape[1]
+    args = (c["b_loc"], c["b_start_loc"], c["b_seq_len"], c["max_input_len"])
+    att_ref = golden.token_attention(c["q"], c["k"], torch.zeros(H, c["total"]), *args, upcast=True)
+    out_ref = golden.token_softmax_reducev(att_ref, c["v"], torch.zeros(c["q"].shape), *args, upcast=True)
+    dargs = (c["b_loc"].cuda(), c["b_start_loc"].cuda(), c["b_seq_len"].cuda(), c["max_input_len"])
+    kd = c["k"].cuda() if k_dev is None else k_dev
+    vd = c["v"].cuda() if v_dev is None else v_dev
+    q = c["q"].cuda()
+    att = torch.zeros(H, c["total"], dtype=dtype, device="cuda")
+    F.token_attention(q, kd, att, *dargs)
+    close(att, att_ref, dtype)
+    out = torch.full(c["q"].shape, 3.0, dtype=dtype, device="cuda")
+    F.token_softmax_reducev(att_ref.to(dtype).cuda(), vd, out, *dargs, 0)
+    close(out, out_ref, dtype)
+    fused = torch.full(c["q"].shape, 3.0, dtype=dtype, device="cuda")
+    F.token_decode_attention(q, kd, vd, fused, *dargs)
+    close(fused, out_ref, dtype)
+    return fused
+
+
+DECODE_CASES = [
+    # B, H, D, dtype, lens
+    (1, 1, 64, torch.float16, [1]),
+    (3, 32, 128, torch.float16, [4, 5, 4]),
+    (5, 32, 128, torch.float16, [300, 0, 1, 1500, 77]),          # an empty request and a long one
+    (4, 32, 128, torch.bfloat16, [129, 513, 2, 64]),
+    (7, 8, 64, torch.float32, [16, 128, 33, 1, 0, 90, 128]),     # the CPU-runnable config's shape
+    (3, 40, 128, torch.float16, [200, 31, 333]),                 # 40 heads: a full head group of 32 and a part group of 8
+    (3, 12, 64, torch.float16, [50, 260, 9]),                    # 8 lanes per head, 5 token groups
+    (2, 6, 256, torch.float16, [120, 45]),                       # 32 lanes per head
+    (2, 4, 128, torch.float32, [70, 300]),                       # fp32, 32 lanes per head
+    (2, 3, 32, torch.float32, [65, 8]),                          # fp32, 8 lanes per head
+    (2, 5, 80, torch.float16, [40, 100]),                        # D*e/16 = 10: plain path
+    (2, 2, 40, torch.float32, [33, 7]),                          # plain path, fp32
+    (2, 64, 128, torch.float16, [700, 256]),                     # 64 heads: two head groups
+]
+
+
+@pytest.mark.parametrize("B,H,D,dtype,lens", DECODE_CASES)
+def test_decode_shapes(F, B, H, D, dtype, lens):
+    check_decode_case(F, make_decode_case(B, H, D, dtype, lens, seed=B * 131 + H))
+
+
+def test_decode_all_small_lengths(F):
+    """Every length from 0 to 33 in one batch (stage and group tails), both index dtypes, b_loc wider than max_input_len."""
+    lens = list(range(0, 34))
+    for idx_dtype in (torch.int32, torch.int64):
+        check_decode_case(F, make_decode_case(len(lens), 8, 128, torch.float16, lens, idx_dtype=idx_dtype, extra_cols=10, seed=3))
+
+
+def test_decode_many_requests(F):
+    g = torch.Generator().manual_seed(11)
+    lens = torch.randint(0, 40, (300,), generator=g).tolist()
+    check_decode_case(F, make_decode_case(300, 4, 64, torch.float16, lens, seed=4))
+
+
+def test_decode_strided_pool(F):
+    """Head shard taken as a view of a wider pool (rows not dense over heads -> plain path), and a pool
+    whose slot stride is padded (rows dense, stride larger -> split path)."""
+    c = make_decode_case(3, 8, 128, torch.float16, [100, 257, 30], seed=9)
+    slots = c["k"].shape[0]
+    wide_k = torch.zeros(slots, 16, 128, dtype=torch.float16, device="cuda")
+    wide_v = torch.zeros_like(wide_k)
+    wide_k[:, 4:12] = c["k"].cuda()
+    wide_v[:, 4:12] = c["v"].cuda()
+    check_decode_case(F, c, wide_k[:, 4:12], wide_v[:, 4:12])
+    pad_k = torch.zeros(slots, 8 * 128 + 64, dtype=torch.float16, device="cuda")
+    pad_v = torch.zeros_like(pad_k)
+    kk = pad_k[:, : 8 * 128].view(slots, 8, 128)   # stride(0) = 1088 elements
+    vv = pad_v[:, : 8 * 128].view(slots, 8, 128)
+    kk.copy_(c["k"].cuda())
+    vv.copy_(c["v"].cuda())
+    check_decode_case(F, c, kk, vv)
+
+
+def test_decode_inputs_not_mutated(F):
+    c = make_decode_case(4, 8, 128, torch.float16, [60, 0, 130, 9], seed=21)
+    dev = {k: (v.cuda() if isinstance(v, torch.Tensor) else v) for k, v in c.items()}
+    before = {k: v.clone() for k, v in dev.items() if isinstance(v, torch.Tensor)}
+    out = torch.empty_like(dev["q"])
+    F.token_decode_attention(dev["q"], dev["k"], dev["v"], out, dev["b_loc"], dev["b_start_loc"], dev["b_seq_len"], dev["max_input_len"])
+    torch.cuda.synchronize()
+    for k, v in before.items():
+        assert torch.equal(dev[k], v), k
+
+
+# ------------------------------------------------------------------ decode at full benchmark size
+@pytest.fixture(scope="module")
+def cfg2():
+    from diopi_b200 import workloads
+    return workloads.decode("cfg2", device="cuda")
+
+
+def compact_oracle(w, reqs, k_pool, v_pool):
+    """Oracle output of a few requests of a large workload: their rows are moved into a compact pool."""
+    mx = w.max_input_len
+    b_loc, lens = w.b_loc.cpu(), w.b_seq_len.cpu()
+    rows, new_loc = [], torch.zeros(len(reqs), mx, dtype=torch.int32)
+    acc = 0
+    for n, i in enumerate(reqs):
+        L = int(lens[i])
+        rows.append(b_loc[i, mx - L:].long())
+        new_loc[n, mx - L:] = torch.arange(acc, acc + L, dtype=torch.int32)
+        acc += L
+    rows = torch.cat(rows).cuda()
+    k, v = k_pool[rows].cpu(), v_pool[rows].cpu()
+    q = w.q[reqs].cpu()
+    ln = lens[reqs]
+    st = torch.cat([torch.zeros(1, dtype=torch.int32), ln.cumsum(0)[:-1].to(torch.int32)])
+    out = torch.zeros(q.shape)
+    return golden.token_decode_attention(q, k, v, out, new_loc, st, ln, mx, upcast=True)
+
+
+def test_decode_cfg2_full_size(F, cfg2):
+    w = cfg2
+    k0 = w.k_pool.clone()
+    # DestIndexCopyKV at full size: the touched rows equal the new rows bit for bit, every other row keeps its bits
+    F.destindex_copy_kv(w.k_new, w.dest_loc, w.k_pool)
+    F.destindex_copy_kv(w.v_new, w.dest_loc, w.v_pool)
+    assert torch.equal(w.k_pool[w.dest_loc.long()], w.k_new)
+    mask = torch.ones(w.k_pool.shape[0], dtype=torch.bool, device="cuda")
+    mask[w.dest_loc.long()] = False
+    assert torch.equal(w.k_pool[mask].view(torch.int16), k0[mask].view(torch.int16))
+    del k0, mask
+
+    fused = torch.empty_like(w.q)
+    F.token_decode_attention(w.q, w.k_pool, w.v_pool, fused, w.b_loc, w.b_start_loc, w.b_seq_len, w.max_input_len)
+    # (1) the two stand-alone ops chained through an fp16 logits tensor agree with the fused kernel
+    att = torch.zeros(w.q.shape[1], w.sum_len, dtype=w.q.dtype, device="cuda")
+    F.token_attention(w.q, w.k_pool, att, w.b_loc, w.b_start_loc, w.b_seq_len, w.max_input_len)
+    two = torch.empty_like(w.q)
+    F.token_softmax_reducev(att, w.v_pool, two, w.b_loc, w.b_start_loc, w.b_seq_len, w.max_input_len, 0)
+    close(two, fused)
+    # (2) a sample of requests against the oracle with fp32 accumulation
+    reqs = [0, 17, 63, int(w.b_seq_len.argmax()), int(w.b_seq_len.argmin())]
+    close(fused[reqs], compact_oracle(w, reqs, w.k_pool, w.v_pool), torch.float16)
+    # (3) the output is linear in V: doubling V doubles it (exact but for fp16 subnormals)
+    w.v_pool.mul_(2)
+    twice = torch.empty_like(w.q)
+    F.token_decode_attention(w.q, w.k_pool, w.v_pool, twice, w.b_loc, w.b_start_loc, w.b_seq_len, w.max_input_len)
+    w.v_pool.mul_(0.5)
+    assert float((twice.float() - 2 * fused.float()).abs().max()) <= 2.0 ** -23
+    # (4) paging invariance: moving every row to another slot and renaming the slots in b_loc changes nothing
+    slots = w.k_pool.shape[0]
+    perm = torch.randperm(slots, device="cuda")
+    inv = torch.empty_like(perm)
+    inv[perm] = torch.arange(slots, device="cuda")
+    k2, v2 = w.k_pool[perm], w.v_pool[perm]          # new slot s holds old row perm[s]
+    b2 = inv[w.b_loc.long()].to(torch.int32)         # old slot -> new slot
+    moved = torch.empty_like(w.q)
+    F.token_decode_attention(w.q, k2, v2, moved, b2, w.b_start_loc, w.b_seq_len, w.max_input_len)
+    assert torch.equal(moved, fused)
+
+
+# ------------------------------------------------------------------ status word, streams
+def test_out_of_range_slot_is_reported(F):
+    c = make_decode_case(2, 8, 128, torch.float16, [20, 40], seed=2)
+    bad = c["b_loc"].clone()
+    bad[1, -3] = c["k"].shape[0] + 5   # beyond the pool: the row is skipped, the next call reports it
+    out = torch.empty(c["q"].shape, dtype=torch.float16, device="cuda")
+    F.token_decode_attention(c["q"].cuda(), c["k"].cuda(), c["v"].cuda(), out, bad.cuda(), c["b_start_loc"].cuda(), c["b_seq_len"].cuda(), c["max_input_len"])
+    torch.cuda.synchronize()
+    from diopi_b200.runtime import DiopiError
+    with pytest.raises(DiopiError, match="outside the pool"):
+        F.token_decode_attention(c["q"].cuda(), c["k"].cuda(), c["v"].cuda(), out, c["b_loc"].cuda(), c["b_start_loc"].cuda(), c["b_seq_len"].cuda(), c["max_input_len"])
+    # the status is reported once; the library keeps working
+    check_decode_case(F, c)
+
+
+def test_two_threads_two_contexts(F):
+    """Ops are called from two host threads on two contexts/streams (the reference's stream test does
+    the same with matmul+sum: diopi_test/python/tests/diopi/test_stream.py:102-108)."""
+    from diopi_b200.runtime import Context
+    c = make_decode_case(6, 8, 128, torch.float16, [100, 200, 50, 300, 10, 64], seed=31)
+    dev = {k: (v.cuda() if isinstance(v, torch.Tensor) else v) for k, v in c.items()}
+    ref = torch.empty_like(dev["q"])
+    F.token_decode_attention(dev["q"], dev["k"], dev["v"], ref, dev["b_loc"], dev["b_start_loc"], dev["b_seq_len"], dev["max_input_len"])
+    torch.cuda.synchronize()
+    results, errors = {}, []
+
+    def worker(n):
+        try:
+            s = torch.cuda.Stream()
+            ctx = Context(s)
+            outs = []
+            for _ in range(20):
+                o = torch.empty_like(dev["q"])
+                F.token_decode_attention(dev["q"], dev["k"], dev["v"], o, dev["b_loc"], dev["b_start_loc"], dev["b_seq_len"], dev["max_input_len"], ctx=ctx)
+                ctx.release()
+                outs.append(o)
+            ctx.synchronize()
+            results[n] = outs
+        except Exception as e:  # noqa: BLE001
+            errors.append(e)
+
+    ts = [threading.Thread(target=worker, args=(n,)) for n in range(2)]
+    [t.start() for t in ts]
+    [t.join() for t in ts]
+    assert not errors, errors
+    for outs in results.values():
+        for o in outs:
+            assert torch.equal(o, ref)
+
+
+# ------------------------------------------------------------------ ApplyPenalty
+@pytest.mark.parametrize("name", fixture_names("apply_penalty"))
+def test_apply_penalty_fixture(F, name):
+    f = load_fixture(name)
+    lg = f["logits"].clone().cuda()
+    ins = cuda(f["presence"], f["frequency"], f["ids"], f["counts"], f["cum"])
+    keep = [t.clone() for t in ins]
+    F.apply_penalty(lg, *ins, 5)
+    assert torch.equal(lg.cpu(), f["out"])
+    for a, b in zip(ins, keep):
+        assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16])
+def test_apply_penalty_cfg5_bit_exact(F, dtype):
+    from diopi_b200 import workloads
+    p = workloads.penalty(device="cuda", dtype=dtype)
+    want = golden.apply_penalty(p["logits"].cpu().clone(), p["presence"].cpu(), p["frequency"].cpu(), p["ids"].cpu(), p["counts"].cpu(), p["cum"].cpu())
+    F.apply_penalty(p["logits"], p["presence"], p["frequency"], p["ids"], p["counts"], p["cum"], p["max_len"])
+    assert torch.equal(p["logits"].cpu(), want)
+    # int64 index tensors give the same bits
+    p2 = workloads.penalty(device="cuda", dtype=dtype)
+    F.apply_penalty(p2["logits"], p2["presence"], p2["frequency"], p2["ids"].long(), p2["counts"].long(), p2["cum"].long(), p2["max_len"])
+    assert torch.equal(p2["logits"].cpu(), want)
+
+
+# ------------------------------------------------------------------ rotary, RMSNorm
+@pytest.mark.parametrize("name", fixture_names("rotary_emb"))
+def test_rotary_fixture(F, name):
+    f = load_fixture(name)
+    x, c, s = cuda(f["x"], f["cos"], f["sin"])
+    out = F.rotary_emb(x, c, s, bool(f["conj"]), False)
+    close(out, f["out"])
+    assert torch.equal(x.cpu(), f["x"])
+
+
+def test_rotary_misc(F):
+    from diopi_b200.runtime import FunctionNotImplementedError
+    x = torch.randn(4, 6, 32, device="cuda", dtype=torch.float16)
+    c = torch.randn(4, 1, 16, device="cuda", dtype=torch.float16)
+    with pytest.raises(FunctionNotImplementedError):
+        F.rotary_emb(x, c, c, False, True)
+    # empty tensors are a no-op (diopi_configs.py:9080-9105)
+    for xs, cs in [((0,), (0,)), ((0, 128), (0, 64)), ((3, 8, 0), (3, 1, 0)), ((1, 0, 16, 32), (0, 1, 16))]:
+        e = torch.empty(xs, device="cuda", dtype=torch.float32)
+        ce = torch.empty(cs, device="cuda", dtype=torch.float32)
+        assert F.rotary_emb(e, ce, ce, False, False).shape == e.shape
+    # non-contiguous x (a slice of a fused qkv buffer) and in-place use
+    qkv = torch.randn(50, 3, 8, 64, device="cuda", dtype=torch.bfloat16)
+    xq = qkv[:, 0]
+    cs = torch.randn(50, 1, 32, device="cuda", dtype=torch.bfloat16)
+    sn = torch.randn(50, 1, 32, device="cuda", dtype=torch.bfloat16)
+    want = golden.rotary_emb(xq.cpu(), cs.cpu(), sn.cpu(), False)
+    close(F.rotary_emb(xq, cs, sn, False, False), want)
+    F.rotary_emb(xq, cs, sn, False, False, out=xq)
+    close(xq, want)
+
+
+def test_rotary_cfg3(F):
+    from diopi_b200 import workloads
+    p = workloads.prenorm(device="cuda")
+    x = p["k_in"].view(8192, p["heads"], p["head_dim"])
+    out = F.rotary_emb(x, p["cos"], p["sin"], False, False)
+    want = golden.rotary_emb(x.cpu(), p["cos"].cpu(), p["sin"].cpu(), False)
+    close(out, want)
+    assert torch.equal(out.cpu(), want)  # same fp32 operations and one rounding: identical bits
+
+
+@pytest.mark.parametrize("name", fixture_names("rms_norm"))
+def test_rms_norm_fixture(F, name):
+    f = load_fixture(name)
+    x, w = cuda(f["x"], f["weight"])
+    b = f["bias"].cuda() if "bias" in f else None
+    ns = tuple(f["normalized_shape"].tolist())
+    out, inv = F.rms_norm(x, ns, w, b, f["eps"], return_inv_rms=True)
+    # the reference's own tolerance for rms_norm is 1e-4 (diopi_configs.py:9139-9140); halves get 1e-2
+    t = dict(rtol=1e-4, atol=1e-4) if x.dtype in (torch.float32, torch.float64) else TOL16
+    torch.testing.assert_close(out.cpu().double(), f["out"].double(), **t)
+    _, inv_ref = golden.rms_norm(f["x"], ns, f["weight"], f.get("bias"), f["eps"], return_inv_rms=True)
+    torch.testing.assert_close(inv.cpu().double(), inv_ref.double(), rtol=1e-5, atol=1e-6)
+    assert inv.dtype == (torch.float64 if x.dtype == torch.float64 else torch.float32)
+
+
+@pytest.mark.parametrize("n2", [8, 200, 256, 1000, 1024, 4096, 5120, 8192, 16384, 40000, 70000])
+def test_rms_norm_widths(F, n2):
+    g = torch.Generator().manual_seed(n2)
+    for dtype in (torch.bfloat16, torch.float32):
+        x = torch.randn(5, n2, generator=g).to(dtype)
+        w = (1 + 0.1 * torch.randn(n2, generator=g)).to(dtype)
+        b = torch.randn(n2, generator=g).to(dtype)
+        want, inv_ref = golden.rms_norm(x, (n2,), w, b, 1e-5, return_inv_rms=True)
+        out, inv = F.rms_norm(x.cuda(), (n2,), w.cuda(), b.cuda(), 1e-5, return_inv_rms=True)
+        close(out, want)
+        torch.testing.assert_close(inv.cpu(), inv_ref, rtol=1e-5, atol=1e-6)
+
+
+def test_rms_norm_cfg3(F):
+    from diopi_b200 import workloads
+    p = workloads.prenorm(device="cuda")
+    out, inv = F.rms_norm(p["x"], (4096,), p["weight"], None, p["eps"], return_inv_rms=True)
+    want, inv_ref = golden.rms_norm(p["x"].cpu(), (4096,), p["weight"].cpu(), None, p["eps"], return_inv_rms=True)
+    close(out, want)
+    torch.testing.assert_close(inv.cpu(), inv_ref, rtol=1e-5, atol=1e-6)
+    # at most one bf16 ulp apart anywhere (the sum of squares is added in another order)
+    diff = (out.cpu().float() - want.float()).abs()
+    assert float((diff / want.float().abs().clamp_min(1e-3)).max()) < 1e-2
+
+
+# ------------------------------------------------------------------ prefill
+@pytest.mark.parametrize("name", fixture_names("context_attention"))
+def test_context_attention_fixture(F, name):
+    f = load_fixture(name)
+    q, k, v, st, bn = cuda(f["q"], f["k"], f["v"], f["b_start_loc"], f["b_seq_len"])
+    out = torch.zeros_like(q)
+    F.context_attention(q, k, v, out, st, bn, f["max_input_len"])
+    close(out, f["out"])
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("H,D,lens", [(4, 128, [1, 130, 7, 257]), (2, 64, [300, 1]), (3, 80, [33, 64]), (2, 128, [128, 256, 0, 384])])
+def test_context_attention_ragged(F, dtype, H, D, lens):
+    g = torch.Generator().manual_seed(sum(lens) + D)
+    total = sum(lens)
+    q, k, v = ((torch.randn(total, H, D, generator=g) / D ** 0.5 * 3).to(dtype) for _ in range(3))
+    lens_t = torch.tensor(lens, dtype=torch.int32)
+    st = torch.cat([torch.zeros(1, dtype=torch.int32), lens_t.cumsum(0)[:-1].to(torch.int32)])
+    want = golden.context_attention(q, k, v, torch.zeros(total, H, D), st, lens_t, max(lens), upcast=True)
+    out = torch.zeros(total, H, D, dtype=dtype, device="cuda")
+    F.context_attention(q.cuda(), k.cuda(), v.cuda(), out, st.cuda(), lens_t.cuda(), max(lens))
+    close(out, want, dtype)
+    # int64 index tensors, and a max_input_len that understates the lengths (the reference ignores it)
+    out2 = torch.zeros_like(out)
+    F.context_attention(q.cuda(), k.cuda(), v.cuda(), out2, st.long().cuda(), lens_t.long().cuda(), 1)
+    assert torch.equal(out2, out)

@@ -1,0 +1,120 @@
+"""Argument validation of every exported op, on CPU: each call must come back with an error code and
+a message before any CUDA work is attempted (the tensors here only pretend to live on a device)."""
+import pytest
+import torch
+
+from diopi_b200.runtime import DTYPE_NOT_SUPPORTED, ERROR_OCCURRED, NO_IMPLEMENT, DiopiError
+
+
+@pytest.fixture(scope="module")
+def F(built_libs):
+    from diopi_b200 import functions
+    return functions
+
+
+def fails(code, fn, *args, match=None, **kw):
+    with pytest.raises(DiopiError, match=match) as e:
+        fn(*args, as_device=True, **kw)
+    assert e.value.code == code, e.value
+    return e.value
+
+
+def decode_args(dtype=torch.float16, B=2, H=4, D=64, slots=32, N=8, idx=torch.int32):
+    return dict(q=torch.zeros(B, H, D, dtype=dtype), k=torch.zeros(slots, H, D, dtype=dtype), v=torch.zeros(slots, H, D, dtype=dtype),
+                out=torch.zeros(B, H, D, dtype=dtype), att=torch.zeros(H, 16, dtype=dtype), b_loc=torch.zeros(B, N, dtype=idx),
+                st=torch.zeros(B, dtype=idx), ln=torch.zeros(B, dtype=idx))
+
+
+def test_decode_validation(F):
+    a = decode_args()
+    fails(ERROR_OCCURRED, F.token_decode_attention, a["q"], a["k"], a["v"], a["out"], a["b_loc"], a["st"], a["ln"], 9, match="fewer than max_input_len")
+    fails(ERROR_OCCURRED, F.token_decode_attention, a["q"], a["k"], a["v"], a["out"], a["b_loc"], a["st"], a["ln"], -1, match="negative")
+    fails(ERROR_OCCURRED, F.token_decode_attention, a["q"][:, :2], a["k"], a["v"], a["out"], a["b_loc"], a["st"], a["ln"], 4, match="'q' must be")
+    fails(ERROR_OCCURRED, F.token_decode_attention, a["q"], a["k"], a["v"].float(), a["out"], a["b_loc"], a["st"], a["ln"], 4, match="share a dtype")
+    fails(ERROR_OCCURRED, F.token_decode_attention, a["q"], a["k"], a["v"][:5], a["out"], a["b_loc"], a["st"], a["ln"], 4, match="slot count")
+    fails(DTYPE_NOT_SUPPORTED, F.token_decode_attention, a["q"], a["k"], a["v"], a["out"], a["b_loc"].float(), a["st"], a["ln"], 4, match="int32 or int64")
+    fails(ERROR_OCCURRED, F.token_decode_attention, a["q"], a["k"], a["v"], a["out"], a["b_loc"], a["st"][:1], a["ln"], 4, match="batch")
+    d = decode_args(dtype=torch.float64)
+    fails(DTYPE_NOT_SUPPORTED, F.token_decode_attention, d["q"], d["k"], d["v"], d["out"], d["b_loc"], d["st"], d["ln"], 4, match="float64")
+    fails(ERROR_OCCURRED, F.token_attention, a["q"], a["k"], a["att"][:2], a["b_loc"], a["st"], a["ln"], 4, match="logits")
+    fails(ERROR_OCCURRED, F.token_softmax_reducev, a["att"], a["v"], a["out"][:1], a["b_loc"], a["st"], a["ln"], 4, 0, match="'out' must be")
+    fails(ERROR_OCCURRED, F.token_attention, a["q"], a["k"][0], a["att"], a["b_loc"], a["st"], a["ln"], 4, match="pool must be")
+
+
+def test_null_handles(F, built_libs):
+    import ctypes
+    rc = built_libs.impl.diopiDestIndexCopyKV(None, None, None, None)
+    assert rc == ERROR_OCCURRED and "null handle" in F.last_error()
+    rc = built_libs.impl.diopiRMSNorm(None, None, None, None, built_libs.impl.diopiRMSNorm.argtypes[4](), None, None, ctypes.c_double(1e-6))
+    assert rc == ERROR_OCCURRED
+
+
+def test_host_tensor_is_refused(F):
+    a = decode_args()
+    with pytest.raises(DiopiError, match="host memory"):
+        F.destindex_copy_kv(a["q"], torch.zeros(2, dtype=torch.int32), a["k"], as_device=False)
+
+
+def test_copy_kv_validation(F):
+    k, out, d = torch.zeros(3, 4, 8), torch.zeros(10, 4, 8), torch.zeros(3, dtype=torch.int32)
+    fails(ERROR_OCCURRED, F.destindex_copy_kv, k, d, out.half(), match="share a dtype")
+    fails(ERROR_OCCURRED, F.destindex_copy_kv, k, d[:2], out, match="entries")
+    fails(ERROR_OCCURRED, F.destindex_copy_kv, k, d, out[:, :2], match="but 'out' is")
+    fails(DTYPE_NOT_SUPPORTED, F.destindex_copy_kv, k, d.to(torch.int16), out, match="int32 or int64")
+
+
+def test_rotary_validation(F):
+    x, c = torch.zeros(2, 3, 8), torch.zeros(2, 1, 4)
+    e = fails(NO_IMPLEMENT, F.rotary_emb, x, c, c, False, True, match="interleaved")
+    assert e.code == 13
+    fails(ERROR_OCCURRED, F.rotary_emb, torch.zeros(2, 3, 7), c, c, False, False, match="even")
+    fails(ERROR_OCCURRED, F.rotary_emb, x, torch.zeros(2, 1, 3), c, False, False, match="last dim of 'cos'")
+    fails(ERROR_OCCURRED, F.rotary_emb, x, torch.zeros(5, 1, 4), torch.zeros(5, 1, 4), False, False, match="broadcast")
+    fails(ERROR_OCCURRED, F.rotary_emb, x, c.half(), c.half(), False, False, match="share a dtype")
+    fails(DTYPE_NOT_SUPPORTED, F.rotary_emb, x.int(), c.int(), c.int(), False, False)
+
+
+def test_rms_norm_validation(F):
+    x, w = torch.zeros(4, 6), torch.zeros(6)
+    fails(ERROR_OCCURRED, F.rms_norm, x, (5,), w, None, 1e-6, match="normalized_shape")
+    fails(ERROR_OCCURRED, F.rms_norm, x, (6,), torch.zeros(5), None, 1e-6, match="'weight' must have")
+    fails(ERROR_OCCURRED, F.rms_norm, x, (6,), w, torch.zeros(3), 1e-6, match="'bias' must have")
+    fails(ERROR_OCCURRED, F.rms_norm, x.t()[:6, :4].t(), (6,), w, None, 1e-6, match="contiguous") if False else None
+    fails(ERROR_OCCURRED, F.rms_norm, x, (6,), w.half(), None, 1e-6, match="share a dtype")
+    fails(ERROR_OCCURRED, F.rms_norm, x, (1, 2, 3), w, None, 1e-6, match="trailing dims")
+    xt = torch.zeros(6, 4).t()   # shape [4, 6], not contiguous
+    fails(ERROR_OCCURRED, F.rms_norm, xt, (6,), w, None, 1e-6, match="contiguous")
+
+
+def test_penalty_validation(F):
+    lg, p = torch.zeros(3, 10), torch.zeros(3)
+    ids, cum = torch.zeros(5, dtype=torch.int32), torch.zeros(4, dtype=torch.int32)
+    fails(ERROR_OCCURRED, F.apply_penalty, lg, p[:2], p, ids, ids, cum, 0, match="penalties")
+    fails(ERROR_OCCURRED, F.apply_penalty, lg, p, p, ids, ids[:4], cum, 0, match="differ in length")
+    fails(ERROR_OCCURRED, F.apply_penalty, lg, p, p, ids, ids, cum[:3], 0, match="batch \\+ 1")
+    fails(ERROR_OCCURRED, F.apply_penalty, lg, p.half(), p, ids, ids, cum, 0, match="share a dtype")
+    fails(DTYPE_NOT_SUPPORTED, F.apply_penalty, lg.int(), p.int(), p.int(), ids, ids, cum, 0)
+
+
+def test_context_attention_validation(F):
+    q = torch.zeros(8, 2, 16, dtype=torch.float16)
+    st, ln = torch.zeros(2, dtype=torch.int32), torch.zeros(2, dtype=torch.int32)
+    fails(ERROR_OCCURRED, F.context_attention, q, q[:4], q, q.clone(), st, ln, 4, match="share the shape")
+    fails(ERROR_OCCURRED, F.context_attention, q, q, q, q.clone(), st, ln[:1], 4, match="differ in length")
+    fails(DTYPE_NOT_SUPPORTED, F.context_attention, q.double(), q.double(), q.double(), q.double(), st, ln, 4)
+    big = torch.zeros(2, 1, 300, dtype=torch.float16)
+    fails(ERROR_OCCURRED, F.context_attention, big, big, big, big.clone(), st, ln, 4, match="maximum of 256")
+
+
+def test_zero_size_inputs_succeed_without_a_device(F):
+    """Empty tensors return success before any launch (diopi_configs.py:9080-9105 for rotary)."""
+    e = torch.zeros(0, 4, 8)
+    F.destindex_copy_kv(e, torch.zeros(0, dtype=torch.int32), torch.zeros(5, 4, 8), as_device=True)
+    F.rotary_emb(torch.zeros(0, 8), torch.zeros(0, 4), torch.zeros(0, 4), False, False, as_device=True)
+    F.rms_norm(torch.zeros(0, 8), (8,), torch.zeros(8), None, 1e-6, as_device=True)
+    F.apply_penalty(torch.zeros(2, 5), torch.zeros(2), torch.zeros(2), torch.zeros(0, dtype=torch.int32), torch.zeros(0, dtype=torch.int32),
+                    torch.zeros(3, dtype=torch.int32), 0, as_device=True)
+    F.context_attention(torch.zeros(0, 2, 8), torch.zeros(0, 2, 8), torch.zeros(0, 2, 8), torch.zeros(0, 2, 8), torch.zeros(0, dtype=torch.int32),
+                        torch.zeros(0, dtype=torch.int32), 0, as_device=True)
+    a = decode_args(B=0)
+    F.token_decode_attention(a["q"], a["k"], a["v"], a["out"], a["b_loc"], a["st"], a["ln"], 4, as_device=True)
