@@ -22,6 +22,8 @@ DECODE_CONFIGS = {
     # name: (batch, heads, head_dim, dtype, len_lo, len_hi, pool rule, kv std, seed)
     "cfg1": dict(B=4, H=8, D=64, dtype=torch.float32, lo=16, hi=128, pool="sum+64", std=1.0, seed=1001),
     "cfg2": dict(B=64, H=32, D=128, dtype=torch.float16, lo=512, hi=4096, pool="B*hi", std=0.5, seed=1002),
+    # a quarter of cfg2 (same rows, 16 requests): small enough for a multi-pass profiler capture, still >> L2
+    "cfg2s": dict(B=16, H=32, D=128, dtype=torch.float16, lo=512, hi=4096, pool="B*hi", std=0.5, seed=1012),
     "cfg5": dict(B=128, H=64, D=128, dtype=torch.float16, lo=1024, hi=8192, pool="sum+128", std=0.5, seed=1005),
 }
 
