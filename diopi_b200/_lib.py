@@ -34,6 +34,7 @@ OPS = {
     "diopiTokenAttentionInference": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int],
     "diopiTokenSoftmaxReduceVInference": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int],
     "diopiTokenDecodeAttentionInference": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int],
+    "diopiTokenDecodeAttentionInferenceNoAlloc": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int],
     "diopiContextAttentionInference": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int],
     "diopiApplyPenalty": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int],
     "diopiRotaryEmbedding": [c_void_p, c_void_p, c_void_p, c_void_p, c_bool, c_bool],

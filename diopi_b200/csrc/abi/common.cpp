@@ -202,6 +202,8 @@ int* async_status_device_ptr() {
     return h;
 }
 
+int* async_status_device_ptr_if_ready() { return g_status_host.load(std::memory_order_acquire); }
+
 void check_async_status() {
     int* h = g_status_host.load(std::memory_order_acquire);
     if (!h) return;

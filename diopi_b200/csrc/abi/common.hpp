@@ -88,6 +88,8 @@ const DeviceInfo& device_info();
 // must refuse (an index outside the pool, a wait that ran out). Read at the start of every op
 // at no cost; a non-zero value is reported once as an error of the op that sees it.
 int* async_status_device_ptr();
+// The same word if an earlier call already set it up, else null (kernels accept null). Never allocates.
+int* async_status_device_ptr_if_ready();
 void check_async_status();
 
 // Runs `body`, mapping exceptions to return codes; nothing escapes the C boundary.

@@ -414,3 +414,92 @@ B200_EXPORT diopiError_t diopiRMSNorm(diopiContextHandle_t ctx, diopiTensorHandl
         B200_CUDA(cudaGetLastError());
     });
 }
+
+// ---------------------------------------------------------------------------------------------
+// The fused decode step for callers that cannot hand out scratch memory.
+//
+// diopiTokenDecodeAttentionInference asks the caller's context (diopiRequireBuffer /
+// diopiRequireTensor) for the few MB its split-KV partials need. Some callers cannot answer that:
+// a serving engine that gave every free byte of HBM to its KV pool at start-up and runs its decode
+// loop with no allocator behind the context, or a thin C harness that implements the tensor
+// accessors but leaves diopiRequireTensor returning an error. This entry point runs the same
+// kernels on a fixed 8 MiB array inside the library's device image instead. It calls no
+// cudaMalloc/cudaFree/cudaHostAlloc and never calls back into diopiRequire*.
+//
+// Limits and rules, all checked or stated here:
+//  * (148 + batch) * head_num * (head_dim + 2) * 4 bytes must fit in 8 MiB (e.g. batch <= 356 at
+//    32 heads x 128); larger problems are refused with an error that names both numbers. Shapes that
+//    the scratch-free plain path serves (odd head_dim, strided rows) have no such limit.
+//  * The first call on each device looks up the array's address (cudaGetSymbolAddress); make that
+//    first call during start-up, before any stream capture begins.
+//  * All calls on a device share the one array. It needs no clearing between calls, but two calls
+//    that may run on the GPU at the same time (different streams) race on it: keep them on one stream
+//    or order them with events.
+//  * Out-of-range slot indices are still skipped, but are only reported through the status word if
+//    an earlier ordinary call created that word; this entry point does not create it.
+B200_EXPORT diopiError_t diopiTokenDecodeAttentionInferenceNoAlloc(diopiContextHandle_t ctx, diopiTensorHandle_t out, diopiConstTensorHandle_t q,
+                                                                   diopiConstTensorHandle_t kh, diopiConstTensorHandle_t v, diopiConstTensorHandle_t b_loc,
+                                                                   diopiConstTensorHandle_t b_start_loc, diopiConstTensorHandle_t b_seq_len,
+                                                                   int max_input_len) {
+    return guard("diopiTokenDecodeAttentionInferenceNoAlloc", [&] {
+        TensorView o = view_of(out, "out"), qv = view_of(q, "q"), kv = view_of(kh, "k"), vv = view_of(v, "v");
+        TensorView bl = view_of(b_loc, "b_loc"), bs = view_of(b_start_loc, "b_start_loc"), bn = view_of(b_seq_len, "b_seq_len");
+        k::DecodeArgs a{};
+        a.mode = k::DecodeMode::FUSED;
+        a.dt = float_dt(kv, "k", false);
+        B200_REQUIRE(kv.ndim == 3 && vv.ndim == 3 && qv.ndim == 3 && o.ndim == 3, "q, k, v and out must have 3 dims");
+        a.H = static_cast<int>(kv.shape[1]);
+        a.D = static_cast<int>(kv.shape[2]);
+        a.slots = kv.shape[0];
+        B200_REQUIRE(bl.ndim == 2, "'b_loc' must be [batch, N], got %d dims", bl.ndim);
+        a.B = static_cast<int>(bl.shape[0]);
+        B200_REQUIRE(max_input_len >= 0 && bl.shape[1] >= max_input_len, "'b_loc' has %ld columns for max_input_len = %d", (long)bl.shape[1], max_input_len);
+        a.max_input_len = max_input_len;
+        a.b_loc = index_arg(bl, "b_loc", 2);
+        a.b_start = index_arg(bs, "b_start_loc", 1);
+        a.b_len = index_arg(bn, "b_seq_len", 1);
+        B200_REQUIRE(bs.shape[0] == a.B && bn.shape[0] == a.B, "'b_start_loc' and 'b_seq_len' must have batch = %d entries", a.B);
+        B200_REQUIRE(a.D <= 512, "head_dim %d is beyond the supported maximum of 512", a.D);
+        same_dtype(qv, "q", kv, "k");
+        same_dtype(vv, "v", kv, "k");
+        same_dtype(o, "out", kv, "k");
+        B200_REQUIRE(qv.shape[0] == a.B && qv.shape[1] == a.H && qv.shape[2] == a.D, "'q' must be [%d, %d, %d]", a.B, a.H, a.D);
+        B200_REQUIRE(o.shape[0] == a.B && o.shape[1] == a.H && o.shape[2] == a.D, "'out' must be [%d, %d, %d]", a.B, a.H, a.D);
+        B200_REQUIRE(vv.shape[0] == kv.shape[0] && vv.shape[1] == a.H && vv.shape[2] == a.D, "'v' must have the shape of 'k'");
+        a.q = qv.data;
+        a.q_s0 = qv.stride[0];
+        a.q_s1 = qv.stride[1];
+        a.q_s2 = qv.stride[2];
+        a.kmat = kv.data;
+        a.k_s0 = kv.stride[0];
+        a.k_s1 = kv.stride[1];
+        a.k_s2 = kv.stride[2];
+        a.vmat = vv.data;
+        a.v_s0 = vv.stride[0];
+        a.v_s1 = vv.stride[1];
+        a.v_s2 = vv.stride[2];
+        a.out = o.data;
+        a.out_s0 = o.stride[0];
+        a.out_s1 = o.stride[1];
+        a.out_s2 = o.stride[2];
+        if (a.B == 0 || a.H == 0 || a.D == 0) return;
+        B200_REQUIRE(a.slots > 0 || max_input_len == 0, "the K/V pool has no slots");
+        cudaStream_t st = stream_of(ctx);
+        if (max_input_len == 0) {
+            B200_REQUIRE(o.contiguous(), "'out' must be contiguous when every request is empty");
+            B200_CUDA(cudaMemsetAsync(o.data, 0, static_cast<size_t>(o.numel * o.elem_size()), st));
+            return;
+        }
+        const DeviceInfo& di = device_info();
+        a.status = async_status_device_ptr_if_ready();
+        int64_t needed = 0;
+        cudaError_t e = k::launch_decode_static_scratch(a, di.sm_count, di.max_smem_optin, st, &needed);
+        if (e == cudaErrorMemoryAllocation)
+            fail(diopiErrorOccurred,
+                 "this problem needs %ld bytes of split-KV scratch but the built-in array holds %ld; use diopiTokenDecodeAttentionInference "
+                 "(scratch from the context) or a smaller batch",
+                 (long)needed, (long)k::decode_static_scratch_capacity());
+        B200_CUDA(e);
+        B200_CUDA(cudaGetLastError());
+    });
+}

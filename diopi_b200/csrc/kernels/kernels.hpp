@@ -55,6 +55,11 @@ struct DecodeArgs {
 int64_t decode_workspace_bytes(const DecodeArgs& a, int sm_count, int max_smem);
 // `ws` must hold decode_workspace_bytes(); ignored by the plain path.
 void launch_decode(const DecodeArgs& a, void* ws, int sm_count, int max_smem, cudaStream_t st);
+// Same launch on the library's built-in scratch array. `needed` receives the scratch size of these arguments;
+// cudaErrorMemoryAllocation means it exceeds decode_static_scratch_capacity() and nothing was launched.
+// The first call on a device looks up the array's device address (cudaGetSymbolAddress). Allocates nothing.
+int64_t decode_static_scratch_capacity();
+cudaError_t launch_decode_static_scratch(const DecodeArgs& a, int sm_count, int max_smem, cudaStream_t st, int64_t* needed);
 
 // ---- RMSNorm ----------------------------------------------------------------
 struct RmsNormArgs {

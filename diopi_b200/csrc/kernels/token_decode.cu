@@ -29,6 +29,7 @@
 // rows are not 16-byte aligned/dense or D*e/16 is not 8, 16 or 32.
 #include <cfloat>
 #include <cstdlib>
+#include <mutex>
 
 #include "dev_util.cuh"
 
@@ -761,6 +762,41 @@ void launch_plain_mode(const DecodeArgs& a, cudaStream_t st) {
 int64_t split_ws_floats_acc(const DecodeArgs& a, const SplitPlan& p) { return static_cast<int64_t>(p.n_cta + a.B) * a.H * a.D; }
 int64_t split_ws_floats_ml(const DecodeArgs& a, const SplitPlan& p) { return static_cast<int64_t>(p.n_cta + a.B) * a.H * 2; }
 
+// ---------------------------------------------------------------------------
+// Built-in scratch for callers that cannot provide any.
+//
+// The fused decode kernel needs a few MB for its split-KV partials. The regular entry point asks the
+// caller's context for them. A serving engine that gives all free HBM to its KV pool at start-up and
+// then runs its decode loop without an allocator has nothing to answer that request with, so a second
+// entry point runs the same kernels on this fixed array instead. The array is part of the library's
+// device image: every GPU that loads the library holds kStaticScratchBytes of it until the process ends.
+// All calls on a device share it; nothing in it has to start at zero (each partial the merge kernel
+// reads was written earlier in the same call), but two calls that run on the GPU at the same time
+// (different streams) would overwrite each other's partials.
+// ---------------------------------------------------------------------------
+constexpr int64_t kStaticScratchBytes = 8ll << 20;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+// In host code `g_static_scratch` is only a handle for the run time, not an address a kernel may use:
+// the device address is looked up once per device (with that device current) and cached.
+cudaError_t static_scratch_address(void** out) {
+    static std::mutex mu;
+    static void* cached[64] = {nullptr};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+    std::lock_guard<std::mutex> lock(mu);
+    if (cached[dev] == nullptr) {
+        void* p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_static_scratch);
+        if (e != cudaSuccess) return e;
+        cached[dev] = p;
+    }
+    *out = cached[dev];
+    return cudaSuccess;
+}
+
 }  // namespace
 
 int64_t decode_workspace_bytes(const DecodeArgs& a, int sm_count, int max_smem) {
@@ -795,6 +831,20 @@ void launch_decode(const DecodeArgs& a, void* ws, int sm_count, int max_smem, cu
         case Dt::F32: launch_plain_mode<float>(a, st); break;
         default: break;  // fp64 is refused by the caller
     }
+}
+
+int64_t decode_static_scratch_capacity() { return kStaticScratchBytes; }
+
+cudaError_t launch_decode_static_scratch(const DecodeArgs& a, int sm_count, int max_smem, cudaStream_t st, int64_t* needed) {
+    *needed = decode_workspace_bytes(a, sm_count, max_smem);
+    if (*needed > kStaticScratchBytes) return cudaErrorMemoryAllocation;  // the caller turns this into its own message
+    void* ws = nullptr;
+    if (*needed > 0) {
+        cudaError_t e = static_scratch_address(&ws);
+        if (e != cudaSuccess) return e;
+    }
+    launch_decode(a, ws, sm_count, max_smem, st);
+    return cudaSuccess;
 }
 
 }  // namespace k

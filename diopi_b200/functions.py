@@ -72,6 +72,15 @@ def token_decode_attention(q, k, v, out, b_loc, b_start_loc, b_seq_len, max_inpu
     return out
 
 
+def token_decode_attention_noalloc(q, k, v, out, b_loc, b_start_loc, b_seq_len, max_input_len, *, ctx=None, as_device=None):
+    """The fused decode step on the library's built-in scratch array: for callers whose context cannot
+    hand out device memory (no allocator behind diopiRequireTensor). Same result as token_decode_attention;
+    refuses problems whose split-KV partials exceed the 8 MiB array. Returns out."""
+    ts = [_t(x, as_device) for x in (out, q, k, v, b_loc, b_start_loc, b_seq_len)]
+    _call("diopiTokenDecodeAttentionInferenceNoAlloc", ctx, *[_h(t) for t in ts], int(max_input_len))
+    return out
+
+
 def context_attention(q, k, v, out, b_start_loc, b_seq_len, max_input_len, *, ctx=None, as_device=None):
     """Causal prefill over the packed ragged batch; returns out."""
     ts = [_t(x, as_device) for x in (out, q, k, v, b_start_loc, b_seq_len)]

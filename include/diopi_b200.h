@@ -191,6 +191,18 @@ diopiError_t diopiTokenDecodeAttentionInference(diopiContextHandle_t ctx, diopiT
                                                 diopiConstTensorHandle_t v, diopiConstTensorHandle_t b_loc, diopiConstTensorHandle_t b_start_loc,
                                                 diopiConstTensorHandle_t b_seq_len, int max_input_len);
 
+/* Extension with no counterpart in the reference: the same fused decode step for callers that
+ * cannot provide scratch memory (an engine whose HBM all went to the KV pool and whose context has
+ * no allocator; a harness whose diopiRequireTensor fails). It never calls diopiRequireBuffer /
+ * diopiRequireTensor and allocates nothing: the split-KV partials go to a fixed 8 MiB array inside
+ * the library's device image, held by every GPU that loads the library. Refuses, with an error,
+ * problems whose partials ((148 + batch) * head_num * (head_dim + 2) * 4 bytes) exceed it. The first
+ * call on a device looks up the array's address: make it before any stream capture. Calls that may
+ * overlap on one GPU share the array and race; keep them on one stream. */
+diopiError_t diopiTokenDecodeAttentionInferenceNoAlloc(diopiContextHandle_t ctx, diopiTensorHandle_t out, diopiConstTensorHandle_t q,
+                                                       diopiConstTensorHandle_t k, diopiConstTensorHandle_t v, diopiConstTensorHandle_t b_loc,
+                                                       diopiConstTensorHandle_t b_start_loc, diopiConstTensorHandle_t b_seq_len, int max_input_len);
+
 #if defined(__cplusplus)
 }
 #endif
