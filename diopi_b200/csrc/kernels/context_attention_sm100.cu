@@ -1,11 +1,530 @@
-// Tensor-core causal prefill for sm_100a (tcgen05 + TMEM + TMA). Placeholder until the kernel
-// lands: reports "not taken" so that every shape runs on the blockwise SIMT kernel.
+// Tensor-core causal prefill for sm_100a: tcgen05.mma with accumulators in TMEM, operands staged by TMA.
+// Path of diopiContextAttentionInference for fp16/bf16, head_dim 128, dense 16-byte aligned rows; every
+// other shape runs on the blockwise SIMT kernel. Replaces the per-request matmul/mask/softmax/matmul
+// chain of impl/torch/functions/functions_lightllm.cpp:109-147.
+//
+// One CTA = one tile of 128 query rows of one (request, head); two CTAs share an SM so that one CTA's
+// soft-max overlaps the other's MMAs. Per CTA, for key blocks of 64 up to the causal limit:
+//   warp 0 (one lane)  TMA: Q once (two 64-wide boxes, 128-byte swizzle), then K_j and V_j into a 2-stage ring
+//   warp 1 (one lane)  S_j = Q K_j^T   (tcgen05.mma M128 N64 K16 x 8, both operands K-major) -> TMEM S[j%2]
+//                      O  += P_j V_j   (tcgen05.mma M128 N128 K16 x 4, P K-major from shared memory, V MN-major)
+//   warps 2-5          thread = query row: tcgen05.ld of its S row, scale, causal/length mask, online soft-max
+//                      in base 2 with a lazily updated maximum (O in TMEM is rescaled only when the maximum
+//                      grew by more than 2^8), P_j as fp16/bf16 into shared memory in the MMA's swizzled layout
+// The L x L score and mask tensors of the reference never exist; FLOPs counted = 4*D*L*(L+1)/2 per head.
+//
+// All waits are bounded (2 s); a wait that runs out sets a flag, every role leaves its loop, TMEM is
+// freed and the status word is written. No TMA multicast is used.
+#include <cuda.h>
+
+#include <mutex>
+
 #include "dev_util.cuh"
 
 namespace b200 {
 namespace k {
 
-void launch_prefill_tc(const PrefillArgs& /*a*/, int /*sm_count*/, int /*max_smem*/, cudaStream_t /*st*/, bool* taken) { *taken = false; }
+namespace {
+
+constexpr int BM = 128;      // query rows per CTA
+constexpr int BN = 64;       // keys per block
+constexpr int HD = 128;      // head dim
+constexpr int kStages = 2;   // K/V ring
+constexpr int kThreads = 192;
+constexpr unsigned long long kWaitLimitNs = 2000000000ull;
+constexpr float kLog2e = 1.4426950408889634f;
+
+// shared memory map (bytes); every operand tile starts on a 1024-byte boundary (128-byte swizzle atoms)
+constexpr int kQBytes = BM * HD * 2;            // 32 KB: two [128 x 64] blocks
+constexpr int kKStage = BN * HD * 2;            // 16 KB: two [64 x 64] blocks
+constexpr int kVStage = BN * HD * 2;            // 16 KB
+constexpr int kPBytes = BM * BN * 2;            // 16 KB: one [128 x 64] block
+constexpr int kOffQ = 0;
+constexpr int kOffK = kOffQ + kQBytes;
+constexpr int kOffV = kOffK + kStages * kKStage;
+constexpr int kOffP = kOffV + kStages * kVStage;
+constexpr int kOffBar = kOffP + kPBytes;        // 112 KB
+constexpr int kNumBars = 1 + 4 * kStages + 2 * 2 + 3;   // q, k/v full+empty, s full+empty, p full/empty, o full
+constexpr int kOffTmemSlot = kOffBar + kNumBars * 8;
+constexpr int kOffFlag = kOffTmemSlot + 8;
+constexpr int kSmemBytes = kOffFlag + 8;          // two CTAs per SM: 2 * (112.2 KB + 1 KB reserved) fits the SM's 228 KB
+
+// TMEM columns (fp32): S[0] 0..63, S[1] 64..127, O 128..255
+constexpr uint32_t kTmemCols = 256;
+constexpr uint32_t kColS0 = 0, kColO = 128;
+
+enum Bar { Q_FULL = 0, K_FULL = 1, V_FULL = 3, K_EMPTY = 5, V_EMPTY = 7, S_FULL = 9, S_EMPTY = 11, P_FULL = 13, P_EMPTY = 14, O_FULL = 15 };
+
+struct TcParams {
+    IndexArg b_start, b_len;
+    int B, H;
+    int64_t total_rows;
+    void* out;
+    int64_t o_s0, o_s1;
+    int n_tiles_max;
+    float scale_log2;
+    int is_bf16;
+    int* status;
+};
+
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) { asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory"); }
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) { asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory"); }
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* give_up) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const unsigned long long t0 = global_ns();
+    uint32_t spins = 0;
+    while (!mbar_try_wait(bar, parity)) {
+        if ((++spins & 0x3fu) == 0) {
+            if (*give_up) return false;
+            if (global_ns() - t0 > kWaitLimitNs) {
+                *give_up = 1;
+                return false;
+            }
+        }
+    }
+    return true;
+}
+
+// Warp-uniform form for code that goes on to warp-collective tcgen05.ld/st: all lanes agree on the outcome.
+__device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, volatile int* give_up) {
+    return __all_sync(0xffffffffu, mbar_wait(bar, parity, give_up) ? 1 : 0) != 0;
+}
+
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];" ::"r"(dst),
+                 "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(c2), "r"(bar)
+                 : "memory");
+}
+
+// Shared-memory matrix descriptor for tcgen05.mma, 128-byte swizzle.
+//   bits  0-13  start address >> 4          bits 16-29  leading-dimension byte offset >> 4
+//   bits 32-45  stride byte offset >> 4     bits 46-47  descriptor version (1 on sm_100)
+//   bits 61-63  swizzle mode (2 = 128-byte)
+__device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((smem_addr & 0x3ffffu) >> 4);
+    d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3fffu) << 16;
+    d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3fffu) << 32;
+    d |= 1ull << 46;
+    d |= 2ull << 61;
+    return d;
+}
+
+// Instruction descriptor, kind::f16, fp32 accumulate.
+//   bits 4-5 D format (1 = f32)   bits 7-9 A format, 10-12 B format (0 = f16, 1 = bf16)
+//   bit 15 A major, bit 16 B major (0 = K-major, 1 = MN-major)   bits 17-22 N>>3   bits 24-28 M>>4
+__device__ __forceinline__ uint32_t make_idesc(int m, int n, int bf16, int b_mn_major) {
+    uint32_t d = 0;
+    d |= 1u << 4;
+    d |= static_cast<uint32_t>(bf16 ? 1 : 0) << 7;
+    d |= static_cast<uint32_t>(bf16 ? 1 : 0) << 10;
+    d |= static_cast<uint32_t>(b_mn_major ? 1 : 0) << 16;
+    d |= static_cast<uint32_t>(n >> 3) << 17;
+    d |= static_cast<uint32_t>(m >> 4) << 24;
+    return d;
+}
+
+__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(tmem_d),
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]),
+          "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
+          "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]),
+          "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};" ::"r"(taddr),
+        "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]),
+        "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]),
+        "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+__device__ __forceinline__ uint32_t pack2(float a, float b, int bf16) {
+    if (bf16) {
+        __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+        return *reinterpret_cast<uint32_t*>(&v);
+    }
+    __half2 v = __floats2half2_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+__global__ void __launch_bounds__(kThreads, 2) prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                                                                   const __grid_constant__ CUtensorMap map_v, const TcParams p) {
+    extern __shared__ __align__(1024) unsigned char smem[];
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kOffBar);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + kOffTmemSlot);
+    volatile int* give_up = reinterpret_cast<volatile int*>(smem + kOffFlag);
+    auto bar = [&](int i) { return smem_u32(&bars[i]); };
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int h = blockIdx.y;
+
+    // ---- which (request, row tile) is this CTA? Heaviest tiles (late rows) are handed out first. ----
+    int req = -1;
+    int64_t L = 0, start = 0, r0 = 0;
+    {
+        const int64_t flat = static_cast<int64_t>(p.n_tiles_max) - 1 - blockIdx.x;
+        int64_t before = 0;
+        for (int i = 0; i < p.B; ++i) {
+            int64_t Li = load_index(p.b_len, i);
+            const int64_t si = load_index(p.b_start, i);
+            if (Li <= 0 || si < 0 || si >= p.total_rows) continue;
+            Li = imin64(Li, p.total_rows - si);
+            const int64_t nt = (Li + BM - 1) / BM;
+            if (flat < before + nt) {
+                req = i;
+                L = Li;
+                start = si;
+                r0 = (flat - before) * BM;
+                break;
+            }
+            before += nt;
+        }
+    }
+    if (req < 0) return;  // the whole CTA leaves together, before any barrier or TMEM use
+    const int nblk = static_cast<int>((imin64(L, r0 + BM) + BN - 1) / BN);
+
+    if ((smem_u32(smem) & 1023u) != 0) {  // the swizzled tiles need a 1024-byte aligned base; refuse rather than compute garbage
+        if (tid == 0) report_status(p.status, 3);
+        return;
+    }
+    if (tid == 0) {
+        mbar_init(bar(Q_FULL), 1);
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(bar(K_FULL + s), 1);
+            mbar_init(bar(V_FULL + s), 1);
+            mbar_init(bar(K_EMPTY + s), 1);
+            mbar_init(bar(V_EMPTY + s), 1);
+            mbar_init(bar(S_FULL + s), 1);
+            mbar_init(bar(S_EMPTY + s), 4);
+        }
+        mbar_init(bar(P_FULL), 4);
+        mbar_init(bar(P_EMPTY), 1);
+        mbar_init(bar(O_FULL), 1);
+        *give_up = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(kTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ================================ TMA producer =================================
+        if (lane == 0) {
+            const int row0 = static_cast<int>(start + r0);
+            mbar_expect_tx(bar(Q_FULL), kQBytes);
+            tma_load_3d(smem_u32(smem + kOffQ), &map_q, 0, h, row0, bar(Q_FULL));
+            tma_load_3d(smem_u32(smem + kOffQ + BM * 128), &map_q, 64, h, row0, bar(Q_FULL));
+            for (int j = 0; j < nblk; ++j) {
+                const int s = j % kStages;
+                const uint32_t ph = static_cast<uint32_t>((j / kStages) & 1);
+                const int krow = static_cast<int>(start + static_cast<int64_t>(j) * BN);
+                if (!mbar_wait(bar(K_EMPTY + s), ph ^ 1u, give_up)) break;
+                mbar_expect_tx(bar(K_FULL + s), kKStage);
+                tma_load_3d(smem_u32(smem + kOffK + s * kKStage), &map_k, 0, h, krow, bar(K_FULL + s));
+                tma_load_3d(smem_u32(smem + kOffK + s * kKStage + BN * 128), &map_k, 64, h, krow, bar(K_FULL + s));
+                if (!mbar_wait(bar(V_EMPTY + s), ph ^ 1u, give_up)) break;
+                mbar_expect_tx(bar(V_FULL + s), kVStage);
+                tma_load_3d(smem_u32(smem + kOffV + s * kVStage), &map_v, 0, h, krow, bar(V_FULL + s));
+                tma_load_3d(smem_u32(smem + kOffV + s * kVStage + BN * 128), &map_v, 64, h, krow, bar(V_FULL + s));
+            }
+        }
+    } else if (warp == 1) {
+        // ================================ MMA issuer ===================================
+        if (lane == 0) {
+            const uint32_t idesc_qk = make_idesc(BM, BN, p.is_bf16, 0);
+            const uint32_t idesc_pv = make_idesc(BM, HD, p.is_bf16, 1);
+            const uint32_t q_addr = smem_u32(smem + kOffQ), p_addr = smem_u32(smem + kOffP);
+            bool ok = mbar_wait(bar(Q_FULL), 0, give_up);
+            auto issue_pv = [&](int i) -> bool {
+                const int s = i % kStages;
+                if (!mbar_wait(bar(P_FULL), static_cast<uint32_t>(i & 1), give_up)) return false;
+                if (!mbar_wait(bar(V_FULL + s), static_cast<uint32_t>((i / kStages) & 1), give_up)) return false;
+                tc_fence_after();
+                const uint32_t v_addr = smem_u32(smem + kOffV + s * kVStage);
+#pragma unroll
+                for (int t = 0; t < BN / 16; ++t) {
+                    // A = P [128 rows x 64 keys], K-major: 16 keys = 32 bytes inside the 128-byte swizzled row
+                    const uint64_t ad = make_desc(p_addr + t * 32, 0, 1024);
+                    // B = V [64 keys x 128 d], MN-major: 16 keys = 16 rows of 128 bytes; the second 64-wide d block is 8 KB further
+                    const uint64_t bd = make_desc(v_addr + t * 16 * 128, BN * 128, 1024);
+                    umma(tmem_base + kColO, ad, bd, idesc_pv, (i > 0 || t > 0) ? 1u : 0u);
+                }
+                umma_commit(bar(P_EMPTY));
+                umma_commit(bar(V_EMPTY + s));
+                umma_commit(bar(O_FULL));
+                return true;
+            };
+            for (int j = 0; ok && j < nblk; ++j) {
+                const int s = j % kStages;
+                const uint32_t ph = static_cast<uint32_t>((j / kStages) & 1);
+                if (!mbar_wait(bar(K_FULL + s), ph, give_up) || !mbar_wait(bar(S_EMPTY + s), ph ^ 1u, give_up)) {
+                    ok = false;
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t k_addr = smem_u32(smem + kOffK + s * kKStage);
+#pragma unroll
+                for (int t = 0; t < HD / 16; ++t) {
+                    // both operands K-major; d block t/4 (64 wide), 16 d = 32 bytes inside the swizzled row
+                    const uint64_t ad = make_desc(q_addr + (t / 4) * (BM * 128) + (t % 4) * 32, 0, 1024);
+                    const uint64_t bd = make_desc(k_addr + (t / 4) * (BN * 128) + (t % 4) * 32, 0, 1024);
+                    umma(tmem_base + kColS0 + s * BN, ad, bd, idesc_qk, t > 0 ? 1u : 0u);
+                }
+                umma_commit(bar(S_FULL + s));
+                umma_commit(bar(K_EMPTY + s));
+                if (j > 0 && !issue_pv(j - 1)) {
+                    ok = false;
+                    break;
+                }
+            }
+            if (ok) issue_pv(nblk - 1);
+        }
+    } else {
+        // ================================ soft-max warps: thread = query row ==========================
+        const int quarter = warp & 3;                 // the TMEM lane quarter this warp may touch
+        const int row = quarter * 32 + lane;          // row inside the tile
+        const int64_t rr = r0 + row;                  // row inside the request
+        const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+        float m_used = -INFINITY, l = 0.f;
+        bool ok = true;
+        for (int j = 0; j < nblk; ++j) {
+            const int s = j % kStages;
+            const uint32_t ph = static_cast<uint32_t>((j / kStages) & 1);
+            if (!warp_wait(bar(S_FULL + s), ph, give_up)) {
+                ok = false;
+                break;
+            }
+            tc_fence_after();
+            uint32_t u0[32], u1[32];
+            tmem_ld32(lane_base + kColS0 + s * BN, u0);
+            tmem_ld32(lane_base + kColS0 + s * BN + 32, u1);
+            tmem_wait_ld();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar(S_EMPTY + s));
+
+            float sc[BN];
+            const int64_t key0 = static_cast<int64_t>(j) * BN;
+            const bool edge = (key0 + BN - 1 > r0) || (key0 + BN > L);  // block touches the diagonal or the request's end
+            float mx = -INFINITY;
+#pragma unroll
+            for (int c = 0; c < BN; ++c) {
+                float v = __uint_as_float(c < 32 ? u0[c] : u1[c - 32]) * p.scale_log2;
+                if (edge) {
+                    const int64_t key = key0 + c;
+                    if (key > rr || key >= L) v = -INFINITY;
+                }
+                sc[c] = v;
+                mx = fmaxf(mx, v);
+            }
+            // Lazy maximum: keep the old reference while the new maximum is within 2^8 of it.
+            const float m_new = fmaxf(m_used, mx);
+            const bool need = (m_new > m_used + 8.0f) || (m_used == -INFINITY && m_new != -INFINITY);
+            if (__any_sync(0xffffffffu, need)) {
+                const float m_next = need ? m_new : m_used;
+                const float alpha = (m_used == -INFINITY) ? 0.f : exp2f(m_used - m_next);
+                if (j > 0) {
+                    if (!warp_wait(bar(O_FULL), static_cast<uint32_t>((j - 1) & 1), give_up)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+#pragma unroll
+                    for (int c4 = 0; c4 < HD / 32; ++c4) {
+                        uint32_t o[32];
+                        tmem_ld32(lane_base + kColO + c4 * 32, o);
+                        tmem_wait_ld();
+#pragma unroll
+                        for (int c = 0; c < 32; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * alpha);
+                        tmem_st32(lane_base + kColO + c4 * 32, o);
+                    }
+                    tmem_wait_st();
+                }
+                l *= alpha;
+                m_used = m_next;
+            }
+            const float m_ref = (m_used == -INFINITY) ? 0.f : m_used;
+            float rs = 0.f;
+#pragma unroll
+            for (int c = 0; c < BN; ++c) {
+                sc[c] = exp2f(sc[c] - m_ref);
+                rs += sc[c];
+            }
+            l += rs;
+            // P_j into shared memory once the previous P has been consumed
+            if (!warp_wait(bar(P_EMPTY), static_cast<uint32_t>((j & 1) ^ 1), give_up)) {
+                ok = false;
+                break;
+            }
+            unsigned char* prow = smem + kOffP + (row >> 3) * 1024 + (row & 7) * 128;
+#pragma unroll
+            for (int ch = 0; ch < BN / 8; ++ch) {
+                uint4 v;
+                v.x = pack2(sc[ch * 8 + 0], sc[ch * 8 + 1], p.is_bf16);
+                v.y = pack2(sc[ch * 8 + 2], sc[ch * 8 + 3], p.is_bf16);
+                v.z = pack2(sc[ch * 8 + 4], sc[ch * 8 + 5], p.is_bf16);
+                v.w = pack2(sc[ch * 8 + 6], sc[ch * 8 + 7], p.is_bf16);
+                *reinterpret_cast<uint4*>(prow + ((ch ^ (row & 7)) << 4)) = v;
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar(P_FULL));
+        }
+        if (ok && warp_wait(bar(O_FULL), static_cast<uint32_t>((nblk - 1) & 1), give_up)) {
+            tc_fence_after();
+            const float inv = l > 0.f ? 1.f / l : 0.f;
+            const bool store = rr < L;
+            unsigned char* dst = static_cast<unsigned char*>(p.out) + ((start + rr) * p.o_s0 + static_cast<int64_t>(h) * p.o_s1) * 2;
+#pragma unroll
+            for (int c4 = 0; c4 < HD / 32; ++c4) {
+                uint32_t o[32];
+                tmem_ld32(lane_base + kColO + c4 * 32, o);
+                tmem_wait_ld();
+                if (store) {
+#pragma unroll
+                    for (int ch = 0; ch < 4; ++ch) {
+                        uint4 v;
+                        v.x = pack2(__uint_as_float(o[ch * 8 + 0]) * inv, __uint_as_float(o[ch * 8 + 1]) * inv, p.is_bf16);
+                        v.y = pack2(__uint_as_float(o[ch * 8 + 2]) * inv, __uint_as_float(o[ch * 8 + 3]) * inv, p.is_bf16);
+                        v.z = pack2(__uint_as_float(o[ch * 8 + 4]) * inv, __uint_as_float(o[ch * 8 + 5]) * inv, p.is_bf16);
+                        v.w = pack2(__uint_as_float(o[ch * 8 + 6]) * inv, __uint_as_float(o[ch * 8 + 7]) * inv, p.is_bf16);
+                        *reinterpret_cast<uint4*>(dst + c4 * 64 + ch * 16) = v;
+                    }
+                }
+            }
+        }
+    }
+
+    // ---- common exit: everybody arrives, TMEM is returned by the warp that took it ----
+    tc_fence_before();
+    __syncthreads();
+    if (*give_up) {
+        if (tid == 0) report_status(p.status, 3);
+        const unsigned long long t_begin = global_ns();
+        while (global_ns() - t_begin < 2000000ull) __nanosleep(1000);  // let copies/MMAs still in flight finish
+        __syncthreads();
+    }
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                              const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeFn encode_fn() {
+    static EncodeFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess && qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeFn>(ptr);
+    });
+    return fn;
+}
+
+// 3-D view [D, H, rows] of a packed [rows, H, D] tensor; box = 64 elements x 1 head x `box_rows` rows, 128-byte swizzle.
+bool make_map(CUtensorMap* map, const void* base, int64_t rows, int H, int64_t s0, int64_t s1, int box_rows, bool bf16) {
+    EncodeFn fn = encode_fn();
+    if (!fn) return false;
+    const cuuint64_t dims[3] = {static_cast<cuuint64_t>(HD), static_cast<cuuint64_t>(H), static_cast<cuuint64_t>(rows)};
+    const cuuint64_t strides[2] = {static_cast<cuuint64_t>(s1) * 2, static_cast<cuuint64_t>(s0) * 2};
+    const cuuint32_t box[3] = {64, 1, static_cast<cuuint32_t>(box_rows)};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = fn(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS;
+}
+
+}  // namespace
+
+void launch_prefill_tc(const PrefillArgs& a, int /*sm_count*/, int max_smem, cudaStream_t st, bool* taken) {
+    *taken = false;
+    static const bool disabled = [] {
+        const char* v = std::getenv("DIOPI_B200_PREFILL_SIMT");
+        return v && v[0] && v[0] != '0';
+    }();
+    if (disabled) return;
+    if (a.dt != Dt::F16 && a.dt != Dt::BF16) return;
+    if (a.D != HD || a.H > 65535 || kSmemBytes > max_smem) return;
+    if (a.total_rows >= (1ll << 31) - BM) return;
+    auto ok = [](const void* p, int64_t s0, int64_t s1) {
+        return reinterpret_cast<uintptr_t>(p) % 16 == 0 && (s0 * 2) % 16 == 0 && (s1 * 2) % 16 == 0 && s0 > 0 && s1 > 0;
+    };
+    if (!ok(a.q, a.q_s0, a.q_s1) || !ok(a.kmat, a.k_s0, a.k_s1) || !ok(a.vmat, a.v_s0, a.v_s1) || !ok(a.out, a.o_s0, a.o_s1)) return;
+    const bool bf16 = a.dt == Dt::BF16;
+    CUtensorMap mq, mk, mv;
+    if (!make_map(&mq, a.q, a.total_rows, a.H, a.q_s0, a.q_s1, BM, bf16)) return;
+    if (!make_map(&mk, a.kmat, a.total_rows, a.H, a.k_s0, a.k_s1, BN, bf16)) return;
+    if (!make_map(&mv, a.vmat, a.total_rows, a.H, a.v_s0, a.v_s1, BN, bf16)) return;
+
+    TcParams p;
+    p.b_start = a.b_start;
+    p.b_len = a.b_len;
+    p.B = a.B;
+    p.H = a.H;
+    p.total_rows = a.total_rows;
+    p.out = a.out;
+    p.o_s0 = a.o_s0;
+    p.o_s1 = a.o_s1;
+    p.n_tiles_max = static_cast<int>(a.total_rows / BM + a.B);
+    p.scale_log2 = kLog2e / sqrtf(static_cast<float>(HD));
+    p.is_bf16 = bf16 ? 1 : 0;
+    p.status = nullptr;
+    cudaFuncSetAttribute(prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    dim3 grid(p.n_tiles_max, a.H, 1);
+    prefill_tc_kernel<<<grid, kThreads, kSmemBytes, st>>>(mq, mk, mv, p);
+    *taken = true;
+}
 
 }  // namespace k
 }  // namespace b200
