@@ -193,18 +193,34 @@ def run_b200(args):
         return
 
     # ---- end to end: the same step driven from pinned host buffers ----
-    host_in = {k: getattr(w, k).cpu().pin_memory() for k in ("q", "k_new", "v_new", "dest_loc", "b_loc", "b_start_loc", "b_seq_len")}
-    dev_in = {k: torch.empty_like(getattr(w, k)) for k in host_in}
+    # The engine stages the step's inputs (q, new K/V rows, slot tables, lengths) in ONE pinned host buffer and moves
+    # them with one H2D copy; tensor handles of the persistent device buffers are made once, as a framework would.
+    from diopi_b200.runtime import Tensor
+    names = ("q", "k_new", "v_new", "dest_loc", "b_loc", "b_start_loc", "b_seq_len")
+    offs, total_in = {}, 0
+    for k in names:
+        t = getattr(w, k)
+        offs[k] = total_in
+        total_in += (t.numel() * t.element_size() + 255) // 256 * 256
+    host_buf = torch.empty(total_in, dtype=torch.uint8).pin_memory()
+    dev_buf = torch.empty(total_in, dtype=torch.uint8, device="cuda")
+    dev_in = {}
+    for k in names:
+        t = getattr(w, k)
+        nb = t.numel() * t.element_size()
+        host_buf[offs[k]:offs[k] + nb].view(t.dtype).view(t.shape).copy_(t.cpu())
+        dev_in[k] = dev_buf[offs[k]:offs[k] + nb].view(t.dtype).view(t.shape)
     host_out = torch.empty(out.shape, dtype=out.dtype).pin_memory()
-    h2d = sum(t.numel() * t.element_size() for t in host_in.values())
+    h2d = sum(getattr(w, k).numel() * getattr(w, k).element_size() for k in names)
     d2h = host_out.numel() * host_out.element_size()
+    hd = {k: Tensor(v) for k, v in dev_in.items()}
+    h_kpool, h_vpool, h_out = Tensor(w.k_pool), Tensor(w.v_pool), Tensor(out)
 
     def e2e_step():
-        for k, t in host_in.items():
-            dev_in[k].copy_(t, non_blocking=True)
-        F.destindex_copy_kv(dev_in["k_new"], dev_in["dest_loc"], w.k_pool, ctx=ctx)
-        F.destindex_copy_kv(dev_in["v_new"], dev_in["dest_loc"], w.v_pool, ctx=ctx)
-        F.token_decode_attention(dev_in["q"], w.k_pool, w.v_pool, out, dev_in["b_loc"], dev_in["b_start_loc"], dev_in["b_seq_len"], w.max_input_len, ctx=ctx)
+        dev_buf.copy_(host_buf, non_blocking=True)
+        F.destindex_copy_kv(hd["k_new"], hd["dest_loc"], h_kpool, ctx=ctx)
+        F.destindex_copy_kv(hd["v_new"], hd["dest_loc"], h_vpool, ctx=ctx)
+        F.token_decode_attention(hd["q"], h_kpool, h_vpool, h_out, hd["b_loc"], hd["b_start_loc"], hd["b_seq_len"], w.max_input_len, ctx=ctx)
         host_out.copy_(out, non_blocking=True)
         ctx.release()
         torch.cuda.synchronize()  # the caller reads the result

@@ -19,13 +19,17 @@ struct Offsets {
     int64_t x, o, c, s;
 };
 
-__device__ __forceinline__ Offsets lead_offsets(const RopeArgs& a, int64_t lead) {
+// IDX = uint32_t when every extent and the element count fit 32 bits (the usual case): 32-bit
+// division is several times cheaper than 64-bit, and this chain is most of the kernel's arithmetic.
+template <typename IDX>
+__device__ __forceinline__ Offsets lead_offsets(const RopeArgs& a, IDX lead) {
     Offsets r{0, 0, 0, 0};
 #pragma unroll
     for (int d = kRopeMaxDims - 1; d >= 0; --d) {
         if (d < a.nd) {
-            const int64_t q = lead / a.size[d];
-            const int64_t i = lead - q * a.size[d];
+            const IDX sz = static_cast<IDX>(a.size[d]);
+            const IDX q = lead / sz;
+            const int64_t i = static_cast<int64_t>(lead - q * sz);
             lead = q;
             r.x += i * a.xs[d];
             r.o += i * a.os[d];
@@ -48,14 +52,15 @@ __device__ __forceinline__ void rotate(float x1, float x2, float c, float s, boo
 }
 
 // One thread per 16-byte vector of x1 (and the matching vector of x2). Last dims dense and aligned.
-template <typename T>
+template <typename T, typename IDX>
 __global__ void __launch_bounds__(256) rope_vec_kernel(RopeArgs a, int vec_per_half, int64_t total_vec) {
     constexpr int N = Vec16<T>::N;
-    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
-    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total_vec; i += stride) {
-        const int64_t lead = i / vec_per_half;
-        const int v = static_cast<int>(i - lead * vec_per_half);
-        const Offsets of = lead_offsets(a, lead);
+    const IDX stride = static_cast<IDX>(gridDim.x) * blockDim.x;
+    const IDX total = static_cast<IDX>(total_vec);
+    for (IDX i = static_cast<IDX>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+        const IDX lead = i / static_cast<IDX>(vec_per_half);
+        const int v = static_cast<int>(i - lead * static_cast<IDX>(vec_per_half));
+        const Offsets of = lead_offsets<IDX>(a, lead);
         const T* x = static_cast<const T*>(a.x) + of.x;
         T* o = static_cast<T*>(a.out) + of.o;
         const uint4 r1 = __ldcs(reinterpret_cast<const uint4*>(x) + v);
@@ -87,7 +92,7 @@ __global__ void __launch_bounds__(256) rope_scalar_kernel(RopeArgs a, int64_t to
     for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
         const int64_t lead = i / a.half;
         const int64_t j = i - lead * a.half;
-        const Offsets of = lead_offsets(a, lead);
+        const Offsets of = lead_offsets<int64_t>(a, lead);
         const T* x = static_cast<const T*>(a.x) + of.x;
         T* o = static_cast<T*>(a.out) + of.o;
         const float c = Io<T>::ld(static_cast<const T*>(a.cos) + of.c + j * a.c_ls);
@@ -104,7 +109,7 @@ __global__ void __launch_bounds__(256) rope_scalar_f64_kernel(RopeArgs a, int64_
     for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
         const int64_t lead = i / a.half;
         const int64_t j = i - lead * a.half;
-        const Offsets of = lead_offsets(a, lead);
+        const Offsets of = lead_offsets<int64_t>(a, lead);
         const double* x = static_cast<const double*>(a.x) + of.x;
         double* o = static_cast<double*>(a.out) + of.o;
         const double c = static_cast<const double*>(a.cos)[of.c + j * a.c_ls];
@@ -128,7 +133,10 @@ void launch_typed(const RopeArgs& a, cudaStream_t st) {
         const int vph = static_cast<int>(a.half / N);
         const int64_t total = a.n_lead * vph;
         const unsigned blocks = static_cast<unsigned>(std::min<int64_t>((total + 255) / 256, 148ll * 64));
-        rope_vec_kernel<T><<<blocks, 256, 0, st>>>(a, vph, total);
+        if (total < (1ll << 31))
+            rope_vec_kernel<T, uint32_t><<<blocks, 256, 0, st>>>(a, vph, total);
+        else
+            rope_vec_kernel<T, int64_t><<<blocks, 256, 0, st>>>(a, vph, total);
     } else {
         const int64_t total = a.n_lead * a.half;
         const unsigned blocks = static_cast<unsigned>(std::min<int64_t>((total + 255) / 256, 148ll * 64));

@@ -43,7 +43,7 @@ constexpr int kConsumerThreads = kConsumerWarps * 32;
 constexpr int kThreads = kConsumerThreads + 32;  // + one producer warp
 constexpr int kMaxB = 2048;                      // request prefix sums live in shared memory
 constexpr int kMaxG = 32;                        // token groups per CTA
-constexpr int kMaxStages = 8;
+constexpr int kMaxStages = 32;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // a wait longer than this is given up
 
@@ -56,11 +56,13 @@ struct SplitPlan {
     int TT;           // tokens per stage = G * tpg
     int tpg;          // tokens per group per stage
     int nmat;         // matrices streamed: 2 when fused
-    int stage_bytes;  // TT * C * 16 * nmat
-    int nstages;
+    int stage_bytes;  // one ring slot: ups * G tokens, K rows then V rows = ups * G * C * 16 * nmat bytes
+    int nstages;      // ring slots
     int n_cta;        // CTAs along the flattened token axis
     int smem_bytes;
     int off_bars, off_pre, off_red, off_flag;
+    int ups;           // token groups per ring slot (1, 2 or 4): a tile of TPG groups spans TPG / ups ring slots
+    int pdl;           // launch the merge kernel as a programmatic dependent
 };
 
 // ---------------------------------------------------------------------------
@@ -179,6 +181,10 @@ __global__ void __launch_bounds__(kThreads, 1) decode_split_kernel(const DecodeA
     float* red = reinterpret_cast<float*>(smem + p.off_red);
     volatile int* give_up = reinterpret_cast<volatile int*>(smem + p.off_flag);
 
+    // Let the merge kernel (launched with programmatic stream serialization) become resident early; it
+    // does its own set-up and then blocks in griddepcontrol.wait until this whole grid has finished.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
     const int tid = threadIdx.x;
     const int warp = tid >> 5;
     const int lane = tid & 31;
@@ -223,20 +229,25 @@ __global__ void __launch_bounds__(kThreads, 1) decode_split_kernel(const DecodeA
     const int t1 = static_cast<int>(static_cast<int64_t>(total) * (cta + 1) / p.n_cta);
     const int TT = p.TT;
 
+    // A tile = TT = G * TPG tokens = TPG token groups. It occupies TPG / ups consecutive ring slots of
+    // ups * G tokens each (K rows, then V rows). ups = TPG (one 64 KB slot per tile) measured fastest: every
+    // extra mbarrier round trip per token costs more than the finer refill granularity wins.
     if (warp == kConsumerWarps) {
         // =========================== producer warp ===============================
         const char* kbase = kHasK ? static_cast<const char*>(a.kmat) + static_cast<int64_t>(hg0) * a.k_s1 * sizeof(T) : nullptr;
         const char* vbase = kHasV ? static_cast<const char*>(a.vmat) + static_cast<int64_t>(hg0) * a.v_s1 * sizeof(T) : nullptr;
         const int64_t k_row = a.k_s0 * static_cast<int64_t>(sizeof(T));
         const int64_t v_row = a.v_s0 * static_cast<int64_t>(sizeof(T));
-        const uint32_t v_off = kFused ? static_cast<uint32_t>(TT) * static_cast<uint32_t>(p.C) * 16u : 0u;
+        const int tps = p.ups * p.G;      // tokens per ring slot
+        const int spt = TPG / p.ups;      // ring slots per tile
+        const uint32_t v_off = kFused ? static_cast<uint32_t>(tps) * static_cast<uint32_t>(p.C) * 16u : 0u;
 
         StageWalk walk;
         walk.init(pre, a.B, t0, t1);
         int req, j0, cnt;
         bool last;
         bool have = walk.next(TT, req, j0, cnt, last);
-        int64_t slot[TPG];
+        int64_t slot[TPG];  // tokens lane, lane+32, ... of the tile
         auto fetch_slots = [&](int r, int j, int n, int64_t (&out)[TPG]) {
             const int L = pre[r + 1] - pre[r];
             const int64_t col0 = static_cast<int64_t>(a.max_input_len) - L + j;
@@ -245,42 +256,61 @@ __global__ void __launch_bounds__(kThreads, 1) decode_split_kernel(const DecodeA
                 const int t = lane + 32 * u;
                 out[u] = 0;
                 if (t < n) {
-                    int64_t s = load_index(a.b_loc, r, col0 + t);
-                    if (s < 0 || s >= a.slots) {
+                    int64_t sl = load_index(a.b_loc, r, col0 + t);
+                    if (sl < 0 || sl >= a.slots) {
                         report_status(a.status, 1);
-                        s = 0;  // keep the byte count of the stage intact
+                        sl = 0;  // keep the byte count of the slot intact
                     }
-                    out[u] = s;
+                    out[u] = sl;
                 }
             }
         };
         if (have) fetch_slots(req, j0, cnt, slot);
-        int n = 0;
+        int ring = 0;          // ring slot of the tile's first token group
+        uint32_t ring_phase = 0;
         while (have) {
             const int cur_cnt = cnt;
             int64_t cur_slot[TPG];
 #pragma unroll
             for (int u = 0; u < TPG; ++u) cur_slot[u] = slot[u];
-            // Look up the next stage's slots before blocking, so that load overlaps the wait.
+            // Look up the next tile's pool slots before blocking, so that load overlaps the waits.
             have = walk.next(TT, req, j0, cnt, last);
             if (have) fetch_slots(req, j0, cnt, slot);
-
-            const int s = n % p.nstages;
-            const uint32_t parity = static_cast<uint32_t>((n / p.nstages) & 1);
-            if (!mbar_wait(smem_u32(&bars[p.nstages + s]), parity ^ 1u, give_up)) break;
-            const uint32_t full = smem_u32(&bars[s]);
-            if (lane == 0) mbar_arrive_expect_tx(full, static_cast<uint32_t>(cur_cnt) * row_bytes * static_cast<uint32_t>(p.nmat));
-            __syncwarp();
-            const uint32_t stage = smem_u32(smem + static_cast<size_t>(s) * p.stage_bytes);
+            // Lane u < spt owns ring slot u of this tile: waits until it is free and announces its bytes.
+            bool mine_ok = true;
+            if (lane < spt) {
+                int s = ring + lane;
+                uint32_t parity = ring_phase;
+                if (s >= p.nstages) {
+                    s -= p.nstages;
+                    parity ^= 1u;
+                }
+                mine_ok = mbar_wait(smem_u32(&bars[p.nstages + s]), parity ^ 1u, give_up);
+                if (mine_ok) {
+                    const int here = min(max(cur_cnt - lane * tps, 0), tps);  // tokens of the tile that fall into this ring slot
+                    mbar_arrive_expect_tx(smem_u32(&bars[s]), static_cast<uint32_t>(here) * row_bytes * static_cast<uint32_t>(p.nmat));
+                }
+            }
+            if (!__all_sync(0xffffffffu, mine_ok ? 1 : 0)) break;
+            // Then every lane issues the copies of its tokens (token t lives in ring slot t / tps at position t % tps).
 #pragma unroll
             for (int u = 0; u < TPG; ++u) {
                 const int t = lane + 32 * u;
                 if (t < cur_cnt) {
-                    if (kHasK) bulk_g2s(stage + static_cast<uint32_t>(t) * row_bytes, kbase + cur_slot[u] * k_row, row_bytes, full);
-                    if (kHasV) bulk_g2s(stage + v_off + static_cast<uint32_t>(t) * row_bytes, vbase + cur_slot[u] * v_row, row_bytes, full);
+                    const int su = t / tps;
+                    int s = ring + su;
+                    if (s >= p.nstages) s -= p.nstages;
+                    const uint32_t full = smem_u32(&bars[s]);
+                    const uint32_t dst = smem_u32(smem + static_cast<size_t>(s) * p.stage_bytes) + static_cast<uint32_t>(t - su * tps) * row_bytes;
+                    if (kHasK) bulk_g2s(dst, kbase + cur_slot[u] * k_row, row_bytes, full);
+                    if (kHasV) bulk_g2s(dst + v_off, vbase + cur_slot[u] * v_row, row_bytes, full);
                 }
             }
-            ++n;
+            ring += spt;
+            if (ring >= p.nstages) {
+                ring -= p.nstages;
+                ring_phase ^= 1u;
+            }
         }
     } else {
         // =========================== consumer warps ==============================
@@ -295,7 +325,10 @@ __global__ void __launch_bounds__(kThreads, 1) decode_split_kernel(const DecodeA
         const int hl = c / LPH;    // head within this CTA's group
         const int lih = c % LPH;   // lane within the head
         const int h = hg0 + hl;
-        const uint32_t v_off = kFused ? static_cast<uint32_t>(TT) * static_cast<uint32_t>(p.C) * 16u : 0u;
+        const int ups_mask = p.ups - 1;   // ups is 1, 2 or 4
+        const uint32_t v_off = kFused ? static_cast<uint32_t>(p.ups * p.G) * static_cast<uint32_t>(p.C) * 16u : 0u;
+        const uint32_t my_off = static_cast<uint32_t>(g) * row_bytes + static_cast<uint32_t>(c) * 16u;  // my 16 bytes of token group 0 of a ring slot
+        const uint32_t group_step = static_cast<uint32_t>(p.G) * row_bytes;                              // next token group inside the slot
         const float sqrt_d = sqrtf(static_cast<float>(a.D));
         const float qscale = kLog2e / sqrt_d;  // softmax runs in base 2
 
@@ -310,8 +343,10 @@ __global__ void __launch_bounds__(kThreads, 1) decode_split_kernel(const DecodeA
         walk.init(pre, a.B, t0, t1);
         int req, j0, cnt;
         bool last;
-        int n = 0;
-        while (walk.next(TT, req, j0, cnt, last)) {
+        int ring = 0;          // next ring slot to consume (kept incrementally: no division in the loop)
+        uint32_t ring_phase = 0;
+        bool ok = true;
+        while (ok && walk.next(TT, req, j0, cnt, last)) {
             if (req != cur_req) {
                 cur_req = req;
                 m = -INFINITY;
@@ -331,8 +366,6 @@ __global__ void __launch_bounds__(kThreads, 1) decode_split_kernel(const DecodeA
                 }
                 if (!kFused) att_col0 = load_index(a.b_start, req);
             }
-            const int s = n % p.nstages;
-            const uint32_t parity = static_cast<uint32_t>((n / p.nstages) & 1);
 
             float sc[TPG];
             if (!kHasK) {
@@ -346,16 +379,30 @@ __global__ void __launch_bounds__(kThreads, 1) decode_split_kernel(const DecodeA
                         sc[u] = Cvt<T>::to_f(static_cast<const T*>(a.att)[static_cast<int64_t>(h) * a.att_s0 + col * a.att_s1]) * kLog2e;
                 }
             }
-            if (!mbar_wait(smem_u32(&bars[s]), parity, give_up)) break;
-            const unsigned char* stage = smem + static_cast<size_t>(s) * p.stage_bytes;
-
-            if (kHasK) {
+            // token group u sits in ring slot u / ups; a slot is waited for right before its first use
+            const unsigned char* slot_ptr[TPG];
+            uint32_t empty_bar[TPG];
 #pragma unroll
-                for (int u = 0; u < TPG; ++u) {
+            for (int u = 0; u < TPG; ++u) {
+                if ((u & ups_mask) == 0) {
+                    const int s = ring;
+                    const uint32_t parity = ring_phase;
+                    if (++ring == p.nstages) {
+                        ring = 0;
+                        ring_phase ^= 1u;
+                    }
+                    slot_ptr[u] = smem + static_cast<size_t>(s) * p.stage_bytes + my_off;
+                    empty_bar[u] = smem_u32(&bars[p.nstages + s]);
+                    if (ok && !mbar_wait(smem_u32(&bars[s]), parity, give_up)) ok = false;
+                } else {
+                    slot_ptr[u] = slot_ptr[u - 1] + group_step;
+                    empty_bar[u] = empty_bar[u - 1];
+                }
+                if (kHasK) {
                     const int t = g + u * p.G;
                     float part = 0.f;
-                    if (t < cnt) {
-                        const uint4 kv = *reinterpret_cast<const uint4*>(stage + static_cast<uint32_t>(t) * row_bytes + c * 16);
+                    if (ok && t < cnt) {
+                        const uint4 kv = *reinterpret_cast<const uint4*>(slot_ptr[u]);
                         float f[EPC];
                         unpack16<T>(kv, f);
 #pragma unroll
@@ -366,6 +413,9 @@ __global__ void __launch_bounds__(kThreads, 1) decode_split_kernel(const DecodeA
                     sc[u] = (t < cnt) ? part : -INFINITY;
                 }
             }
+            ok = __all_sync(0xffffffffu, ok ? 1 : 0) != 0;  // the whole warp leaves together
+            if (!ok) break;
+
             if (MODE == static_cast<int>(DecodeMode::QK)) {
                 if (real && lih == 0) {
 #pragma unroll
@@ -375,6 +425,12 @@ __global__ void __launch_bounds__(kThreads, 1) decode_split_kernel(const DecodeA
                         if (t < cnt && col >= 0 && col < a.att_cols)
                             static_cast<T*>(a.att)[static_cast<int64_t>(h) * a.att_s0 + col * a.att_s1] = Cvt<T>::from_f(sc[u] / sqrt_d);
                     }
+                }
+                __syncwarp();
+                if (lane == 0) {
+#pragma unroll
+                    for (int u = 0; u < TPG; ++u)
+                        if ((u & ups_mask) == ups_mask) mbar_arrive(empty_bar[u]);
                 }
             } else {
                 float m_new = m;
@@ -391,18 +447,20 @@ __global__ void __launch_bounds__(kThreads, 1) decode_split_kernel(const DecodeA
                     if (t < cnt) {
                         const float pr = exp2f(sc[u] - m_ref);
                         l += pr;
-                        const uint4 vv = *reinterpret_cast<const uint4*>(stage + v_off + static_cast<uint32_t>(t) * row_bytes + c * 16);
+                        const uint4 vv = *reinterpret_cast<const uint4*>(slot_ptr[u] + v_off);
                         float f[EPC];
                         unpack16<T>(vv, f);
 #pragma unroll
                         for (int e = 0; e < EPC; ++e) acc[e] = fmaf(pr, f[e], acc[e]);
                     }
+                    // last token group of a ring slot: the slot is done for the whole warp, hand it back
+                    if ((u & ups_mask) == ups_mask) {
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(empty_bar[u]);
+                    }
                 }
                 m = m_new;
             }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&bars[p.nstages + s]));
-            ++n;
 
             if (last && kHasV) {
                 // The request's part in this CTA is done: merge the token groups, then store the partial.
@@ -415,7 +473,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_split_kernel(const DecodeA
                     }
                     __syncwarp();
                     if (lane == 0) mbar_arrive(smem_u32(&bars[2 * p.nstages]));
-                    if (!mbar_wait(smem_u32(&bars[2 * p.nstages]), red_phase, give_up)) break;
+                    if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&bars[2 * p.nstages]), red_phase, give_up) ? 1 : 0)) break;
                     if (real && g == 0) {
                         float M = m;
                         for (int gg = 1; gg < p.G; ++gg) M = fmaxf(M, red[(gg * p.C + c) * (EPC + 2)]);
@@ -435,7 +493,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_split_kernel(const DecodeA
                     }
                     __syncwarp();
                     if (lane == 0) mbar_arrive(smem_u32(&bars[2 * p.nstages + 1]));
-                    if (!mbar_wait(smem_u32(&bars[2 * p.nstages + 1]), red_phase, give_up)) break;
+                    if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&bars[2 * p.nstages + 1]), red_phase, give_up) ? 1 : 0)) break;
                     red_phase ^= 1u;
                 }
                 if (real && g == 0) {
@@ -485,6 +543,9 @@ __global__ void __launch_bounds__(128) decode_combine_kernel(const DecodeArgs a,
     before = s_part[0][0] + s_part[1][0] + s_part[2][0] + s_part[3][0];
     all = s_part[0][1] + s_part[1][1] + s_part[2][1] + s_part[3][1];
 
+    // Everything above read only the caller's inputs. The partials are written by the split kernel, which may
+    // still be running when this kernel was launched early: wait for it to finish (no-op for a plain launch).
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const int h = blockIdx.y * 4 + warp;
     if (h >= a.H) return;
     const int L = request_len(a, i);
@@ -667,11 +728,19 @@ bool make_split_plan(const DecodeArgs& a, int sm_count, int max_smem, SplitPlan&
     p.n_hg = (a.H + p.hg - 1) / p.hg;
     p.C = p.hg * lph;
     p.G = std::min(kConsumerThreads / p.C, kMaxG);
-    p.tpg = (a.mode == DecodeMode::FUSED) ? env_int("DIOPI_B200_DECODE_TPG", 4) : 4;
-    if (p.tpg != 2 && p.tpg != 4) p.tpg = 4;
+    if (a.mode == DecodeMode::FUSED) {
+        p.tpg = env_int("DIOPI_B200_DECODE_TPG", 4);
+        if (p.tpg != 2 && p.tpg != 4) p.tpg = 4;
+    } else {
+        p.tpg = 8;
+    }
     p.TT = p.G * p.tpg;
     p.nmat = (has_k && has_v) ? 2 : 1;
-    p.stage_bytes = p.TT * p.C * 16 * p.nmat;
+    p.pdl = env_int("DIOPI_B200_DECODE_PDL", 1);
+    p.ups = env_int("DIOPI_B200_DECODE_UPS", p.tpg);
+    if (p.ups != 1 && p.ups != 2 && p.ups != 4 && p.ups != 8) p.ups = p.tpg;
+    if (p.ups > p.tpg) p.ups = p.tpg;
+    p.stage_bytes = p.ups * p.G * p.C * 16 * p.nmat;
     const int ctas_per_sm = std::max(1, std::min(2, env_int("DIOPI_B200_DECODE_CTAS_PER_SM", 1)));
 
     const int red_bytes = (p.G > 1 && has_v) ? kConsumerThreads * (16 / e + 2) * 4 : 0;
@@ -695,7 +764,7 @@ bool make_split_plan(const DecodeArgs& a, int sm_count, int max_smem, SplitPlan&
     }
     int nst = (budget - fixed) / p.stage_bytes;
     nst = std::min(nst, std::min(kMaxStages, std::max(2, env_int("DIOPI_B200_DECODE_STAGES", kMaxStages))));
-    if (nst < 2) return false;
+    if (nst < p.tpg / p.ups + 1) return false;  // a tile holds tpg/ups ring slots at once; one more must be in flight
     p.nstages = nst;
     off = nst * p.stage_bytes;
     p.off_bars = take((2 * kMaxStages + 2) * 8, 8);
@@ -716,18 +785,32 @@ bool make_split_plan(const DecodeArgs& a, int sm_count, int max_smem, SplitPlan&
 template <typename T, int LPH, int MODE>
 void launch_split_t(const DecodeArgs& a, const SplitPlan& p, float* ws_acc, float* ws_ml, cudaStream_t st) {
     dim3 grid(p.n_cta, p.n_hg);
-    if (p.tpg == 2 && MODE == static_cast<int>(DecodeMode::FUSED)) {
-        auto kern = decode_split_kernel<T, LPH, MODE, (MODE == static_cast<int>(DecodeMode::FUSED) ? 2 : 4)>;
+    constexpr bool fused = MODE == static_cast<int>(DecodeMode::FUSED);
+    // fused: 4 token groups per tile (2 with DIOPI_B200_DECODE_TPG=2); one matrix only: 8, so that a tile is 64 KB either way
+    if (fused && p.tpg == 2) {
+        auto kern = decode_split_kernel<T, LPH, MODE, (fused ? 2 : 8)>;
         cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, p.smem_bytes);
         kern<<<grid, kThreads, p.smem_bytes, st>>>(a, p, ws_acc, ws_ml);
     } else {
-        auto kern = decode_split_kernel<T, LPH, MODE, 4>;
+        auto kern = decode_split_kernel<T, LPH, MODE, (fused ? 4 : 8)>;
         cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, p.smem_bytes);
         kern<<<grid, kThreads, p.smem_bytes, st>>>(a, p, ws_acc, ws_ml);
     }
     if (MODE != static_cast<int>(DecodeMode::QK)) {
-        dim3 cgrid(a.B, (a.H + 3) / 4);
-        decode_combine_kernel<T><<<cgrid, 128, 0, st>>>(a, p.n_cta, ws_acc, ws_ml);
+        // Programmatic dependent launch: the merge kernel's launch latency and set-up overlap the split kernel.
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(a.B, (a.H + 3) / 4);
+        cfg.blockDim = dim3(128);
+        cfg.dynamicSmemBytes = 0;
+        cfg.stream = st;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = p.pdl ? 1 : 0;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        const float* acc_c = ws_acc;
+        const float* ml_c = ws_ml;
+        cudaLaunchKernelEx(&cfg, decode_combine_kernel<T>, a, p.n_cta, acc_c, ml_c);
     }
 }
 

@@ -1,0 +1,110 @@
+"""Per-op micro-benchmark through the C ABI: `python -m diopi_b200.opbench --op <name> [--size full|small]`.
+
+Times one op of the path on its benchmark config with CUDA events (L2 flushed between iterations with a
+512 MB write for the ops whose working set is near the L2 size) and prints one JSON line with the time, the
+algorithmic bytes or FLOPs and the achieved rate against the measured peak. bench.py covers the decode step
+(the headline metric); this covers the other ops and gives profiler captures a small, committed command.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import sys
+from pathlib import Path
+
+import torch
+
+from . import functions as F
+from . import workloads
+from .runtime import Context
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return float(d["hbm_gbs"]), float(d["bf16_tflops"]), float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), "measured"
+    return 6650.0, 1590.0, 1400.0, "fallback"
+
+
+def time_op(fn, iters, warmup, flush):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(iters):
+        if flush is not None:
+            flush.zero_()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        torch.cuda.synchronize()
+        times.append(a.elapsed_time(b))
+    times.sort()
+    return times[len(times) // 2], times[0]
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--op", required=True, choices=["prefill", "rms_norm", "rotary", "penalty", "copy_kv", "qk", "pv", "decode"])
+    ap.add_argument("--size", default="full", choices=["full", "small"])
+    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    args = ap.parse_args()
+    hbm, tf_burst, tf_sust, kind = peaks()
+    ctx = Context()
+    flush = torch.empty(512 << 20, dtype=torch.uint8, device="cuda")
+    rec = {"op": args.op, "size": args.size, "peak_source": kind}
+
+    if args.op == "prefill":
+        pf = workloads.prefill() if args.size == "full" else workloads.prefill(B=4, lo=512, hi=2048)
+        out = torch.empty_like(pf["q"])
+        med, best = time_op(lambda: F.context_attention(pf["q"], pf["k"], pf["v"], out, pf["b_start_loc"], pf["b_seq_len"], pf["max_input_len"], ctx=ctx),
+                            args.iters, args.warmup, None)
+        tf = pf["flops"] / med / 1e9
+        rec.update(ms=med, ms_best=best, flops=pf["flops"], tflops=tf, frac_of_burst_peak=tf / tf_burst, frac_of_sustained_peak=tf / tf_sust,
+                   lens=pf["lens"].tolist(), unit="TFLOP/s (causal-only FLOPs, fp16)")
+    elif args.op in ("rms_norm", "rotary"):
+        tokens = 8192 if args.size == "full" else 1024
+        p = workloads.prenorm(tokens=tokens)
+        if args.op == "rms_norm":
+            x = p["x"]
+            nbytes = 2 * x.numel() * 2 + tokens * 4 + 4096 * 2
+            med, best = time_op(lambda: F.rms_norm(x, (4096,), p["weight"], None, p["eps"], ctx=ctx), args.iters, args.warmup, flush)
+        else:
+            x = p["k_in"].view(tokens, p["heads"], p["head_dim"])
+            out = torch.empty_like(x)
+            nbytes = 2 * x.numel() * 2 + 2 * p["cos"].numel() * 2
+            med, best = time_op(lambda: F.rotary_emb(x, p["cos"], p["sin"], False, False, out=out, ctx=ctx), args.iters, args.warmup, flush)
+        rec.update(ms=med, ms_best=best, bytes=nbytes, gbs=nbytes / med / 1e6, frac_of_peak=nbytes / med / 1e6 / hbm, unit="GB/s")
+    elif args.op == "penalty":
+        p = workloads.penalty()
+        med, best = time_op(lambda: F.apply_penalty(p["logits"], p["presence"], p["frequency"], p["ids"], p["counts"], p["cum"], p["max_len"], ctx=ctx),
+                            args.iters, args.warmup, flush)
+        E = int(p["ids"].numel())
+        rec.update(ms=med, ms_best=best, entries=E, bytes=E * (2 * 4 + 2 * 4) + 2 * 128 * 4 + 129 * 4, sector_bytes=E * 2 * 32, unit="ms (latency-bound)")
+    else:
+        w = workloads.decode("cfg2" if args.size == "full" else "cfg2s")
+        out = torch.empty_like(w.q)
+        att = torch.zeros(w.q.shape[1], w.sum_len, dtype=w.q.dtype, device="cuda")
+        fns = {
+            "copy_kv": (lambda: F.destindex_copy_kv(w.k_new, w.dest_loc, w.k_pool, ctx=ctx), w.copy_bytes() // 2),
+            "qk": (lambda: F.token_attention(w.q, w.k_pool, att, w.b_loc, w.b_start_loc, w.b_seq_len, w.max_input_len, ctx=ctx), w.fused_bytes() // 2),
+            "pv": (lambda: F.token_softmax_reducev(att, w.v_pool, out, w.b_loc, w.b_start_loc, w.b_seq_len, w.max_input_len, 0, ctx=ctx), w.fused_bytes() // 2),
+            "decode": (lambda: F.token_decode_attention(w.q, w.k_pool, w.v_pool, out, w.b_loc, w.b_start_loc, w.b_seq_len, w.max_input_len, ctx=ctx), w.fused_bytes()),
+        }
+        fn, nbytes = fns[args.op]
+
+        def run():
+            fn()
+            ctx.release()
+        med, best = time_op(run, args.iters, args.warmup, flush if args.op == "copy_kv" else None)
+        rec.update(ms=med, ms_best=best, bytes=nbytes, gbs=nbytes / med / 1e6, frac_of_peak=nbytes / med / 1e6 / hbm, unit="GB/s", sum_len=w.sum_len)
+    print(json.dumps(rec), flush=True)
+
+
+if __name__ == "__main__":
+    sys.exit(main())
