@@ -178,6 +178,13 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
+// 2^x by the special-function unit alone (ex2.approx.ftz): -inf gives 0, no range fix-up code around it.
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 __device__ __forceinline__ uint32_t pack2(float a, float b, int bf16) {
     if (bf16) {
         __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
@@ -348,26 +355,36 @@ __global__ void __launch_bounds__(kThreads, 2) prefill_tc_kernel(const __grid_co
             __syncwarp();
             if (lane == 0) mbar_arrive(bar(S_EMPTY + s));
 
+            // Raw scores stay in the registers the TMEM load filled; scale and maximum are folded into the
+            // exponent: p = 2^(s * scale - m) is one fma and one ex2 per element.
             float sc[BN];
-            const int64_t key0 = static_cast<int64_t>(j) * BN;
-            const bool edge = (key0 + BN - 1 > r0) || (key0 + BN > L);  // block touches the diagonal or the request's end
-            float mx = -INFINITY;
 #pragma unroll
-            for (int c = 0; c < BN; ++c) {
-                float v = __uint_as_float(c < 32 ? u0[c] : u1[c - 32]) * p.scale_log2;
-                if (edge) {
-                    const int64_t key = key0 + c;
-                    if (key > rr || key >= L) v = -INFINITY;
-                }
-                sc[c] = v;
-                mx = fmaxf(mx, v);
+            for (int c = 0; c < 32; ++c) {
+                sc[c] = __uint_as_float(u0[c]);
+                sc[c + 32] = __uint_as_float(u1[c]);
             }
+            const int64_t key0 = static_cast<int64_t>(j) * BN;
+            if ((key0 + BN - 1 > r0) || (key0 + BN > L)) {  // block touches the diagonal or the request's end
+                const int64_t lim = imin64(rr, L - 1) - key0;  // last allowed column of this row inside the block
+#pragma unroll
+                for (int c = 0; c < BN; ++c)
+                    if (c > lim) sc[c] = -INFINITY;
+            }
+            float mx0 = sc[0], mx1 = sc[1], mx2 = sc[2], mx3 = sc[3];
+#pragma unroll
+            for (int c = 4; c < BN; c += 4) {
+                mx0 = fmaxf(mx0, sc[c]);
+                mx1 = fmaxf(mx1, sc[c + 1]);
+                mx2 = fmaxf(mx2, sc[c + 2]);
+                mx3 = fmaxf(mx3, sc[c + 3]);
+            }
+            const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * p.scale_log2;  // scale > 0: max commutes with it
             // Lazy maximum: keep the old reference while the new maximum is within 2^8 of it.
             const float m_new = fmaxf(m_used, mx);
             const bool need = (m_new > m_used + 8.0f) || (m_used == -INFINITY && m_new != -INFINITY);
             if (__any_sync(0xffffffffu, need)) {
                 const float m_next = need ? m_new : m_used;
-                const float alpha = (m_used == -INFINITY) ? 0.f : exp2f(m_used - m_next);
+                const float alpha = (m_used == -INFINITY) ? 0.f : fast_exp2(m_used - m_next);
                 if (j > 0) {
                     if (!warp_wait(bar(O_FULL), static_cast<uint32_t>((j - 1) & 1), give_up)) {
                         ok = false;
@@ -388,14 +405,16 @@ __global__ void __launch_bounds__(kThreads, 2) prefill_tc_kernel(const __grid_co
                 l *= alpha;
                 m_used = m_next;
             }
-            const float m_ref = (m_used == -INFINITY) ? 0.f : m_used;
-            float rs = 0.f;
+            const float neg_m = (m_used == -INFINITY) ? 0.f : -m_used;
+            float rs0 = 0.f, rs1 = 0.f;
 #pragma unroll
-            for (int c = 0; c < BN; ++c) {
-                sc[c] = exp2f(sc[c] - m_ref);
-                rs += sc[c];
+            for (int c = 0; c < BN; c += 2) {
+                sc[c] = fast_exp2(fmaf(sc[c], p.scale_log2, neg_m));
+                sc[c + 1] = fast_exp2(fmaf(sc[c + 1], p.scale_log2, neg_m));
+                rs0 += sc[c];
+                rs1 += sc[c + 1];
             }
-            l += rs;
+            l += rs0 + rs1;
             // P_j into shared memory once the previous P has been consumed
             if (!warp_wait(bar(P_EMPTY), static_cast<uint32_t>((j & 1) ^ 1), give_up)) {
                 ok = false;
