@@ -37,6 +37,8 @@ OPS = {
     "diopiTokenDecodeAttentionInferenceNoAlloc": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int],
     "diopiContextAttentionInference": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int],
     "diopiApplyPenalty": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int],
+    "diopiRotaryEmbeddingV2": [c_void_p, c_void_p, c_void_p, c_void_p, c_int64],
+    "diopiApplyPenaltyV2": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
     "diopiRotaryEmbedding": [c_void_p, c_void_p, c_void_p, c_void_p, c_bool, c_bool],
     "diopiRMSNorm": [c_void_p, c_void_p, c_void_p, diopiSize_t, c_void_p, c_void_p, c_double],
 }

@@ -503,3 +503,83 @@ B200_EXPORT diopiError_t diopiTokenDecodeAttentionInferenceNoAlloc(diopiContextH
         B200_CUDA(cudaGetLastError());
     });
 }
+
+// ---------------------------------------------------------------------------------------------
+// The newer lightllm call forms of rotary embedding and penalty.
+B200_EXPORT diopiError_t diopiRotaryEmbeddingV2(diopiContextHandle_t ctx, diopiTensorHandle_t query, diopiTensorHandle_t key, diopiConstTensorHandle_t cos,
+                                                diopiConstTensorHandle_t sin, int64_t dim) {
+    return guard("diopiRotaryEmbeddingV2", [&] {
+        TensorView qv = view_of(query, "query"), kv = view_of(key, "key"), cv = view_of(cos, "cos"), sv = view_of(sin, "sin");
+        k::RopeV2Args a{};
+        a.dt = float_dt(qv, "query", true);
+        same_dtype(kv, "key", qv, "query");
+        same_dtype(cv, "cos", qv, "query");
+        same_dtype(sv, "sin", qv, "query");
+        B200_REQUIRE(dim > 0 && dim % 2 == 0, "dim (%ld) must be positive and even", (long)dim);
+        B200_REQUIRE(qv.ndim == 2 && kv.ndim == 2 && qv.shape[0] == kv.shape[0], "'query' and 'key' must be [tokens, heads * dim] with the same tokens");
+        B200_REQUIRE(qv.shape[1] % dim == 0 && kv.shape[1] % dim == 0, "the width of 'query'/'key' must be a multiple of dim = %ld", (long)dim);
+        B200_REQUIRE((qv.shape[1] == 1 || qv.stride[1] == 1) && (kv.shape[1] == 1 || kv.stride[1] == 1), "rows of 'query' and 'key' must be dense");
+        a.T = qv.shape[0];
+        a.dim = dim;
+        a.q_heads = qv.shape[1] / dim;
+        a.k_heads = kv.shape[1] / dim;
+        a.q = qv.data;
+        a.q_s0 = qv.stride[0];
+        a.kk = kv.data;
+        a.k_s0 = kv.stride[0];
+        // cos/sin: [tokens or 1, (1,) dim]; a middle head dim may be 1 (broadcast) or match both head counts
+        auto table = [&](const TensorView& t, const char* name, int64_t& st, int64_t& sh) {
+            B200_REQUIRE(t.ndim == 2 || t.ndim == 3, "'%s' must be [tokens, dim] or [tokens, 1, dim]", name);
+            B200_REQUIRE(t.shape[t.ndim - 1] == dim && (dim == 1 || t.stride[t.ndim - 1] == 1), "the last dim of '%s' must be dim = %ld and dense", name, (long)dim);
+            B200_REQUIRE(t.shape[0] == a.T || t.shape[0] == 1, "'%s' has %ld rows for %ld tokens", name, (long)t.shape[0], (long)a.T);
+            st = t.shape[0] == 1 ? 0 : t.stride[0];
+            sh = 0;
+            if (t.ndim == 3 && t.shape[1] != 1) {
+                B200_REQUIRE(t.shape[1] == a.q_heads && t.shape[1] == a.k_heads, "'%s' has %ld heads; expected 1 or the head count of query and key", name,
+                             (long)t.shape[1]);
+                sh = t.stride[1];
+            }
+        };
+        table(cv, "cos", a.c_st, a.c_sh);
+        table(sv, "sin", a.s_st, a.s_sh);
+        a.cos = cv.data;
+        a.sin = sv.data;
+        if (a.T == 0 || (qv.numel == 0 && kv.numel == 0)) return;
+        cudaStream_t st = stream_of(ctx);
+        k::launch_rope_v2(a, st);
+        B200_CUDA(cudaGetLastError());
+    });
+}
+
+B200_EXPORT diopiError_t diopiApplyPenaltyV2(diopiContextHandle_t ctx, diopiTensorHandle_t logits, diopiConstTensorHandle_t presence_penalty,
+                                             diopiConstTensorHandle_t frequency_penalty, diopiConstTensorHandle_t repetition_penalty,
+                                             diopiConstTensorHandle_t p_token_ids, diopiConstTensorHandle_t p_token_counts) {
+    return guard("diopiApplyPenaltyV2", [&] {
+        TensorView lg = view_of(logits, "logits"), pp = view_of(presence_penalty, "presence_penalty"), fp = view_of(frequency_penalty, "frequency_penalty");
+        TensorView rp = view_of(repetition_penalty, "repetition_penalty"), ids = view_of(p_token_ids, "p_token_ids"), cnt = view_of(p_token_counts, "p_token_counts");
+        k::PenaltyV2Args a{};
+        a.dt = float_dt(lg, "logits", true);
+        same_dtype(pp, "presence_penalty", lg, "logits");
+        same_dtype(fp, "frequency_penalty", lg, "logits");
+        same_dtype(rp, "repetition_penalty", lg, "logits");
+        a.ids = index_arg(ids, "p_token_ids", 1);
+        a.counts = index_arg(cnt, "p_token_counts", 1);
+        a.E = ids.shape[0];
+        B200_REQUIRE(cnt.shape[0] == a.E, "'p_token_ids' and 'p_token_counts' differ in length");
+        for (const TensorView* t : {&pp, &fp, &rp}) B200_REQUIRE(t->ndim == 1 && t->shape[0] == a.E, "the penalties must have one entry per token id (%ld)", (long)a.E);
+        B200_REQUIRE(lg.contiguous(), "'logits' must be contiguous (it is indexed as a flat array)");
+        a.logits = lg.data;
+        a.numel = lg.numel;
+        a.presence = pp.data;
+        a.p_s = pp.stride[0];
+        a.frequency = fp.data;
+        a.f_s = fp.stride[0];
+        a.repetition = rp.data;
+        a.r_s = rp.stride[0];
+        if (a.E == 0 || a.numel == 0) return;
+        cudaStream_t st = stream_of(ctx);
+        a.status = async_status_device_ptr();
+        k::launch_apply_penalty_v2(a, st);
+        B200_CUDA(cudaGetLastError());
+    });
+}

@@ -77,7 +77,82 @@ __global__ void __launch_bounds__(256) penalty_kernel(PenaltyArgs a) {
     }
 }
 
+// V2 (diopi_test/python/conformance/customized_test.py:823-841): entries index the flattened logits, every entry
+// has its own penalties, and a repetition penalty comes first: x > 0 ? x / r : x * r, then - count * f - p.
+// Each operation is rounded on its own in the dtype of logits, as the golden tensor expression does.
+template <typename T>
+struct Rnd;
+template <>
+struct Rnd<float> {
+    static __device__ __forceinline__ float ld(const void* p, int64_t i) { return static_cast<const float*>(p)[i]; }
+    static __device__ __forceinline__ float r(float v) { return v; }
+    static __device__ __forceinline__ void st(void* p, int64_t i, float v) { static_cast<float*>(p)[i] = v; }
+};
+template <>
+struct Rnd<__half> {
+    static __device__ __forceinline__ float ld(const void* p, int64_t i) { return __half2float(static_cast<const __half*>(p)[i]); }
+    static __device__ __forceinline__ float r(float v) { return __half2float(__float2half_rn(v)); }
+    static __device__ __forceinline__ void st(void* p, int64_t i, float v) { static_cast<__half*>(p)[i] = __float2half_rn(v); }
+};
+template <>
+struct Rnd<__nv_bfloat16> {
+    static __device__ __forceinline__ float ld(const void* p, int64_t i) { return __bfloat162float(static_cast<const __nv_bfloat16*>(p)[i]); }
+    static __device__ __forceinline__ float r(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+    static __device__ __forceinline__ void st(void* p, int64_t i, float v) { static_cast<__nv_bfloat16*>(p)[i] = __float2bfloat16_rn(v); }
+};
+
+template <typename T>
+__global__ void __launch_bounds__(256) penalty_v2_kernel(PenaltyV2Args a) {
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t e = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; e < a.E; e += stride) {
+        int64_t id = load_index(a.ids, e);
+        if (id < 0) id += a.numel;
+        if (id < 0 || id >= a.numel) {
+            report_status(a.status, 2);
+            continue;
+        }
+        const float x = Rnd<T>::ld(a.logits, id);
+        const float rp = Rnd<T>::ld(a.repetition, e * a.r_s);
+        const float f = Rnd<T>::ld(a.frequency, e * a.f_s);
+        const float pr = Rnd<T>::ld(a.presence, e * a.p_s);
+        const float cnt = Rnd<T>::r(static_cast<float>(load_index(a.counts, e)));
+        const float rep = Rnd<T>::r(x > 0.f ? __fdiv_rn(x, rp) : __fmul_rn(x, rp));
+        const float prod = Rnd<T>::r(__fmul_rn(cnt, f));
+        const float d = Rnd<T>::r(__fsub_rn(rep, prod));
+        Rnd<T>::st(a.logits, id, __fsub_rn(d, pr));
+    }
+}
+
+__global__ void __launch_bounds__(256) penalty_v2_f64_kernel(PenaltyV2Args a) {
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t e = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; e < a.E; e += stride) {
+        int64_t id = load_index(a.ids, e);
+        if (id < 0) id += a.numel;
+        if (id < 0 || id >= a.numel) {
+            report_status(a.status, 2);
+            continue;
+        }
+        double* lg = static_cast<double*>(a.logits);
+        const double x = lg[id];
+        const double rp = static_cast<const double*>(a.repetition)[e * a.r_s];
+        const double rep = x > 0.0 ? __ddiv_rn(x, rp) : __dmul_rn(x, rp);
+        const double prod = __dmul_rn(static_cast<double>(load_index(a.counts, e)), static_cast<const double*>(a.frequency)[e * a.f_s]);
+        lg[id] = __dsub_rn(__dsub_rn(rep, prod), static_cast<const double*>(a.presence)[e * a.p_s]);
+    }
+}
+
 }  // namespace
+
+void launch_apply_penalty_v2(const PenaltyV2Args& a, cudaStream_t st) {
+    if (a.E == 0 || a.numel == 0) return;
+    const unsigned blocks = static_cast<unsigned>(std::min<int64_t>((a.E + 255) / 256, 148ll * 32));
+    switch (a.dt) {
+        case Dt::F16: penalty_v2_kernel<__half><<<blocks, 256, 0, st>>>(a); break;
+        case Dt::BF16: penalty_v2_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>(a); break;
+        case Dt::F32: penalty_v2_kernel<float><<<blocks, 256, 0, st>>>(a); break;
+        case Dt::F64: penalty_v2_f64_kernel<<<blocks, 256, 0, st>>>(a); break;
+    }
+}
 
 void launch_apply_penalty(const PenaltyArgs& a, cudaStream_t st) {
     if (a.E == 0 || a.B == 0) return;

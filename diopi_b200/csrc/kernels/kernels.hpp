@@ -90,6 +90,17 @@ struct RopeArgs {
 };
 void launch_rope(const RopeArgs& a, cudaStream_t st);
 
+// In-place rotate-half form on [T, H*dim] query and key with full-width cos/sin (diopiRotaryEmbeddingV2).
+struct RopeV2Args {
+    Dt dt;
+    void* q; int64_t q_s0; int64_t q_heads;     // [T, q_heads*dim], row stride in elements
+    void* kk; int64_t k_s0; int64_t k_heads;    // [T, k_heads*dim]
+    const void* cos; const void* sin;
+    int64_t c_st, c_sh, s_st, s_sh;             // strides of cos/sin over token and head (0 where broadcast)
+    int64_t T, dim;
+};
+void launch_rope_v2(const RopeV2Args& a, cudaStream_t st);
+
 // ---- ApplyPenalty -----------------------------------------------------------
 struct PenaltyArgs {
     Dt dt;
@@ -101,6 +112,18 @@ struct PenaltyArgs {
     int* status;
 };
 void launch_apply_penalty(const PenaltyArgs& a, cudaStream_t st);
+
+// Flattened form with a repetition penalty and per-entry penalties (diopiApplyPenaltyV2).
+struct PenaltyV2Args {
+    Dt dt;
+    void* logits; int64_t numel;                // contiguous, indexed flat
+    const void* presence; const void* frequency; const void* repetition;  // [E]
+    int64_t p_s, f_s, r_s;
+    IndexArg ids, counts;
+    int64_t E;
+    int* status;
+};
+void launch_apply_penalty_v2(const PenaltyV2Args& a, cudaStream_t st);
 
 // ---- causal prefill ---------------------------------------------------------
 struct PrefillArgs {

@@ -144,7 +144,74 @@ void launch_typed(const RopeArgs& a, cudaStream_t st) {
     }
 }
 
+// V2 (diopi_test/python/conformance/customized_test.py:843-852): query and key [T, H*dim] are rotated in place,
+// x = x * cos + rotate_half(x) * sin with rotate_half(x) = (-x2, x1) and cos/sin as wide as the head. The golden
+// works in the dtype of the tensors: both products and the sum are each rounded to that dtype.
+template <typename T>
+struct RtT {
+    static __device__ __forceinline__ float r(float v) { return Cvt<T>::to_f(Cvt<T>::from_f(v)); }
+};
+template <>
+struct RtT<float> {
+    static __device__ __forceinline__ float r(float v) { return v; }
+};
+
+template <typename T>
+__global__ void __launch_bounds__(256) rope_v2_kernel(RopeV2Args a, int64_t total) {
+    const int64_t half = a.dim / 2;
+    const int64_t heads = a.q_heads + a.k_heads;
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+        const int64_t j = i % half;
+        const int64_t th = i / half;
+        const int64_t hh = th % heads;
+        const int64_t t = th / heads;
+        const bool is_q = hh < a.q_heads;
+        const int64_t h = is_q ? hh : hh - a.q_heads;
+        T* x = (is_q ? static_cast<T*>(a.q) + t * a.q_s0 : static_cast<T*>(a.kk) + t * a.k_s0) + h * a.dim;
+        const T* c = static_cast<const T*>(a.cos) + t * a.c_st + h * a.c_sh;
+        const T* s = static_cast<const T*>(a.sin) + t * a.s_st + h * a.s_sh;
+        const float x1 = Cvt<T>::to_f(x[j]), x2 = Cvt<T>::to_f(x[j + half]);
+        const float o1 = RtT<T>::r(__fadd_rn(RtT<T>::r(__fmul_rn(x1, Cvt<T>::to_f(c[j]))), RtT<T>::r(__fmul_rn(-x2, Cvt<T>::to_f(s[j])))));
+        const float o2 = RtT<T>::r(__fadd_rn(RtT<T>::r(__fmul_rn(x2, Cvt<T>::to_f(c[j + half]))), RtT<T>::r(__fmul_rn(x1, Cvt<T>::to_f(s[j + half])))));
+        x[j] = Cvt<T>::from_f(o1);
+        x[j + half] = Cvt<T>::from_f(o2);
+    }
+}
+
+__global__ void __launch_bounds__(256) rope_v2_f64_kernel(RopeV2Args a, int64_t total) {
+    const int64_t half = a.dim / 2;
+    const int64_t heads = a.q_heads + a.k_heads;
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+        const int64_t j = i % half;
+        const int64_t th = i / half;
+        const int64_t hh = th % heads;
+        const int64_t t = th / heads;
+        const bool is_q = hh < a.q_heads;
+        const int64_t h = is_q ? hh : hh - a.q_heads;
+        double* x = (is_q ? static_cast<double*>(a.q) + t * a.q_s0 : static_cast<double*>(a.kk) + t * a.k_s0) + h * a.dim;
+        const double* c = static_cast<const double*>(a.cos) + t * a.c_st + h * a.c_sh;
+        const double* s = static_cast<const double*>(a.sin) + t * a.s_st + h * a.s_sh;
+        const double x1 = x[j], x2 = x[j + half];
+        x[j] = __dadd_rn(__dmul_rn(x1, c[j]), __dmul_rn(-x2, s[j]));
+        x[j + half] = __dadd_rn(__dmul_rn(x2, c[j + half]), __dmul_rn(x1, s[j + half]));
+    }
+}
+
 }  // namespace
+
+void launch_rope_v2(const RopeV2Args& a, cudaStream_t st) {
+    const int64_t total = a.T * (a.q_heads + a.k_heads) * (a.dim / 2);
+    if (total == 0) return;
+    const unsigned blocks = static_cast<unsigned>(std::min<int64_t>((total + 255) / 256, 148ll * 64));
+    switch (a.dt) {
+        case Dt::F16: rope_v2_kernel<__half><<<blocks, 256, 0, st>>>(a, total); break;
+        case Dt::BF16: rope_v2_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>(a, total); break;
+        case Dt::F32: rope_v2_kernel<float><<<blocks, 256, 0, st>>>(a, total); break;
+        case Dt::F64: rope_v2_f64_kernel<<<blocks, 256, 0, st>>>(a, total); break;
+    }
+}
 
 void launch_rope(const RopeArgs& a, cudaStream_t st) {
     if (a.n_lead == 0 || a.half == 0) return;

@@ -105,6 +105,21 @@ def rotary_emb(input, cos, sin, conj, interleaved, *, out=None, ctx=None, as_dev
     return out
 
 
+def rotary_emb_v2(query, key, cos, sin, dim, *, ctx=None, as_device=None):
+    """In-place rotate-half rotary embedding on query and key [tokens, heads*dim]; returns (query, key)
+    (diopi_functions.py:8051)."""
+    ts = [_t(x, as_device) for x in (query, key, cos, sin)]
+    _call("diopiRotaryEmbeddingV2", ctx, *[_h(t) for t in ts], int(dim))
+    return query, key
+
+
+def apply_penalty_v2(logits, presence_penalty, frequency_penalty, repetition_penalty, p_token_ids, p_token_counts, *, ctx=None, as_device=None):
+    """In-place penalty on flattened logits with per-entry penalties; returns logits (diopi_functions.py:8019)."""
+    ts = [_t(x, as_device) for x in (logits, presence_penalty, frequency_penalty, repetition_penalty, p_token_ids, p_token_counts)]
+    _call("diopiApplyPenaltyV2", ctx, *[_h(t) for t in ts])
+    return logits
+
+
 def rms_norm(input, normalized_shape, weight, bias, eps, *, return_inv_rms=False, ctx=None, as_device=None):
     """Returns out (and inv_rms when asked). inv_rms is fp32 for fp16/bf16/fp32 input, fp64 for fp64."""
     out = torch.empty_like(input)

@@ -182,6 +182,19 @@ diopiError_t diopiRotaryEmbedding(diopiContextHandle_t ctx, diopiTensorHandle_t 
 diopiError_t diopiRMSNorm(diopiContextHandle_t ctx, diopiTensorHandle_t out, diopiTensorHandle_t inv_rms, diopiConstTensorHandle_t input,
                           diopiSize_t normalized_shape, diopiConstTensorHandle_t weight, diopiConstTensorHandle_t bias, double eps);
 
+/* In-place rotary embedding on query and key [tokens, heads*dim] in the rotate-half form with cos/sin
+ * as wide as a head: x = x*cos + (-x2, x1)*sin, each operation rounded in the tensors' dtype.
+ * Replaces functions_ext.h:649-650. */
+diopiError_t diopiRotaryEmbeddingV2(diopiContextHandle_t ctx, diopiTensorHandle_t query, diopiTensorHandle_t key, diopiConstTensorHandle_t cos,
+                                    diopiConstTensorHandle_t sin, int64_t dim);
+
+/* In-place penalty on the flattened logits with one penalty triple per entry:
+ * x = logits.flat[id]; x = x > 0 ? x / repetition : x * repetition; x -= count * frequency; x -= presence.
+ * Replaces functions_ext.h:547-549. */
+diopiError_t diopiApplyPenaltyV2(diopiContextHandle_t ctx, diopiTensorHandle_t logits, diopiConstTensorHandle_t presence_penalty,
+                                 diopiConstTensorHandle_t frequency_penalty, diopiConstTensorHandle_t repetition_penalty,
+                                 diopiConstTensorHandle_t p_token_ids, diopiConstTensorHandle_t p_token_counts);
+
 /* Extension (not in the DIOPI headers): the fused decode step. Equivalent to
  * diopiTokenAttentionInference followed by diopiTokenSoftmaxReduceVInference on
  * the same index tensors, but the logits never reach memory: one pass over the

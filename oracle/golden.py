@@ -164,3 +164,25 @@ def rms_norm(input, normalized_shape, weight, bias=None, eps=1e-6, return_inv_rm
     if return_inv_rms:
         return y, inv.reshape(input.shape[: input.dim() - len(dims)])
     return y
+
+
+def rotary_emb_v2(query, key, cos, sin, dim):
+    """Rotate-half form on [tokens, heads*dim] query and key with cos/sin as wide as a head, in the
+    dtype of the tensors (customized_test.py:843-852). Returns new (query, key)."""
+    def one(x):
+        x3 = x.view(x.shape[0], -1, dim)
+        x1, x2 = x3[..., : dim // 2], x3[..., dim // 2:]
+        rot = torch.cat((-x2, x1), dim=-1)
+        return (x3 * cos + rot * sin).view(x.shape[0], -1)
+    return one(query), one(key)
+
+
+def apply_penalty_v2(logits, presence_penalty, frequency_penalty, repetition_penalty, p_token_ids, p_token_counts):
+    """Flattened penalty with a repetition term first (customized_test.py:823-841); in place on logits."""
+    flat = logits.view(-1)
+    ids = p_token_ids.long()
+    cur = flat.index_select(0, ids)
+    rep = torch.where(cur > 0, cur / repetition_penalty, cur * repetition_penalty)
+    rep = rep - p_token_counts * frequency_penalty - presence_penalty
+    flat[ids] = rep
+    return logits

@@ -152,3 +152,27 @@ for tag, dt in {**DT, "f64": torch.float64, "bf16": torch.bfloat16}.items():
         b = randn(*ns, dtype=dt) if with_bias else None
         out = G.rms_norm(x, ns, w, b, eps)
         save(f"rms_norm_config{case}_{tag}", x=x, weight=w, bias=b, eps=np.array(eps), normalized_shape=np.array(ns), out=out)
+
+# ---- apply_penalty_v2: literal values of diopi_configs.py:9470-9515, plus a seeded case ----------
+for tag, dt in DT.items():
+    logits = torch.tensor([[0.1, 0.5, 0.4, 0.3, 0.5], [0.2, 0.4, 0.0, 0.0, 0.0], [0.3, 0.4, 0.5, 0.3, 0.0]], dtype=dt)
+    pen = torch.tensor([0.1, 0.1, 0.1, 0.1, 0.8, 0.8, 0.8, 0.8, 1.0, 1.0, 1.0], dtype=dt)
+    ids = torch.tensor([0, 1, 2, 3, 4, 5, 6, 8, 9, 10, 11], dtype=torch.int32)
+    cnt = torch.tensor([3, 3, 2, 2, 1, 3, 3, 3, 3, 2, 2], dtype=torch.int32)
+    out = G.apply_penalty_v2(logits.clone(), pen, pen, pen, ids, cnt)
+    save(f"apply_penalty_v2_config_{tag}", logits=logits, presence=pen, frequency=pen, repetition=pen, ids=ids, counts=cnt, out=out)
+    B, V, E = 7, 501, 300
+    logits = randn(B, V, dtype=dt, scale=2.0)
+    ids = torch.randperm(B * V, generator=gen)[:E].to(torch.int32)
+    cnt = torch.randint(1, 9, (E,), generator=gen).to(torch.int32)
+    pres, freq = torch.rand(E, generator=gen).to(dt), torch.rand(E, generator=gen).to(dt)
+    rep = (0.5 + torch.rand(E, generator=gen)).to(dt)
+    out = G.apply_penalty_v2(logits.clone(), pres, freq, rep, ids, cnt)
+    save(f"apply_penalty_v2_seeded_{tag}", logits=logits, presence=pres, frequency=freq, repetition=rep, ids=ids, counts=cnt, out=out)
+
+# ---- rotary_emb_v2: diopi_configs.py:9107-9135 (query/key (8, 4096), cos/sin (8, 1, 128), dim 128) ----
+for tag, dt in DT.items():
+    q, k = randn(8, 4096, dtype=dt), randn(8, 1024, dtype=dt)
+    c, s_ = randn(8, 1, 128, dtype=dt), randn(8, 1, 128, dtype=dt)
+    oq, ok = G.rotary_emb_v2(q.clone(), k.clone(), c, s_, 128)
+    save(f"rotary_emb_v2_config_{tag}", query=q, key=k, cos=c, sin=s_, dim=np.array(128), out_query=oq, out_key=ok)

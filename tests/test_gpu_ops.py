@@ -369,7 +369,34 @@ def test_two_threads_two_contexts(F):
 
 
 # ------------------------------------------------------------------ ApplyPenalty
-@pytest.mark.parametrize("name", fixture_names("apply_penalty"))
+@pytest.mark.parametrize("name", fixture_names("apply_penalty_v2"))
+def test_apply_penalty_v2_fixture(F, name):
+    f = load_fixture(name)
+    lg = f["logits"].clone().cuda()
+    F.apply_penalty_v2(lg, *cuda(f["presence"], f["frequency"], f["repetition"], f["ids"], f["counts"]))
+    assert torch.equal(lg.cpu(), f["out"])   # bit-exact: every operation is rounded as the golden rounds it
+    lg64 = f["logits"].clone().cuda()
+    F.apply_penalty_v2(lg64, *cuda(f["presence"], f["frequency"], f["repetition"], f["ids"].long(), f["counts"].long()))
+    assert torch.equal(lg64.cpu(), f["out"])
+
+
+@pytest.mark.parametrize("name", fixture_names("rotary_emb_v2"))
+def test_rotary_emb_v2_fixture(F, name):
+    f = load_fixture(name)
+    q, k = f["query"].clone().cuda(), f["key"].clone().cuda()
+    F.rotary_emb_v2(q, k, f["cos"].cuda(), f["sin"].cuda(), f["dim"])
+    assert torch.equal(q.cpu(), f["out_query"]) and torch.equal(k.cpu(), f["out_key"])
+    # [tokens, dim] tables, bf16, and rows taken from a wider buffer
+    g = torch.Generator().manual_seed(3)
+    wide = torch.randn(6, 3 * 256, generator=g).to(torch.bfloat16).cuda()
+    qv, kv = wide[:, :512], wide[:, 512:]
+    c, s_ = torch.randn(6, 64, generator=g).to(torch.bfloat16), torch.randn(6, 64, generator=g).to(torch.bfloat16)
+    wq, wk = golden.rotary_emb_v2(qv.cpu().contiguous(), kv.cpu().contiguous(), c.view(6, 1, 64), s_.view(6, 1, 64), 64)
+    F.rotary_emb_v2(qv, kv, c.cuda(), s_.cuda(), 64)
+    assert torch.equal(qv.cpu(), wq) and torch.equal(kv.cpu(), wk)
+
+
+@pytest.mark.parametrize("name", [n for n in fixture_names("apply_penalty") if "_v2_" not in n])
 def test_apply_penalty_fixture(F, name):
     f = load_fixture(name)
     lg = f["logits"].clone().cuda()
@@ -395,7 +422,7 @@ def test_apply_penalty_cfg5_bit_exact(F, dtype):
 
 
 # ------------------------------------------------------------------ rotary, RMSNorm
-@pytest.mark.parametrize("name", fixture_names("rotary_emb"))
+@pytest.mark.parametrize("name", [n for n in fixture_names("rotary_emb") if "_v2_" not in n])
 def test_rotary_fixture(F, name):
     f = load_fixture(name)
     x, c, s = cuda(f["x"], f["cos"], f["sin"])

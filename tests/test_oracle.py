@@ -15,7 +15,21 @@ def close(a, b):
     torch.testing.assert_close(a.double(), b.double(), **TOL[b.dtype])
 
 
-@pytest.mark.parametrize("name", fixture_names("apply_penalty"))
+@pytest.mark.parametrize("name", fixture_names("apply_penalty_v2"))
+def test_apply_penalty_v2_bit_exact(name):
+    f = load_fixture(name)
+    got = golden.apply_penalty_v2(f["logits"].clone(), f["presence"], f["frequency"], f["repetition"], f["ids"], f["counts"])
+    assert torch.equal(got, f["out"])
+
+
+@pytest.mark.parametrize("name", fixture_names("rotary_emb_v2"))
+def test_rotary_emb_v2(name):
+    f = load_fixture(name)
+    q, k = golden.rotary_emb_v2(f["query"], f["key"], f["cos"], f["sin"], f["dim"])
+    assert torch.equal(q, f["out_query"]) and torch.equal(k, f["out_key"])
+
+
+@pytest.mark.parametrize("name", [n for n in fixture_names("apply_penalty") if "_v2_" not in n])
 def test_apply_penalty_bit_exact(name):
     f = load_fixture(name)
     got = golden.apply_penalty(f["logits"].clone(), f["presence"], f["frequency"], f["ids"], f["counts"], f["cum"], 0)
@@ -88,7 +102,7 @@ def test_context_attention(name):
     close(blocked, f["out"])
 
 
-@pytest.mark.parametrize("name", fixture_names("rotary_emb"))
+@pytest.mark.parametrize("name", [n for n in fixture_names("rotary_emb") if "_v2_" not in n])
 def test_rotary_emb(name):
     f = load_fixture(name)
     close(golden.rotary_emb(f["x"], f["cos"], f["sin"], bool(f["conj"]), False), f["out"])

@@ -96,6 +96,22 @@ def test_penalty_validation(F):
     fails(DTYPE_NOT_SUPPORTED, F.apply_penalty, lg.int(), p.int(), p.int(), ids, ids, cum, 0)
 
 
+def test_v2_validation(F):
+    q, k = torch.zeros(4, 64), torch.zeros(4, 32)
+    c = torch.zeros(4, 1, 16)
+    fails(ERROR_OCCURRED, F.rotary_emb_v2, q, k, c, c, 15, match="even")
+    fails(ERROR_OCCURRED, F.rotary_emb_v2, q, k, c, c, 24, match="multiple of dim")
+    fails(ERROR_OCCURRED, F.rotary_emb_v2, q, k[:3], c, c, 16, match="same tokens")
+    fails(ERROR_OCCURRED, F.rotary_emb_v2, q, k, torch.zeros(4, 1, 8), c, 16, match="last dim of 'cos'")
+    fails(ERROR_OCCURRED, F.rotary_emb_v2, q, k, torch.zeros(3, 1, 16), c, 16, match="rows for")
+    lg, pen = torch.zeros(3, 10), torch.zeros(5)
+    ids = torch.zeros(5, dtype=torch.int32)
+    fails(ERROR_OCCURRED, F.apply_penalty_v2, lg, pen[:4], pen, pen, ids, ids, match="one entry per token id")
+    fails(ERROR_OCCURRED, F.apply_penalty_v2, lg, pen, pen, pen, ids, ids[:4], match="differ in length")
+    fails(ERROR_OCCURRED, F.apply_penalty_v2, lg.t(), pen, pen, pen, ids, ids, match="contiguous")
+    fails(ERROR_OCCURRED, F.apply_penalty_v2, lg, pen.half(), pen, pen, ids, ids, match="share a dtype")
+
+
 def test_context_attention_validation(F):
     q = torch.zeros(8, 2, 16, dtype=torch.float16)
     st, ln = torch.zeros(2, dtype=torch.int32), torch.zeros(2, dtype=torch.int32)
