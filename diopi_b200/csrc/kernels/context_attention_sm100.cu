@@ -149,6 +149,13 @@ __device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t adesc, uint64_t b
         "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
+// Same, A operand read from TMEM (for 16-bit types one 32-bit cell holds two consecutive K elements of a row).
+__device__ __forceinline__ void umma_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n" ::"r"(tmem_d),
+        "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
@@ -194,6 +201,9 @@ __device__ __forceinline__ uint32_t pack2(float a, float b, int bf16) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
+// P_IN_TMEM: the soft-max threads write P_j (packed 16-bit pairs) over the first 32 columns of the S buffer they
+// just read and the P V product takes its A operand from TMEM; otherwise P_j goes through shared memory.
+template <bool P_IN_TMEM>
 __global__ void __launch_bounds__(kThreads, 2) prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                                                                    const __grid_constant__ CUtensorMap map_v, const TcParams p) {
     extern __shared__ __align__(1024) unsigned char smem[];
@@ -242,7 +252,7 @@ __global__ void __launch_bounds__(kThreads, 2) prefill_tc_kernel(const __grid_co
             mbar_init(bar(K_EMPTY + s), 1);
             mbar_init(bar(V_EMPTY + s), 1);
             mbar_init(bar(S_FULL + s), 1);
-            mbar_init(bar(S_EMPTY + s), 4);
+            mbar_init(bar(S_EMPTY + s), P_IN_TMEM ? 1 : 4);   // freed by the P V commit, or by the four soft-max warps
         }
         mbar_init(bar(P_FULL), 4);
         mbar_init(bar(P_EMPTY), 1);
@@ -295,13 +305,21 @@ __global__ void __launch_bounds__(kThreads, 2) prefill_tc_kernel(const __grid_co
                 const uint32_t v_addr = smem_u32(smem + kOffV + s * kVStage);
 #pragma unroll
                 for (int t = 0; t < BN / 16; ++t) {
-                    // A = P [128 rows x 64 keys], K-major: 16 keys = 32 bytes inside the 128-byte swizzled row
-                    const uint64_t ad = make_desc(p_addr + t * 32, 0, 1024);
                     // B = V [64 keys x 128 d], MN-major: 16 keys = 16 rows of 128 bytes; the second 64-wide d block is 8 KB further
                     const uint64_t bd = make_desc(v_addr + t * 16 * 128, BN * 128, 1024);
-                    umma(tmem_base + kColO, ad, bd, idesc_pv, (i > 0 || t > 0) ? 1u : 0u);
+                    if (P_IN_TMEM) {
+                        // A = P in TMEM: 16 keys = 8 cells of the S buffer the soft-max threads overwrote
+                        umma_ts(tmem_base + kColO, tmem_base + kColS0 + s * BN + t * 8, bd, idesc_pv, (i > 0 || t > 0) ? 1u : 0u);
+                    } else {
+                        // A = P [128 rows x 64 keys] in shared memory, K-major: 16 keys = 32 bytes inside the 128-byte swizzled row
+                        const uint64_t ad = make_desc(p_addr + t * 32, 0, 1024);
+                        umma(tmem_base + kColO, ad, bd, idesc_pv, (i > 0 || t > 0) ? 1u : 0u);
+                    }
                 }
-                umma_commit(bar(P_EMPTY));
+                if (P_IN_TMEM)
+                    umma_commit(bar(S_EMPTY + s));   // the S/P buffer may be overwritten by Q K^T of block i + 2
+                else
+                    umma_commit(bar(P_EMPTY));
                 umma_commit(bar(V_EMPTY + s));
                 umma_commit(bar(O_FULL));
                 return true;
@@ -351,9 +369,11 @@ __global__ void __launch_bounds__(kThreads, 2) prefill_tc_kernel(const __grid_co
             tmem_ld32(lane_base + kColS0 + s * BN, u0);
             tmem_ld32(lane_base + kColS0 + s * BN + 32, u1);
             tmem_wait_ld();
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(bar(S_EMPTY + s));
+            if (!P_IN_TMEM) {
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar(S_EMPTY + s));
+            }
 
             // Raw scores stay in the registers the TMEM load filled; scale and maximum are folded into the
             // exponent: p = 2^(s * scale - m) is one fma and one ex2 per element.
@@ -415,22 +435,31 @@ __global__ void __launch_bounds__(kThreads, 2) prefill_tc_kernel(const __grid_co
                 rs1 += sc[c + 1];
             }
             l += rs0 + rs1;
-            // P_j into shared memory once the previous P has been consumed
-            if (!warp_wait(bar(P_EMPTY), static_cast<uint32_t>((j & 1) ^ 1), give_up)) {
-                ok = false;
-                break;
-            }
-            unsigned char* prow = smem + kOffP + (row >> 3) * 1024 + (row & 7) * 128;
+            if (P_IN_TMEM) {
+                // P_j over the S cells this thread just consumed: cell c holds keys 2c (low half) and 2c + 1
+                uint32_t pk[32];
 #pragma unroll
-            for (int ch = 0; ch < BN / 8; ++ch) {
-                uint4 v;
-                v.x = pack2(sc[ch * 8 + 0], sc[ch * 8 + 1], p.is_bf16);
-                v.y = pack2(sc[ch * 8 + 2], sc[ch * 8 + 3], p.is_bf16);
-                v.z = pack2(sc[ch * 8 + 4], sc[ch * 8 + 5], p.is_bf16);
-                v.w = pack2(sc[ch * 8 + 6], sc[ch * 8 + 7], p.is_bf16);
-                *reinterpret_cast<uint4*>(prow + ((ch ^ (row & 7)) << 4)) = v;
+                for (int c = 0; c < 32; ++c) pk[c] = pack2(sc[2 * c], sc[2 * c + 1], p.is_bf16);
+                tmem_st32(lane_base + kColS0 + s * BN, pk);
+                tmem_wait_st();
+            } else {
+                // P_j into shared memory once the previous P has been consumed
+                if (!warp_wait(bar(P_EMPTY), static_cast<uint32_t>((j & 1) ^ 1), give_up)) {
+                    ok = false;
+                    break;
+                }
+                unsigned char* prow = smem + kOffP + (row >> 3) * 1024 + (row & 7) * 128;
+#pragma unroll
+                for (int ch = 0; ch < BN / 8; ++ch) {
+                    uint4 v;
+                    v.x = pack2(sc[ch * 8 + 0], sc[ch * 8 + 1], p.is_bf16);
+                    v.y = pack2(sc[ch * 8 + 2], sc[ch * 8 + 3], p.is_bf16);
+                    v.z = pack2(sc[ch * 8 + 4], sc[ch * 8 + 5], p.is_bf16);
+                    v.w = pack2(sc[ch * 8 + 6], sc[ch * 8 + 7], p.is_bf16);
+                    *reinterpret_cast<uint4*>(prow + ((ch ^ (row & 7)) << 4)) = v;
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             }
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar(P_FULL));
@@ -539,9 +568,18 @@ void launch_prefill_tc(const PrefillArgs& a, int /*sm_count*/, int max_smem, cud
     p.scale_log2 = kLog2e / sqrtf(static_cast<float>(HD));
     p.is_bf16 = bf16 ? 1 : 0;
     p.status = nullptr;
-    cudaFuncSetAttribute(prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    static const bool p_smem = [] {
+        const char* v = std::getenv("DIOPI_B200_PREFILL_P_SMEM");
+        return v && v[0] && v[0] != '0';
+    }();
     dim3 grid(p.n_tiles_max, a.H, 1);
-    prefill_tc_kernel<<<grid, kThreads, kSmemBytes, st>>>(mq, mk, mv, p);
+    if (p_smem) {
+        cudaFuncSetAttribute(prefill_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+        prefill_tc_kernel<false><<<grid, kThreads, kSmemBytes, st>>>(mq, mk, mv, p);
+    } else {
+        cudaFuncSetAttribute(prefill_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+        prefill_tc_kernel<true><<<grid, kThreads, kSmemBytes, st>>>(mq, mk, mv, p);
+    }
     *taken = true;
 }
 

@@ -15,29 +15,43 @@ namespace k {
 
 namespace {
 
+template <typename IDX>
 struct Offsets {
-    int64_t x, o, c, s;
+    IDX x, o, c, s;
 };
 
 // IDX = uint32_t when every extent and the element count fit 32 bits (the usual case): 32-bit
 // division is several times cheaper than 64-bit, and this chain is most of the kernel's arithmetic.
 template <typename IDX>
-__device__ __forceinline__ Offsets lead_offsets(const RopeArgs& a, IDX lead) {
-    Offsets r{0, 0, 0, 0};
+__device__ __forceinline__ Offsets<IDX> lead_offsets(const RopeArgs& a, IDX lead) {
+    Offsets<IDX> r{0, 0, 0, 0};
 #pragma unroll
     for (int d = kRopeMaxDims - 1; d >= 0; --d) {
         if (d < a.nd) {
             const IDX sz = static_cast<IDX>(a.size[d]);
             const IDX q = lead / sz;
-            const int64_t i = static_cast<int64_t>(lead - q * sz);
+            const IDX i = lead - q * sz;
             lead = q;
-            r.x += i * a.xs[d];
-            r.o += i * a.os[d];
-            r.c += i * a.cs[d];
-            r.s += i * a.ss[d];
+            r.x += i * static_cast<IDX>(a.xs[d]);
+            r.o += i * static_cast<IDX>(a.os[d]);
+            r.c += i * static_cast<IDX>(a.cs[d]);
+            r.s += i * static_cast<IDX>(a.ss[d]);
         }
     }
     return r;
+}
+
+// Same result as rotate() for fp16/bf16 inputs with one instruction less per output: the product of two such
+// values is exact in fp32, so fma(x1, c, -(x2*s)) rounds exactly once, like the subtraction of the two products.
+__device__ __forceinline__ void rotate16(float x1, float x2, float c, float s, bool conj, float& o1, float& o2) {
+    const float b = x2 * s, e = x2 * c;
+    if (!conj) {
+        o1 = fmaf(x1, c, -b);
+        o2 = fmaf(x1, s, e);
+    } else {
+        o1 = fmaf(x1, c, b);
+        o2 = fmaf(-x1, s, e);
+    }
 }
 
 __device__ __forceinline__ void rotate(float x1, float x2, float c, float s, bool conj, float& o1, float& o2) {
@@ -60,7 +74,7 @@ __global__ void __launch_bounds__(256) rope_vec_kernel(RopeArgs a, int vec_per_h
     for (IDX i = static_cast<IDX>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
         const IDX lead = i / static_cast<IDX>(vec_per_half);
         const int v = static_cast<int>(i - lead * static_cast<IDX>(vec_per_half));
-        const Offsets of = lead_offsets<IDX>(a, lead);
+        const Offsets<IDX> of = lead_offsets<IDX>(a, lead);
         const T* x = static_cast<const T*>(a.x) + of.x;
         T* o = static_cast<T*>(a.out) + of.o;
         const uint4 r1 = __ldcs(reinterpret_cast<const uint4*>(x) + v);
@@ -73,7 +87,12 @@ __global__ void __launch_bounds__(256) rope_vec_kernel(RopeArgs a, int vec_per_h
         unpack16<T>(rc, c);
         unpack16<T>(rs, s);
 #pragma unroll
-        for (int e = 0; e < N; ++e) rotate(x1[e], x2[e], c[e], s[e], a.conj, o1[e], o2[e]);
+        for (int e = 0; e < N; ++e) {
+            if (sizeof(T) == 2)
+                rotate16(x1[e], x2[e], c[e], s[e], a.conj, o1[e], o2[e]);
+            else
+                rotate(x1[e], x2[e], c[e], s[e], a.conj, o1[e], o2[e]);
+        }
         __stcs(reinterpret_cast<uint4*>(o) + v, pack16<T>(o1));
         __stcs(reinterpret_cast<uint4*>(o + a.half) + v, pack16<T>(o2));
     }
@@ -92,7 +111,7 @@ __global__ void __launch_bounds__(256) rope_scalar_kernel(RopeArgs a, int64_t to
     for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
         const int64_t lead = i / a.half;
         const int64_t j = i - lead * a.half;
-        const Offsets of = lead_offsets<int64_t>(a, lead);
+        const Offsets<int64_t> of = lead_offsets<int64_t>(a, lead);
         const T* x = static_cast<const T*>(a.x) + of.x;
         T* o = static_cast<T*>(a.out) + of.o;
         const float c = Io<T>::ld(static_cast<const T*>(a.cos) + of.c + j * a.c_ls);
@@ -109,7 +128,7 @@ __global__ void __launch_bounds__(256) rope_scalar_f64_kernel(RopeArgs a, int64_
     for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
         const int64_t lead = i / a.half;
         const int64_t j = i - lead * a.half;
-        const Offsets of = lead_offsets<int64_t>(a, lead);
+        const Offsets<int64_t> of = lead_offsets<int64_t>(a, lead);
         const double* x = static_cast<const double*>(a.x) + of.x;
         double* o = static_cast<double*>(a.out) + of.o;
         const double c = static_cast<const double*>(a.cos)[of.c + j * a.c_ls];
@@ -133,7 +152,10 @@ void launch_typed(const RopeArgs& a, cudaStream_t st) {
         const int vph = static_cast<int>(a.half / N);
         const int64_t total = a.n_lead * vph;
         const unsigned blocks = static_cast<unsigned>(std::min<int64_t>((total + 255) / 256, 148ll * 64));
-        if (total < (1ll << 31))
+        // 32-bit index arithmetic when every element offset of the four tensors fits
+        int64_t span = a.half * 2;
+        for (int d = 0; d < a.nd; ++d) span += (a.size[d] - 1) * std::max(std::max(a.xs[d], a.os[d]), std::max(a.cs[d], a.ss[d]));
+        if (total < (1ll << 31) && span < (1ll << 31))
             rope_vec_kernel<T, uint32_t><<<blocks, 256, 0, st>>>(a, vph, total);
         else
             rope_vec_kernel<T, int64_t><<<blocks, 256, 0, st>>>(a, vph, total);
