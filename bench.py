@@ -147,7 +147,8 @@ def run_b200(args):
         w = workloads.decode(name, device="cuda", float_seed=1002 + 97 * rank)
         scaling = "weak"
     else:
-        h0, h1 = workloads.shard_heads(64, n, rank)
+        # --shard-of N on one GPU builds rank 0's shard of an N-way split (to study the per-GPU kernel of a wide split)
+        h0, h1 = workloads.shard_heads(64, max(n, args.shard_of), rank)
         w = workloads.decode("cfg5", device="cuda", head_range=(h0, h1))
         scaling = "strong"
     ctx = Context()
@@ -393,6 +394,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="cfg2", choices=["cfg2", "cfg2s", "cfg5"])
     ap.add_argument("--kernels-only", action="store_true", help="run warm-up + timed steps only (for profiler captures)")
+    ap.add_argument("--shard-of", type=int, default=1, help="cfg5 on one GPU: hold only rank 0's head shard of an N-way split")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-budget", type=float, default=20.0)
     args = ap.parse_args()

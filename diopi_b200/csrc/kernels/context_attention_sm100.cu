@@ -6,11 +6,15 @@
 // One CTA = one tile of 128 query rows of one (request, head); two CTAs share an SM so that one CTA's
 // soft-max overlaps the other's MMAs. Per CTA, for key blocks of 64 up to the causal limit:
 //   warp 0 (one lane)  TMA: Q once (two 64-wide boxes, 128-byte swizzle), then K_j and V_j into a 2-stage ring
-//   warp 1 (one lane)  S_j = Q K_j^T   (tcgen05.mma M128 N64 K16 x 8, both operands K-major) -> TMEM S[j%2]
-//                      O  += P_j V_j   (tcgen05.mma M128 N128 K16 x 4, P K-major from shared memory, V MN-major)
-//   warps 2-5          thread = query row: tcgen05.ld of its S row, scale, causal/length mask, online soft-max
-//                      in base 2 with a lazily updated maximum (O in TMEM is rescaled only when the maximum
-//                      grew by more than 2^8), P_j as fp16/bf16 into shared memory in the MMA's swizzled layout
+//   warp 1 (one lane)  issues both products, each as soon as its inputs are ready (probing the barriers, never
+//                      blocking on one while the other could go):
+//                        S_j = Q K_j^T  tcgen05.mma M128 N64 K16 x 8, both operands K-major from shared memory,
+//                                       into TMEM buffer S[j%2] once P V of block j - 2 has released it
+//                        O  += P_j V_j  tcgen05.mma M128 N128 K16 x 4, A = P_j read from TMEM, B = V_j MN-major
+//   warps 2-5          thread = query row: tcgen05.ld of its S row, causal/length mask, online soft-max in base 2
+//                      (scale and maximum folded into one fma + ex2.approx per score; the reference maximum is
+//                      only raised when the row maximum grew by more than 2^8, and only then is O in TMEM
+//                      rescaled), P_j packed to 16 bit and written over the S cells just read
 // The L x L score and mask tensors of the reference never exist; FLOPs counted = 4*D*L*(L+1)/2 per head.
 //
 // All waits are bounded (2 s); a wait that runs out sets a flag, every role leaves its loop, TMEM is
@@ -38,22 +42,20 @@ constexpr float kLog2e = 1.4426950408889634f;
 constexpr int kQBytes = BM * HD * 2;            // 32 KB: two [128 x 64] blocks
 constexpr int kKStage = BN * HD * 2;            // 16 KB: two [64 x 64] blocks
 constexpr int kVStage = BN * HD * 2;            // 16 KB
-constexpr int kPBytes = BM * BN * 2;            // 16 KB: one [128 x 64] block
 constexpr int kOffQ = 0;
 constexpr int kOffK = kOffQ + kQBytes;
 constexpr int kOffV = kOffK + kStages * kKStage;
-constexpr int kOffP = kOffV + kStages * kVStage;
-constexpr int kOffBar = kOffP + kPBytes;        // 112 KB
-constexpr int kNumBars = 1 + 4 * kStages + 2 * 2 + 3;   // q, k/v full+empty, s full+empty, p full/empty, o full
+constexpr int kOffBar = kOffV + kStages * kVStage;   // 96 KB
+constexpr int kNumBars = 15;
 constexpr int kOffTmemSlot = kOffBar + kNumBars * 8;
 constexpr int kOffFlag = kOffTmemSlot + 8;
-constexpr int kSmemBytes = kOffFlag + 8;          // two CTAs per SM: 2 * (112.2 KB + 1 KB reserved) fits the SM's 228 KB
+constexpr int kSmemBytes = kOffFlag + 8;          // two CTAs per SM: 2 * (96.2 KB + 1 KB reserved) of the SM's 228 KB
 
-// TMEM columns (fp32): S[0] 0..63, S[1] 64..127, O 128..255
+// TMEM columns (fp32 cells): S[0] 0..63, S[1] 64..127 (P_j overwrites the first 32 cells of S[j%2]), O 128..255
 constexpr uint32_t kTmemCols = 256;
 constexpr uint32_t kColS0 = 0, kColO = 128;
 
-enum Bar { Q_FULL = 0, K_FULL = 1, V_FULL = 3, K_EMPTY = 5, V_EMPTY = 7, S_FULL = 9, S_EMPTY = 11, P_FULL = 13, P_EMPTY = 14, O_FULL = 15 };
+enum Bar { Q_FULL = 0, K_FULL = 1, V_FULL = 3, K_EMPTY = 5, V_EMPTY = 7, S_FULL = 9, S_EMPTY = 11, P_FULL = 13, O_FULL = 14 };
 
 struct TcParams {
     IndexArg b_start, b_len;
@@ -63,7 +65,6 @@ struct TcParams {
     int64_t o_s0, o_s1;
     int n_tiles_max;
     float scale_log2;
-    int is_bf16;
     int* status;
 };
 
@@ -78,6 +79,16 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
         "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Non-blocking probe of a phase (try_wait may park the thread for a while; this never does).
+__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n.reg .pred p;\nmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
         : "=r"(ok)
         : "r"(bar), "r"(parity)
         : "memory");
@@ -192,8 +203,9 @@ __device__ __forceinline__ float fast_exp2(float x) {
     return y;
 }
 
-__device__ __forceinline__ uint32_t pack2(float a, float b, int bf16) {
-    if (bf16) {
+template <bool BF16>
+__device__ __forceinline__ uint32_t pack2(float a, float b) {
+    if (BF16) {
         __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
         return *reinterpret_cast<uint32_t*>(&v);
     }
@@ -201,9 +213,7 @@ __device__ __forceinline__ uint32_t pack2(float a, float b, int bf16) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
-// P_IN_TMEM: the soft-max threads write P_j (packed 16-bit pairs) over the first 32 columns of the S buffer they
-// just read and the P V product takes its A operand from TMEM; otherwise P_j goes through shared memory.
-template <bool P_IN_TMEM>
+template <bool BF16>
 __global__ void __launch_bounds__(kThreads, 2) prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                                                                    const __grid_constant__ CUtensorMap map_v, const TcParams p) {
     extern __shared__ __align__(1024) unsigned char smem[];
@@ -252,10 +262,9 @@ __global__ void __launch_bounds__(kThreads, 2) prefill_tc_kernel(const __grid_co
             mbar_init(bar(K_EMPTY + s), 1);
             mbar_init(bar(V_EMPTY + s), 1);
             mbar_init(bar(S_FULL + s), 1);
-            mbar_init(bar(S_EMPTY + s), P_IN_TMEM ? 1 : 4);   // freed by the P V commit, or by the four soft-max warps
+            mbar_init(bar(S_EMPTY + s), 1);   // freed by the commit that follows P V of the block that used the buffer
         }
         mbar_init(bar(P_FULL), 4);
-        mbar_init(bar(P_EMPTY), 1);
         mbar_init(bar(O_FULL), 1);
         *give_up = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -293,61 +302,68 @@ __global__ void __launch_bounds__(kThreads, 2) prefill_tc_kernel(const __grid_co
     } else if (warp == 1) {
         // ================================ MMA issuer ===================================
         if (lane == 0) {
-            const uint32_t idesc_qk = make_idesc(BM, BN, p.is_bf16, 0);
-            const uint32_t idesc_pv = make_idesc(BM, HD, p.is_bf16, 1);
-            const uint32_t q_addr = smem_u32(smem + kOffQ), p_addr = smem_u32(smem + kOffP);
+            const uint32_t idesc_qk = make_idesc(BM, BN, BF16 ? 1 : 0, 0);
+            const uint32_t idesc_pv = make_idesc(BM, HD, BF16 ? 1 : 0, 1);
+            const uint32_t q_addr = smem_u32(smem + kOffQ);
             bool ok = mbar_wait(bar(Q_FULL), 0, give_up);
-            auto issue_pv = [&](int i) -> bool {
-                const int s = i % kStages;
-                if (!mbar_wait(bar(P_FULL), static_cast<uint32_t>(i & 1), give_up)) return false;
-                if (!mbar_wait(bar(V_FULL + s), static_cast<uint32_t>((i / kStages) & 1), give_up)) return false;
-                tc_fence_after();
-                const uint32_t v_addr = smem_u32(smem + kOffV + s * kVStage);
+            // Event driven: Q K^T of the next block and P V of the oldest finished soft-max are issued in whatever
+            // order their inputs become ready, so a ready P never queues behind a Q K^T that still waits for its
+            // S buffer, and the other way round.
+            int nqk = 0, npv = 0;
+            unsigned long long idle_since = 0;
+            while (ok && npv < nblk) {
+                bool progressed = false;
+                if (npv < nqk) {
+                    const int i = npv;
+                    const int s = i % kStages;
+                    if (mbar_test(bar(P_FULL), static_cast<uint32_t>(i & 1)) && mbar_test(bar(V_FULL + s), static_cast<uint32_t>((i / kStages) & 1))) {
+                        tc_fence_after();
+                        const uint32_t v_addr = smem_u32(smem + kOffV + s * kVStage);
 #pragma unroll
-                for (int t = 0; t < BN / 16; ++t) {
-                    // B = V [64 keys x 128 d], MN-major: 16 keys = 16 rows of 128 bytes; the second 64-wide d block is 8 KB further
-                    const uint64_t bd = make_desc(v_addr + t * 16 * 128, BN * 128, 1024);
-                    if (P_IN_TMEM) {
-                        // A = P in TMEM: 16 keys = 8 cells of the S buffer the soft-max threads overwrote
-                        umma_ts(tmem_base + kColO, tmem_base + kColS0 + s * BN + t * 8, bd, idesc_pv, (i > 0 || t > 0) ? 1u : 0u);
-                    } else {
-                        // A = P [128 rows x 64 keys] in shared memory, K-major: 16 keys = 32 bytes inside the 128-byte swizzled row
-                        const uint64_t ad = make_desc(p_addr + t * 32, 0, 1024);
-                        umma(tmem_base + kColO, ad, bd, idesc_pv, (i > 0 || t > 0) ? 1u : 0u);
+                        for (int t = 0; t < BN / 16; ++t) {
+                            // B = V [64 keys x 128 d], MN-major: 16 keys = 16 rows of 128 bytes; the second 64-wide d block is 8 KB further
+                            const uint64_t bd = make_desc(v_addr + t * 16 * 128, BN * 128, 1024);
+                            // A = P in TMEM: 16 keys = 8 cells of the S buffer the soft-max threads overwrote
+                            umma_ts(tmem_base + kColO, tmem_base + kColS0 + s * BN + t * 8, bd, idesc_pv, (i > 0 || t > 0) ? 1u : 0u);
+                        }
+                        umma_commit(bar(S_EMPTY + s));   // the S/P buffer may be overwritten by Q K^T of block i + 2
+                        umma_commit(bar(V_EMPTY + s));
+                        umma_commit(bar(O_FULL));
+                        ++npv;
+                        progressed = true;
                     }
                 }
-                if (P_IN_TMEM)
-                    umma_commit(bar(S_EMPTY + s));   // the S/P buffer may be overwritten by Q K^T of block i + 2
-                else
-                    umma_commit(bar(P_EMPTY));
-                umma_commit(bar(V_EMPTY + s));
-                umma_commit(bar(O_FULL));
-                return true;
-            };
-            for (int j = 0; ok && j < nblk; ++j) {
-                const int s = j % kStages;
-                const uint32_t ph = static_cast<uint32_t>((j / kStages) & 1);
-                if (!mbar_wait(bar(K_FULL + s), ph, give_up) || !mbar_wait(bar(S_EMPTY + s), ph ^ 1u, give_up)) {
-                    ok = false;
-                    break;
-                }
-                tc_fence_after();
-                const uint32_t k_addr = smem_u32(smem + kOffK + s * kKStage);
+                if (nqk < nblk) {
+                    const int s = nqk % kStages;
+                    const uint32_t ph = static_cast<uint32_t>((nqk / kStages) & 1);
+                    if (mbar_test(bar(K_FULL + s), ph) && mbar_test(bar(S_EMPTY + s), ph ^ 1u)) {
+                        tc_fence_after();
+                        const uint32_t k_addr = smem_u32(smem + kOffK + s * kKStage);
 #pragma unroll
-                for (int t = 0; t < HD / 16; ++t) {
-                    // both operands K-major; d block t/4 (64 wide), 16 d = 32 bytes inside the swizzled row
-                    const uint64_t ad = make_desc(q_addr + (t / 4) * (BM * 128) + (t % 4) * 32, 0, 1024);
-                    const uint64_t bd = make_desc(k_addr + (t / 4) * (BN * 128) + (t % 4) * 32, 0, 1024);
-                    umma(tmem_base + kColS0 + s * BN, ad, bd, idesc_qk, t > 0 ? 1u : 0u);
+                        for (int t = 0; t < HD / 16; ++t) {
+                            // both operands K-major; d block t/4 (64 wide), 16 d = 32 bytes inside the swizzled row
+                            const uint64_t ad = make_desc(q_addr + (t / 4) * (BM * 128) + (t % 4) * 32, 0, 1024);
+                            const uint64_t bd = make_desc(k_addr + (t / 4) * (BN * 128) + (t % 4) * 32, 0, 1024);
+                            umma(tmem_base + kColS0 + s * BN, ad, bd, idesc_qk, t > 0 ? 1u : 0u);
+                        }
+                        umma_commit(bar(S_FULL + s));
+                        umma_commit(bar(K_EMPTY + s));
+                        ++nqk;
+                        progressed = true;
+                    }
                 }
-                umma_commit(bar(S_FULL + s));
-                umma_commit(bar(K_EMPTY + s));
-                if (j > 0 && !issue_pv(j - 1)) {
-                    ok = false;
-                    break;
+                if (progressed) {
+                    idle_since = 0;
+                } else {
+                    if (*give_up) break;
+                    const unsigned long long now = global_ns();
+                    if (idle_since == 0) idle_since = now;
+                    if (now - idle_since > kWaitLimitNs) {
+                        *give_up = 1;
+                        break;
+                    }
                 }
             }
-            if (ok) issue_pv(nblk - 1);
         }
     } else {
         // ================================ soft-max warps: thread = query row ==========================
@@ -369,11 +385,6 @@ __global__ void __launch_bounds__(kThreads, 2) prefill_tc_kernel(const __grid_co
             tmem_ld32(lane_base + kColS0 + s * BN, u0);
             tmem_ld32(lane_base + kColS0 + s * BN + 32, u1);
             tmem_wait_ld();
-            if (!P_IN_TMEM) {
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(bar(S_EMPTY + s));
-            }
 
             // Raw scores stay in the registers the TMEM load filled; scale and maximum are folded into the
             // exponent: p = 2^(s * scale - m) is one fma and one ex2 per element.
@@ -435,35 +446,19 @@ __global__ void __launch_bounds__(kThreads, 2) prefill_tc_kernel(const __grid_co
                 rs1 += sc[c + 1];
             }
             l += rs0 + rs1;
-            if (P_IN_TMEM) {
-                // P_j over the S cells this thread just consumed: cell c holds keys 2c (low half) and 2c + 1
-                uint32_t pk[32];
+            // P_j over the S cells this thread just consumed: cell c holds keys 2c (low half) and 2c + 1
+            uint32_t pk[32];
 #pragma unroll
-                for (int c = 0; c < 32; ++c) pk[c] = pack2(sc[2 * c], sc[2 * c + 1], p.is_bf16);
-                tmem_st32(lane_base + kColS0 + s * BN, pk);
-                tmem_wait_st();
-            } else {
-                // P_j into shared memory once the previous P has been consumed
-                if (!warp_wait(bar(P_EMPTY), static_cast<uint32_t>((j & 1) ^ 1), give_up)) {
-                    ok = false;
-                    break;
-                }
-                unsigned char* prow = smem + kOffP + (row >> 3) * 1024 + (row & 7) * 128;
-#pragma unroll
-                for (int ch = 0; ch < BN / 8; ++ch) {
-                    uint4 v;
-                    v.x = pack2(sc[ch * 8 + 0], sc[ch * 8 + 1], p.is_bf16);
-                    v.y = pack2(sc[ch * 8 + 2], sc[ch * 8 + 3], p.is_bf16);
-                    v.z = pack2(sc[ch * 8 + 4], sc[ch * 8 + 5], p.is_bf16);
-                    v.w = pack2(sc[ch * 8 + 6], sc[ch * 8 + 7], p.is_bf16);
-                    *reinterpret_cast<uint4*>(prow + ((ch ^ (row & 7)) << 4)) = v;
-                }
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            }
+            for (int c = 0; c < 32; ++c) pk[c] = pack2<BF16>(sc[2 * c], sc[2 * c + 1]);
+            tmem_st32(lane_base + kColS0 + s * BN, pk);
+            tmem_wait_st();
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar(P_FULL));
         }
+        // The last two P V products may both still be in flight here (a finished S_j only proves that P V of block
+        // j - 2 is done), and a parity wait can only tell neighbouring phases apart: wait for them one by one.
+        if (ok && nblk >= 2) ok = warp_wait(bar(O_FULL), static_cast<uint32_t>((nblk - 2) & 1), give_up);
         if (ok && warp_wait(bar(O_FULL), static_cast<uint32_t>((nblk - 1) & 1), give_up)) {
             tc_fence_after();
             const float inv = l > 0.f ? 1.f / l : 0.f;
@@ -478,10 +473,10 @@ __global__ void __launch_bounds__(kThreads, 2) prefill_tc_kernel(const __grid_co
 #pragma unroll
                     for (int ch = 0; ch < 4; ++ch) {
                         uint4 v;
-                        v.x = pack2(__uint_as_float(o[ch * 8 + 0]) * inv, __uint_as_float(o[ch * 8 + 1]) * inv, p.is_bf16);
-                        v.y = pack2(__uint_as_float(o[ch * 8 + 2]) * inv, __uint_as_float(o[ch * 8 + 3]) * inv, p.is_bf16);
-                        v.z = pack2(__uint_as_float(o[ch * 8 + 4]) * inv, __uint_as_float(o[ch * 8 + 5]) * inv, p.is_bf16);
-                        v.w = pack2(__uint_as_float(o[ch * 8 + 6]) * inv, __uint_as_float(o[ch * 8 + 7]) * inv, p.is_bf16);
+                        v.x = pack2<BF16>(__uint_as_float(o[ch * 8 + 0]) * inv, __uint_as_float(o[ch * 8 + 1]) * inv);
+                        v.y = pack2<BF16>(__uint_as_float(o[ch * 8 + 2]) * inv, __uint_as_float(o[ch * 8 + 3]) * inv);
+                        v.z = pack2<BF16>(__uint_as_float(o[ch * 8 + 4]) * inv, __uint_as_float(o[ch * 8 + 5]) * inv);
+                        v.w = pack2<BF16>(__uint_as_float(o[ch * 8 + 6]) * inv, __uint_as_float(o[ch * 8 + 7]) * inv);
                         *reinterpret_cast<uint4*>(dst + c4 * 64 + ch * 16) = v;
                     }
                 }
@@ -566,19 +561,14 @@ void launch_prefill_tc(const PrefillArgs& a, int /*sm_count*/, int max_smem, cud
     p.o_s1 = a.o_s1;
     p.n_tiles_max = static_cast<int>(a.total_rows / BM + a.B);
     p.scale_log2 = kLog2e / sqrtf(static_cast<float>(HD));
-    p.is_bf16 = bf16 ? 1 : 0;
     p.status = nullptr;
-    static const bool p_smem = [] {
-        const char* v = std::getenv("DIOPI_B200_PREFILL_P_SMEM");
-        return v && v[0] && v[0] != '0';
-    }();
     dim3 grid(p.n_tiles_max, a.H, 1);
-    if (p_smem) {
-        cudaFuncSetAttribute(prefill_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
-        prefill_tc_kernel<false><<<grid, kThreads, kSmemBytes, st>>>(mq, mk, mv, p);
-    } else {
+    if (bf16) {
         cudaFuncSetAttribute(prefill_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
         prefill_tc_kernel<true><<<grid, kThreads, kSmemBytes, st>>>(mq, mk, mv, p);
+    } else {
+        cudaFuncSetAttribute(prefill_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+        prefill_tc_kernel<false><<<grid, kThreads, kSmemBytes, st>>>(mq, mk, mv, p);
     }
     *taken = true;
 }
