@@ -40,7 +40,8 @@ namespace {
 
 constexpr int kConsumerWarps = 16;
 constexpr int kConsumerThreads = kConsumerWarps * 32;
-constexpr int kThreads = kConsumerThreads + 32;  // + one producer warp
+constexpr int kMaxProducerWarps = 4;             // short rows need more copy instructions per byte than one warp can issue
+constexpr int kThreads = kConsumerThreads + 32 * kMaxProducerWarps;   // launch bound; the launch uses 512 + 32 * plan.producer_warps
 constexpr int kMaxB = 2048;                      // request prefix sums live in shared memory
 constexpr int kMaxG = 32;                        // token groups per CTA
 constexpr int kMaxStages = 32;
@@ -63,6 +64,7 @@ struct SplitPlan {
     int off_bars, off_pre, off_red, off_flag;
     int ups;           // token groups per ring slot (1, 2 or 4): a tile of TPG groups spans TPG / ups ring slots
     int pdl;           // launch the merge kernel as a programmatic dependent
+    int producer_warps;
 };
 
 // ---------------------------------------------------------------------------
@@ -206,7 +208,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_split_kernel(const DecodeA
         pre[0] = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    for (int i = tid; i < a.B; i += kThreads) pre[i + 1] = request_len(a, i);
+    for (int i = tid; i < a.B; i += static_cast<int>(blockDim.x)) pre[i + 1] = request_len(a, i);
     __syncthreads();
     if (warp == 0) {
         int carry = 0;
@@ -232,8 +234,12 @@ __global__ void __launch_bounds__(kThreads, 1) decode_split_kernel(const DecodeA
     // A tile = TT = G * TPG tokens = TPG token groups. It occupies TPG / ups consecutive ring slots of
     // ups * G tokens each (K rows, then V rows). ups = TPG (one 64 KB slot per tile) measured fastest: every
     // extra mbarrier round trip per token costs more than the finer refill granularity wins.
-    if (warp == kConsumerWarps) {
-        // =========================== producer warp ===============================
+    if (warp >= kConsumerWarps) {
+        // =========================== producer warps ==============================
+        // Producer warp pw issues the copies of the tokens whose index has (t / 8) % producer_warps == pw; warp 0
+        // also announces the bytes of each ring slot. A copy of the other warp may land before that announcement:
+        // the slot's phase cannot complete before the announcing arrive, so the early bytes are only booked ahead.
+        const int pw = warp - kConsumerWarps;
         const char* kbase = kHasK ? static_cast<const char*>(a.kmat) + static_cast<int64_t>(hg0) * a.k_s1 * sizeof(T) : nullptr;
         const char* vbase = kHasV ? static_cast<const char*>(a.vmat) + static_cast<int64_t>(hg0) * a.v_s1 * sizeof(T) : nullptr;
         const int64_t k_row = a.k_s0 * static_cast<int64_t>(sizeof(T));
@@ -278,7 +284,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_split_kernel(const DecodeA
             if (have) fetch_slots(req, j0, cnt, slot);
             // Lane u < spt owns ring slot u of this tile: waits until it is free and announces its bytes.
             bool mine_ok = true;
-            if (lane < spt) {
+            if (lane < spt) {  // every producer warp waits for the slots to be free; only warp 0 announces bytes
                 int s = ring + lane;
                 uint32_t parity = ring_phase;
                 if (s >= p.nstages) {
@@ -286,7 +292,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_split_kernel(const DecodeA
                     parity ^= 1u;
                 }
                 mine_ok = mbar_wait(smem_u32(&bars[p.nstages + s]), parity ^ 1u, give_up);
-                if (mine_ok) {
+                if (mine_ok && pw == 0) {
                     const int here = min(max(cur_cnt - lane * tps, 0), tps);  // tokens of the tile that fall into this ring slot
                     mbar_arrive_expect_tx(smem_u32(&bars[s]), static_cast<uint32_t>(here) * row_bytes * static_cast<uint32_t>(p.nmat));
                 }
@@ -296,7 +302,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_split_kernel(const DecodeA
 #pragma unroll
             for (int u = 0; u < TPG; ++u) {
                 const int t = lane + 32 * u;
-                if (t < cur_cnt) {
+                if (t < cur_cnt && ((t >> 3) % p.producer_warps) == pw) {
                     const int su = t / tps;
                     int s = ring + su;
                     if (s >= p.nstages) s -= p.nstages;
@@ -737,6 +743,7 @@ bool make_split_plan(const DecodeArgs& a, int sm_count, int max_smem, SplitPlan&
     p.TT = p.G * p.tpg;
     p.nmat = (has_k && has_v) ? 2 : 1;
     p.pdl = env_int("DIOPI_B200_DECODE_PDL", 1);
+    p.producer_warps = std::max(1, std::min(kMaxProducerWarps, env_int("DIOPI_B200_DECODE_PRODUCERS", 4)));
     p.ups = env_int("DIOPI_B200_DECODE_UPS", p.tpg);
     if (p.ups != 1 && p.ups != 2 && p.ups != 4 && p.ups != 8) p.ups = p.tpg;
     if (p.ups > p.tpg) p.ups = p.tpg;
@@ -790,11 +797,11 @@ void launch_split_t(const DecodeArgs& a, const SplitPlan& p, float* ws_acc, floa
     if (fused && p.tpg == 2) {
         auto kern = decode_split_kernel<T, LPH, MODE, (fused ? 2 : 8)>;
         cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, p.smem_bytes);
-        kern<<<grid, kThreads, p.smem_bytes, st>>>(a, p, ws_acc, ws_ml);
+        kern<<<grid, kConsumerThreads + 32 * p.producer_warps, p.smem_bytes, st>>>(a, p, ws_acc, ws_ml);
     } else {
         auto kern = decode_split_kernel<T, LPH, MODE, (fused ? 4 : 8)>;
         cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, p.smem_bytes);
-        kern<<<grid, kThreads, p.smem_bytes, st>>>(a, p, ws_acc, ws_ml);
+        kern<<<grid, kConsumerThreads + 32 * p.producer_warps, p.smem_bytes, st>>>(a, p, ws_acc, ws_ml);
     }
     if (MODE != static_cast<int>(DecodeMode::QK)) {
         // Programmatic dependent launch: the merge kernel's launch latency and set-up overlap the split kernel.
