@@ -37,6 +37,8 @@ OPS = {
     "diopiTokenDecodeAttentionInferenceNoAlloc": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int],
     "diopiContextAttentionInference": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int],
     "diopiApplyPenalty": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int],
+    "diopiPagedAttention": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, diopiSize_t, c_int64, c_int64, c_int64, c_void_p, c_int64],
+    "diopiPromptFlashAttention": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, diopiSize_t, c_int64, c_int64, c_int64, c_int64],
     "diopiRotaryEmbeddingV2": [c_void_p, c_void_p, c_void_p, c_void_p, c_int64],
     "diopiApplyPenaltyV2": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
     "diopiRotaryEmbedding": [c_void_p, c_void_p, c_void_p, c_void_p, c_bool, c_bool],

@@ -583,3 +583,147 @@ B200_EXPORT diopiError_t diopiApplyPenaltyV2(diopiContextHandle_t ctx, diopiTens
         B200_CUDA(cudaGetLastError());
     });
 }
+
+// ---------------------------------------------------------------------------------------------
+// Causal prefill over a padded batch in BSH layout: request i owns rows [i * max_input_len, (i + 1) * max_input_len)
+// of query/key/value [batch * max_input_len, heads * dim]. Same kernels as diopiContextAttentionInference, with
+// the request spans computed instead of read, and num_kv_heads < num_heads served as grouped-query attention.
+// As in the golden function (customized_test.py:751-783), every one of the max_input_len rows of a request is
+// computed under the causal mask; atten_mask is not read and actual_seq_lengths only gives the batch size.
+B200_EXPORT diopiError_t diopiPromptFlashAttention(diopiContextHandle_t ctx, diopiTensorHandle_t out, diopiConstTensorHandle_t query,
+                                                   diopiConstTensorHandle_t key, diopiConstTensorHandle_t value, diopiConstTensorHandle_t /*atten_mask*/,
+                                                   diopiSize_t actual_seq_lengths, int64_t max_input_len, int64_t num_heads, int64_t num_kv_heads,
+                                                   int64_t dim) {
+    return guard("diopiPromptFlashAttention", [&] {
+        TensorView o = view_of(out, "out"), qv = view_of(query, "query"), kv = view_of(key, "key"), vv = view_of(value, "value");
+        k::PrefillArgs a{};
+        a.dt = float_dt(qv, "query", false);
+        same_dtype(kv, "key", qv, "query");
+        same_dtype(vv, "value", qv, "query");
+        same_dtype(o, "out", qv, "query");
+        B200_REQUIRE(num_heads > 0 && num_kv_heads > 0 && dim > 0 && num_heads % num_kv_heads == 0,
+                     "num_heads (%ld) must be a positive multiple of num_kv_heads (%ld)", (long)num_heads, (long)num_kv_heads);
+        B200_REQUIRE(dim <= 256, "dim %ld is beyond the supported maximum of 256", (long)dim);
+        const int64_t B = actual_seq_lengths.len;
+        B200_REQUIRE(B >= 0 && max_input_len >= 0, "batch and max_input_len must not be negative");
+        const int64_t rows = B * max_input_len;
+        auto rows_of = [&](const TensorView& t, const char* name, int64_t heads, int64_t& row_stride) {
+            // [rows, heads*dim] or [batch, max_input_len, heads*dim], last dim dense, rows evenly spaced
+            B200_REQUIRE(t.ndim == 2 || t.ndim == 3, "'%s' must be [batch*len, heads*dim] or [batch, len, heads*dim]", name);
+            B200_REQUIRE(t.shape[t.ndim - 1] == heads * dim && (heads * dim == 1 || t.stride[t.ndim - 1] == 1), "the last dim of '%s' must be %ld and dense", name,
+                         (long)(heads * dim));
+            if (t.ndim == 2) {
+                B200_REQUIRE(t.shape[0] == rows, "'%s' has %ld rows; expected batch * max_input_len = %ld", name, (long)t.shape[0], (long)rows);
+                row_stride = t.stride[0];
+            } else {
+                B200_REQUIRE(t.shape[0] == B && t.shape[1] == max_input_len, "'%s' must be [%ld, %ld, *]", name, (long)B, (long)max_input_len);
+                B200_REQUIRE(B <= 1 || t.stride[0] == t.shape[1] * t.stride[1], "the batch stride of '%s' must equal len * row stride", name);
+                row_stride = t.stride[1];
+            }
+        };
+        rows_of(qv, "query", num_heads, a.q_s0);
+        rows_of(o, "out", num_heads, a.o_s0);
+        rows_of(kv, "key", num_kv_heads, a.k_s0);
+        rows_of(vv, "value", num_kv_heads, a.v_s0);
+        a.q_s1 = a.k_s1 = a.v_s1 = a.o_s1 = dim;
+        a.total_rows = rows;
+        a.H = static_cast<int>(num_heads);
+        a.D = static_cast<int>(dim);
+        a.B = static_cast<int>(B);
+        a.max_input_len = static_cast<int>(max_input_len);
+        a.uniform_len = max_input_len;
+        a.kv_group = static_cast<int>(num_heads / num_kv_heads);
+        a.q = qv.data;
+        a.kmat = kv.data;
+        a.vmat = vv.data;
+        a.out = o.data;
+        if (rows == 0) return;
+        cudaStream_t st = stream_of(ctx);
+        const DeviceInfo& di = device_info();
+        k::launch_prefill(a, di.sm_count, di.max_smem_optin, st);
+        B200_CUDA(cudaGetLastError());
+    });
+}
+
+// ---------------------------------------------------------------------------------------------
+// Decode attention over a block-paged KV cache in BSH layout: one query token per request, token j of request i
+// sits in row block_table[i, j / block_size] * block_size + j % block_size of key/value [rows, num_kv_heads*dim].
+// The fused decode kernels do the work (split path when num_kv_heads == num_heads, plain path for grouped heads);
+// the host-side lengths are staged into context scratch with one small asynchronous copy. atten_mask is not
+// read (a decode token sees its whole prefix), as in the golden function (customized_test.py:785-821).
+B200_EXPORT diopiError_t diopiPagedAttention(diopiContextHandle_t ctx, diopiTensorHandle_t out, diopiConstTensorHandle_t q, diopiConstTensorHandle_t kh,
+                                             diopiConstTensorHandle_t v, diopiConstTensorHandle_t /*atten_mask*/, diopiSize_t actual_seq_lengths,
+                                             int64_t num_heads, int64_t num_kv_heads, int64_t dim, diopiConstTensorHandle_t block_table,
+                                             int64_t block_size) {
+    return guard("diopiPagedAttention", [&] {
+        TensorView o = view_of(out, "out"), qv = view_of(q, "q"), kv = view_of(kh, "k"), vv = view_of(v, "v"), bt = view_of(block_table, "block_table");
+        k::DecodeArgs a{};
+        a.mode = k::DecodeMode::FUSED;
+        a.dt = float_dt(qv, "q", false);
+        same_dtype(kv, "k", qv, "q");
+        same_dtype(vv, "v", qv, "q");
+        same_dtype(o, "out", qv, "q");
+        B200_REQUIRE(num_heads > 0 && num_kv_heads > 0 && dim > 0 && num_heads % num_kv_heads == 0,
+                     "num_heads (%ld) must be a positive multiple of num_kv_heads (%ld)", (long)num_heads, (long)num_kv_heads);
+        B200_REQUIRE(dim <= 512, "dim %ld is beyond the supported maximum of 512", (long)dim);
+        B200_REQUIRE(block_size > 0 && block_size < (1ll << 30), "block_size must be positive (got %ld)", (long)block_size);
+        const int64_t B = actual_seq_lengths.len;
+        auto bsh = [&](const TensorView& t, const char* name, int64_t lead, int64_t heads, int64_t& s0) {
+            // [lead, heads*dim] or [lead, 1, heads*dim]
+            B200_REQUIRE((t.ndim == 2 || (t.ndim == 3 && t.shape[1] == 1)) && (lead < 0 || t.shape[0] == lead) && t.shape[t.ndim - 1] == heads * dim,
+                         "'%s' must be [%s, %ld] (a middle dim of 1 is allowed)", name, lead < 0 ? "rows" : "batch", (long)(heads * dim));
+            B200_REQUIRE(heads * dim == 1 || t.stride[t.ndim - 1] == 1, "the last dim of '%s' must be dense", name);
+            s0 = t.stride[0];
+        };
+        bsh(qv, "q", B, num_heads, a.q_s0);
+        bsh(o, "out", B, num_heads, a.out_s0);
+        bsh(kv, "k", -1, num_kv_heads, a.k_s0);
+        bsh(vv, "v", -1, num_kv_heads, a.v_s0);
+        B200_REQUIRE(kv.shape[0] == vv.shape[0], "'k' and 'v' differ in row count");
+        a.q_s1 = a.k_s1 = a.v_s1 = a.out_s1 = dim;
+        a.q_s2 = a.k_s2 = a.v_s2 = a.out_s2 = 1;
+        a.q = qv.data;
+        a.kmat = kv.data;
+        a.vmat = vv.data;
+        a.out = o.data;
+        a.B = static_cast<int>(B);
+        a.H = static_cast<int>(num_heads);
+        a.D = static_cast<int>(dim);
+        a.slots = kv.shape[0];
+        a.block_size = static_cast<int>(block_size);
+        a.kv_group = static_cast<int>(num_heads / num_kv_heads);
+        a.b_loc = index_arg(bt, "block_table", 2);
+        B200_REQUIRE(bt.shape[0] == B, "'block_table' has %ld rows for a batch of %ld", (long)bt.shape[0], (long)B);
+        if (B == 0) return;
+        B200_REQUIRE(actual_seq_lengths.data != nullptr, "actual_seq_lengths has no data");
+        int64_t longest = 0;
+        for (int64_t i = 0; i < B; ++i) {
+            const int64_t L = actual_seq_lengths.data[i];
+            B200_REQUIRE(L >= 0 && L <= bt.shape[1] * block_size, "request %ld has length %ld but its block table covers %ld tokens", (long)i, (long)L,
+                         (long)(bt.shape[1] * block_size));
+            longest = L > longest ? L : longest;
+        }
+        B200_REQUIRE(longest < (1ll << 31), "sequence lengths must fit 31 bits");
+        a.max_input_len = static_cast<int>(longest);
+        cudaStream_t st = stream_of(ctx);
+        if (longest == 0 || a.slots == 0) {
+            B200_REQUIRE(longest == 0, "the K/V cache has no rows");
+            B200_REQUIRE(o.contiguous(), "'out' must be contiguous when every request is empty");
+            B200_CUDA(cudaMemsetAsync(o.data, 0, static_cast<size_t>(o.numel * o.elem_size()), st));
+            return;
+        }
+        // lengths: host array -> context scratch (the copy reads the host array before it returns: pageable source)
+        void* lens_dev = workspace(ctx, B * static_cast<int64_t>(sizeof(int64_t)));
+        B200_CUDA(cudaMemcpyAsync(lens_dev, actual_seq_lengths.data, static_cast<size_t>(B) * sizeof(int64_t), cudaMemcpyHostToDevice, st));
+        a.b_len.ptr = lens_dev;
+        a.b_len.s0 = 1;
+        a.b_len.is64 = 1;
+        a.b_start = a.b_len;  // not read in fused mode
+        const DeviceInfo& di = device_info();
+        a.status = async_status_device_ptr();
+        const int64_t ws_bytes = k::decode_workspace_bytes(a, di.sm_count, di.max_smem_optin);
+        void* ws = ws_bytes > 0 ? workspace(ctx, ws_bytes) : nullptr;
+        k::launch_decode(a, ws, di.sm_count, di.max_smem_optin, st);
+        B200_CUDA(cudaGetLastError());
+    });
+}

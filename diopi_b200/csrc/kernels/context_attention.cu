@@ -36,6 +36,7 @@ __global__ void __launch_bounds__(kRowsPerCta * 32) prefill_simt_kernel(const Pr
     // The host does not know the lengths, so the grid is sized for the worst case
     // (sum of ceil(L_i/8) <= total_rows/8 + B); find which request and row tile this CTA is.
     const int h = blockIdx.y;
+    const int hkv = h / a.kv_group;   // grouped-query attention: several query heads share one K/V head
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     int req = -1;
     int64_t L = 0, start = 0, r0 = 0;
@@ -43,8 +44,8 @@ __global__ void __launch_bounds__(kRowsPerCta * 32) prefill_simt_kernel(const Pr
         int64_t tiles_before = 0;
         const int64_t flat = blockIdx.x;
         for (int i = 0; i < a.B; ++i) {
-            int64_t Li = load_index(a.b_len, i);
-            const int64_t si = load_index(a.b_start, i);
+            int64_t Li = a.uniform_len > 0 ? a.uniform_len : load_index(a.b_len, i);
+            const int64_t si = a.uniform_len > 0 ? i * a.uniform_len : load_index(a.b_start, i);
             if (Li <= 0 || si < 0 || si >= a.total_rows) continue;
             Li = imin64(Li, a.total_rows - si);
             const int64_t nt = (Li + kRowsPerCta - 1) / kRowsPerCta;
@@ -77,8 +78,8 @@ __global__ void __launch_bounds__(kRowsPerCta * 32) prefill_simt_kernel(const Pr
         const int nk = static_cast<int>(imin64(kKeysPerTile, last_key + 1 - j0));
         for (int idx = threadIdx.x; idx < nk * D; idx += blockDim.x) {
             const int jj = idx / D, d = idx - jj * D;
-            sK[jj * kpad + d] = static_cast<const T*>(a.kmat)[(start + j0 + jj) * a.k_s0 + static_cast<int64_t>(h) * a.k_s1 + d];
-            sV[jj * D + d] = static_cast<const T*>(a.vmat)[(start + j0 + jj) * a.v_s0 + static_cast<int64_t>(h) * a.v_s1 + d];
+            sK[jj * kpad + d] = static_cast<const T*>(a.kmat)[(start + j0 + jj) * a.k_s0 + static_cast<int64_t>(hkv) * a.k_s1 + d];
+            sV[jj * D + d] = static_cast<const T*>(a.vmat)[(start + j0 + jj) * a.v_s0 + static_cast<int64_t>(hkv) * a.v_s1 + d];
         }
         __syncthreads();
         if (!row_ok) continue;

@@ -66,6 +66,8 @@ struct TcParams {
     int n_tiles_max;
     float scale_log2;
     int* status;
+    int64_t uniform_len;   // > 0: request i owns rows [i * uniform_len, (i + 1) * uniform_len)
+    int kv_group;          // query heads per K/V head
 };
 
 // ---------------------------------------------------------------------------------------------
@@ -224,6 +226,7 @@ __global__ void __launch_bounds__(kThreads, 2) prefill_tc_kernel(const __grid_co
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int h = blockIdx.y;
+    const int hkv = h / p.kv_group;   // grouped-query attention: several query heads share one K/V head
 
     // ---- which (request, row tile) is this CTA? Heaviest tiles (late rows) are handed out first. ----
     int req = -1;
@@ -232,8 +235,8 @@ __global__ void __launch_bounds__(kThreads, 2) prefill_tc_kernel(const __grid_co
         const int64_t flat = static_cast<int64_t>(p.n_tiles_max) - 1 - blockIdx.x;
         int64_t before = 0;
         for (int i = 0; i < p.B; ++i) {
-            int64_t Li = load_index(p.b_len, i);
-            const int64_t si = load_index(p.b_start, i);
+            int64_t Li = p.uniform_len > 0 ? p.uniform_len : load_index(p.b_len, i);
+            const int64_t si = p.uniform_len > 0 ? i * p.uniform_len : load_index(p.b_start, i);
             if (Li <= 0 || si < 0 || si >= p.total_rows) continue;
             Li = imin64(Li, p.total_rows - si);
             const int64_t nt = (Li + BM - 1) / BM;
@@ -291,12 +294,12 @@ __global__ void __launch_bounds__(kThreads, 2) prefill_tc_kernel(const __grid_co
                 const int krow = static_cast<int>(start + static_cast<int64_t>(j) * BN);
                 if (!mbar_wait(bar(K_EMPTY + s), ph ^ 1u, give_up)) break;
                 mbar_expect_tx(bar(K_FULL + s), kKStage);
-                tma_load_3d(smem_u32(smem + kOffK + s * kKStage), &map_k, 0, h, krow, bar(K_FULL + s));
-                tma_load_3d(smem_u32(smem + kOffK + s * kKStage + BN * 128), &map_k, 64, h, krow, bar(K_FULL + s));
+                tma_load_3d(smem_u32(smem + kOffK + s * kKStage), &map_k, 0, hkv, krow, bar(K_FULL + s));
+                tma_load_3d(smem_u32(smem + kOffK + s * kKStage + BN * 128), &map_k, 64, hkv, krow, bar(K_FULL + s));
                 if (!mbar_wait(bar(V_EMPTY + s), ph ^ 1u, give_up)) break;
                 mbar_expect_tx(bar(V_FULL + s), kVStage);
-                tma_load_3d(smem_u32(smem + kOffV + s * kVStage), &map_v, 0, h, krow, bar(V_FULL + s));
-                tma_load_3d(smem_u32(smem + kOffV + s * kVStage + BN * 128), &map_v, 64, h, krow, bar(V_FULL + s));
+                tma_load_3d(smem_u32(smem + kOffV + s * kVStage), &map_v, 0, hkv, krow, bar(V_FULL + s));
+                tma_load_3d(smem_u32(smem + kOffV + s * kVStage + BN * 128), &map_v, 64, hkv, krow, bar(V_FULL + s));
             }
         }
     } else if (warp == 1) {
@@ -547,8 +550,8 @@ void launch_prefill_tc(const PrefillArgs& a, int /*sm_count*/, int max_smem, cud
     const bool bf16 = a.dt == Dt::BF16;
     CUtensorMap mq, mk, mv;
     if (!make_map(&mq, a.q, a.total_rows, a.H, a.q_s0, a.q_s1, BM, bf16)) return;
-    if (!make_map(&mk, a.kmat, a.total_rows, a.H, a.k_s0, a.k_s1, BN, bf16)) return;
-    if (!make_map(&mv, a.vmat, a.total_rows, a.H, a.v_s0, a.v_s1, BN, bf16)) return;
+    if (!make_map(&mk, a.kmat, a.total_rows, a.H / a.kv_group, a.k_s0, a.k_s1, BN, bf16)) return;
+    if (!make_map(&mv, a.vmat, a.total_rows, a.H / a.kv_group, a.v_s0, a.v_s1, BN, bf16)) return;
 
     TcParams p;
     p.b_start = a.b_start;
@@ -562,6 +565,8 @@ void launch_prefill_tc(const PrefillArgs& a, int /*sm_count*/, int max_smem, cud
     p.n_tiles_max = static_cast<int>(a.total_rows / BM + a.B);
     p.scale_log2 = kLog2e / sqrtf(static_cast<float>(HD));
     p.status = nullptr;
+    p.uniform_len = a.uniform_len;
+    p.kv_group = a.kv_group;
     dim3 grid(p.n_tiles_max, a.H, 1);
     if (bf16) {
         cudaFuncSetAttribute(prefill_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);

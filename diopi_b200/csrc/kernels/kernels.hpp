@@ -48,6 +48,9 @@ struct DecodeArgs {
     int64_t slots;       // extent of dim 0 of the pool (bounds check)
     int64_t att_cols;    // extent of dim 1 of att (bounds check)
     int* status;
+    int block_size;      // 0: b_loc names one slot per token, right-aligned in its first max_input_len columns;
+                         // > 0: b_loc is a block table, token j of request i sits in row b_loc[i, j / block_size] * block_size + j % block_size
+    int kv_group;        // query heads per K/V head (plain path only; 0 or 1 = one to one)
 };
 
 // Size in bytes of the scratch the split-KV path needs for these arguments, 0 if the
@@ -130,10 +133,12 @@ struct PrefillArgs {
     Dt dt;
     const void* q; const void* kmat; const void* vmat; void* out;   // [sumL, H, D]
     int64_t q_s0, q_s1, k_s0, k_s1, v_s0, v_s1, o_s0, o_s1;          // last dim dense
-    IndexArg b_start, b_len;
+    IndexArg b_start, b_len;     // ignored when uniform_len > 0
     int B, H, D;
     int64_t total_rows;
     int max_input_len;
+    int64_t uniform_len = 0;     // > 0: padded batch, request i owns rows [i * uniform_len, (i + 1) * uniform_len)
+    int kv_group = 1;            // query heads per K/V head (grouped-query attention); k/v have H / kv_group heads
 };
 void launch_prefill(const PrefillArgs& a, int sm_count, int max_smem, cudaStream_t st);
 

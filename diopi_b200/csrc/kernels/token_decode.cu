@@ -161,6 +161,15 @@ struct StageWalk {
     }
 };
 
+// Pool row of token j of request r (L = clamped length of the request).
+__device__ __forceinline__ int64_t token_slot(const DecodeArgs& a, int r, int L, int64_t j) {
+    if (a.block_size > 0) {
+        const int64_t blk = load_index(a.b_loc, r, j / a.block_size);
+        return blk < 0 ? -1 : blk * a.block_size + j % a.block_size;
+    }
+    return load_index(a.b_loc, r, static_cast<int64_t>(a.max_input_len) - L + j);
+}
+
 // Clamped request length: never negative, never beyond the window b_loc holds.
 __device__ __forceinline__ int request_len(const DecodeArgs& a, int i) {
     int64_t L = load_index(a.b_len, i);
@@ -256,13 +265,12 @@ __global__ void __launch_bounds__(kThreads, 1) decode_split_kernel(const DecodeA
         int64_t slot[TPG];  // tokens lane, lane+32, ... of the tile
         auto fetch_slots = [&](int r, int j, int n, int64_t (&out)[TPG]) {
             const int L = pre[r + 1] - pre[r];
-            const int64_t col0 = static_cast<int64_t>(a.max_input_len) - L + j;
 #pragma unroll
             for (int u = 0; u < TPG; ++u) {
                 const int t = lane + 32 * u;
                 out[u] = 0;
                 if (t < n) {
-                    int64_t sl = load_index(a.b_loc, r, col0 + t);
+                    int64_t sl = token_slot(a, r, L, static_cast<int64_t>(j) + t);
                     if (sl < 0 || sl >= a.slots) {
                         report_status(a.status, 1);
                         sl = 0;  // keep the byte count of the slot intact
@@ -612,9 +620,10 @@ __global__ void __launch_bounds__(128) decode_plain_kernel(const DecodeArgs a) {
     __shared__ float s_m[4], s_l[4];
     __shared__ float s_acc[4][512];
     const int i = blockIdx.x, h = blockIdx.y;
+    const int hkv = a.kv_group > 1 ? h / a.kv_group : h;   // grouped-query attention: the K/V head this query head reads
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int L = request_len(a, i);
-    const int64_t col0 = load_index(a.b_start, i);
+    const int64_t col0 = (MODE == static_cast<int>(DecodeMode::FUSED)) ? 0 : load_index(a.b_start, i);
     const float inv_sqrt_d = 1.0f / sqrtf(static_cast<float>(a.D));
 
     float qf[R], acc[R];
@@ -627,7 +636,7 @@ __global__ void __launch_bounds__(128) decode_plain_kernel(const DecodeArgs a) {
     }
     float m = -INFINITY, l = 0.f;
     for (int j = warp; j < L; j += 4) {
-        int64_t slot = load_index(a.b_loc, i, static_cast<int64_t>(a.max_input_len) - L + j);
+        int64_t slot = token_slot(a, i, L, j);
         if (slot < 0 || slot >= a.slots) {
             if (lane == 0) report_status(a.status, 1);
             continue;
@@ -635,7 +644,7 @@ __global__ void __launch_bounds__(128) decode_plain_kernel(const DecodeArgs a) {
         const int64_t col = col0 + j;
         float sc;
         if (kHasK) {
-            const T* kp = static_cast<const T*>(a.kmat) + slot * a.k_s0 + static_cast<int64_t>(h) * a.k_s1;
+            const T* kp = static_cast<const T*>(a.kmat) + slot * a.k_s0 + static_cast<int64_t>(hkv) * a.k_s1;
             float part = 0.f;
 #pragma unroll
             for (int r = 0; r < R; ++r) {
@@ -658,7 +667,7 @@ __global__ void __launch_bounds__(128) decode_plain_kernel(const DecodeArgs a) {
             const float m_new = fmaxf(m, sc);
             const float alpha = exp2f(m - m_new), pr = exp2f(sc - m_new);
             l = l * alpha + pr;
-            const T* vp = static_cast<const T*>(a.vmat) + slot * a.v_s0 + static_cast<int64_t>(h) * a.v_s1;
+            const T* vp = static_cast<const T*>(a.vmat) + slot * a.v_s0 + static_cast<int64_t>(hkv) * a.v_s1;
 #pragma unroll
             for (int r = 0; r < R; ++r) {
                 const int d = lane + 32 * r;
@@ -714,6 +723,7 @@ int env_int(const char* name, int dflt) {
 // Fills `p` when the arguments qualify for the split path.
 bool make_split_plan(const DecodeArgs& a, int sm_count, int max_smem, SplitPlan& p) {
     if (a.dt == Dt::F64) return false;
+    if (a.kv_group > 1) return false;  // a K/V row shared by several query heads: plain path
     if (env_int("DIOPI_B200_DECODE_PLAIN", 0)) return false;
     const int e = elem_bytes(a.dt);
     const bool has_k = a.mode != DecodeMode::PV, has_v = a.mode != DecodeMode::QK;

@@ -88,6 +88,25 @@ def context_attention(q, k, v, out, b_start_loc, b_seq_len, max_input_len, *, ct
     return out
 
 
+def prompt_flash_attention(query, key, value, attenMask, actualSeqLengths, maxInputLen, numHeads, numKeyValueHeads, dim, *, ctx=None, as_device=None):
+    """Causal prefill over a padded BSH batch; returns a new tensor like query (diopi_functions.py:7951)."""
+    out = torch.empty_like(query)
+    ts = [_t(x, as_device) for x in (out, query, key, value, attenMask)]
+    _call("diopiPromptFlashAttention", ctx, *[_h(t) for t in ts], Sizes(list(actualSeqLengths)), int(maxInputLen), int(numHeads),
+          int(numKeyValueHeads), int(dim))
+    return out
+
+
+def paged_attention(query, key, value, attenMask, actualSeqLengths, numHeads, numKeyValueHeads, dim, blockTable, blockSize, *, ctx=None, as_device=None):
+    """Decode attention over a block-paged KV cache (BSH); returns a new tensor like query (diopi_functions.py:7984)."""
+    out = torch.empty_like(query)
+    ts = [_t(x, as_device) for x in (out, query, key, value, attenMask)]
+    tb = _t(blockTable, as_device)
+    _call("diopiPagedAttention", ctx, *[_h(t) for t in ts], Sizes(list(actualSeqLengths)), int(numHeads), int(numKeyValueHeads), int(dim), _h(tb),
+          int(blockSize))
+    return out
+
+
 def apply_penalty(logits, presence_penalty, frequency_penalty, p_token_ids, p_token_counts, p_cumsum_seq_len,
                   p_max_len_in_batch, *, ctx=None, as_device=None):
     """In-place presence/frequency penalty; returns logits."""

@@ -195,6 +195,21 @@ diopiError_t diopiApplyPenaltyV2(diopiContextHandle_t ctx, diopiTensorHandle_t l
                                  diopiConstTensorHandle_t frequency_penalty, diopiConstTensorHandle_t repetition_penalty,
                                  diopiConstTensorHandle_t p_token_ids, diopiConstTensorHandle_t p_token_counts);
 
+/* Causal prefill over a padded batch in BSH layout: request i owns rows [i*max_input_len, (i+1)*max_input_len)
+ * of query/out [batch*max_input_len, num_heads*dim] and key/value [.., num_kv_heads*dim]; num_kv_heads may divide
+ * num_heads (grouped-query attention). atten_mask is not read (the mask is causal) and actual_seq_lengths gives
+ * the batch size only, as in the reference's golden function. Replaces functions_ext.h:684-686. */
+diopiError_t diopiPromptFlashAttention(diopiContextHandle_t ctx, diopiTensorHandle_t out, diopiConstTensorHandle_t query, diopiConstTensorHandle_t key,
+                                       diopiConstTensorHandle_t value, diopiConstTensorHandle_t atten_mask, diopiSize_t actual_seq_lengths,
+                                       int64_t max_input_len, int64_t num_heads, int64_t num_kv_heads, int64_t dim);
+
+/* Decode attention over a block-paged KV cache, BSH layout: q/out [batch, num_heads*dim], k/v [rows, num_kv_heads*dim],
+ * token j of request i in row block_table[i, j/block_size]*block_size + j%block_size, lengths given on the host.
+ * atten_mask is not read. Replaces functions_ext.h:616-618. */
+diopiError_t diopiPagedAttention(diopiContextHandle_t ctx, diopiTensorHandle_t out, diopiConstTensorHandle_t q, diopiConstTensorHandle_t k,
+                                 diopiConstTensorHandle_t v, diopiConstTensorHandle_t atten_mask, diopiSize_t actual_seq_lengths, int64_t num_heads,
+                                 int64_t num_kv_heads, int64_t dim, diopiConstTensorHandle_t block_table, int64_t block_size);
+
 /* Extension (not in the DIOPI headers): the fused decode step. Equivalent to
  * diopiTokenAttentionInference followed by diopiTokenSoftmaxReduceVInference on
  * the same index tensors, but the logits never reach memory: one pass over the

@@ -186,3 +186,41 @@ def apply_penalty_v2(logits, presence_penalty, frequency_penalty, repetition_pen
     rep = rep - p_token_counts * frequency_penalty - presence_penalty
     flat[ids] = rep
     return logits
+
+
+def prompt_flash_attention(query, key, value, atten_mask, actual_seq_lengths, max_input_len, num_heads, num_kv_heads, dim, upcast=False):
+    """Padded-batch causal prefill in BSH layout (customized_test.py:751-783): every request has max_input_len rows,
+    all of them computed under the causal mask; the mask argument and the actual lengths are not used there.
+    num_kv_heads < num_heads repeats each K/V head (the reference only runs the equal case)."""
+    bs = len(actual_seq_lengths)
+    rows = bs * max_input_len
+    q = query.reshape(rows, num_heads, dim)
+    rep = num_heads // num_kv_heads
+    k = key.reshape(rows, num_kv_heads, dim).repeat_interleave(rep, dim=1)
+    v = value.reshape(rows, num_kv_heads, dim).repeat_interleave(rep, dim=1)
+    start = torch.arange(bs, dtype=torch.int32) * max_input_len
+    lens = torch.full((bs,), max_input_len, dtype=torch.int32)
+    out = torch.zeros(rows, num_heads, dim, dtype=torch.float32 if upcast else query.dtype)
+    context_attention(q, k, v, out, start, lens, max_input_len, upcast=upcast)
+    return out.reshape(rows, num_heads * dim)
+
+
+def paged_attention(query, key, value, atten_mask, actual_seq_lengths, num_heads, num_kv_heads, dim, block_table, block_size, upcast=False):
+    """Decode attention over a block-paged cache: token j of request i is row block_table[i, j // bs] * bs + j % bs.
+    The reference's golden (customized_test.py:785-821) is written for one request whose block table starts at
+    block 0 (rows 0..L-1); this is the same formula for any batch and table, and equals it on that case."""
+    B = len(actual_seq_lengths)
+    rep = num_heads // num_kv_heads
+    k = key.reshape(-1, num_kv_heads, dim).repeat_interleave(rep, dim=1)
+    v = value.reshape(-1, num_kv_heads, dim).repeat_interleave(rep, dim=1)
+    q = query.reshape(B, num_heads, dim)
+    mx = max(int(x) for x in actual_seq_lengths) if B else 0
+    b_loc = torch.zeros(B, max(mx, 1), dtype=torch.int64)
+    for i, L in enumerate(actual_seq_lengths):
+        j = torch.arange(int(L))
+        b_loc[i, mx - int(L):mx] = block_table[i].long()[j // block_size] * block_size + j % block_size
+    lens = torch.tensor([int(x) for x in actual_seq_lengths], dtype=torch.int32)
+    start = torch.cat([torch.zeros(1, dtype=torch.int32), lens.cumsum(0)[:-1].to(torch.int32)]) if B else lens
+    out = torch.zeros(B, num_heads, dim, dtype=torch.float32 if upcast else query.dtype)
+    token_decode_attention(q, k, v, out, b_loc, start, lens, mx, upcast=upcast)
+    return out.reshape(B, num_heads * dim)

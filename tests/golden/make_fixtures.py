@@ -8,8 +8,9 @@ diopi_test/python/configs/diopi_configs.py (index tensors, shapes and values typ
 lines 9053-9078, 9137-9337, 9339-9381, 9517-9610; some head counts and leading extents are cut down so
 that the files stay small) with seeded random float data where the config draws random data, and (b) small seeded cases of the benchmark's shapes.
 context_attention calls ``.cuda()`` on its mask (customized_test.py:16); there is no GPU here, so
-``torch.Tensor.cuda`` is patched to the identity for the duration of this script — the function
-body itself runs unchanged, on CPU.
+``torch.Tensor.cuda`` is patched to the identity for the duration of this script (and, for paged_attention,
+``device="cuda"`` arguments of torch.empty/torch.arange are routed to the CPU) — the function bodies
+themselves run unchanged, on CPU.
 bfloat16 tensors are stored as their uint16 bit patterns (numpy has no bfloat16).
 """
 import sys
@@ -176,3 +177,31 @@ for tag, dt in DT.items():
     c, s_ = randn(8, 1, 128, dtype=dt), randn(8, 1, 128, dtype=dt)
     oq, ok = G.rotary_emb_v2(q.clone(), k.clone(), c, s_, 128)
     save(f"rotary_emb_v2_config_{tag}", query=q, key=k, cos=c, sin=s_, dim=np.array(128), out_query=oq, out_key=ok)
+
+# ---- prompt_flash_attention: diopi_configs.py:9383-9421 (maxInputLen 2, two requests, 32 heads x 128; fp16 only there) ----
+for tag, dt in DT.items():
+    for case, (bs, mlen, heads) in enumerate([(2, 2, 32), (3, 70, 2)]):
+        q, k, v = (randn(bs * mlen, heads * 128, dtype=dt) for _ in range(3))
+        mask = torch.zeros(bs, mlen, mlen, dtype=torch.bool)
+        out = G.prompt_flash_attention(q, k, v, mask, [mlen] * bs, mlen, heads, heads, 128)
+        save(f"prompt_flash_attention_config{case}_{tag}", query=q, key=k, value=v, batch=np.array(bs), max_input_len=np.array(mlen), heads=np.array(heads), out=out)
+
+# paged_attention also names device="cuda" in torch.empty/torch.arange; route those to the CPU for this script
+def _cpu_device(fn):
+    def wrapped(*a, **k):
+        if k.get("device") == "cuda":
+            k["device"] = "cpu"
+        return fn(*a, **k)
+    return wrapped
+
+
+torch.empty = _cpu_device(torch.empty)
+torch.arange = _cpu_device(torch.arange)
+
+# ---- paged_attention: diopi_configs.py:9423-9468 (one request of length 5, block table [[0, 1]], block size 128) ----
+for tag, dt in DT.items():
+    heads = 32 if tag == "f16" else 4
+    q = randn(1, heads * 128, dtype=dt)
+    k, v = randn(1026, heads * 128, dtype=dt)[:300], randn(1026, heads * 128, dtype=dt)[:300]   # only rows < 256 are addressable
+    out = G.paged_attention(q, k, v, torch.zeros(1, 1, 5, dtype=torch.bool), [5], heads, heads, 128, torch.tensor([[0, 1]], dtype=torch.int32), 128)
+    save(f"paged_attention_config_{tag}", query=q, key=k[:8], value=v[:8], heads=np.array(heads), out=out)

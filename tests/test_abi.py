@@ -28,7 +28,7 @@ def nm(lib, flag):
 
 def test_header_lists_the_hot_path():
     want = {"diopiDestIndexCopyKV", "diopiTokenAttentionInference", "diopiTokenSoftmaxReduceVInference", "diopiRMSNorm", "diopiRotaryEmbedding",
-            "diopiApplyPenalty", "diopiContextAttentionInference", "diopiRotaryEmbeddingV2", "diopiApplyPenaltyV2", "diopiGetVendorName", "diopiGetImplVersion", "diopiGetLastErrorString"}
+            "diopiApplyPenalty", "diopiContextAttentionInference", "diopiRotaryEmbeddingV2", "diopiApplyPenaltyV2", "diopiPromptFlashAttention", "diopiPagedAttention", "diopiGetVendorName", "diopiGetImplVersion", "diopiGetLastErrorString"}
     assert want <= set(declared_exports())
 
 

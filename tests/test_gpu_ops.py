@@ -529,3 +529,64 @@ def test_context_attention_ragged(F, dtype, H, D, lens):
     out2 = torch.zeros_like(out)
     F.context_attention(q.cuda(), k.cuda(), v.cuda(), out2, st.long().cuda(), lens_t.long().cuda(), 1)
     assert torch.equal(out2, out)
+
+
+# ------------------------------------------------------------------ padded-batch prefill (BSH) with grouped-query heads
+@pytest.mark.parametrize("name", fixture_names("prompt_flash_attention"))
+def test_prompt_flash_attention_fixture(F, name):
+    f = load_fixture(name)
+    bs, mlen, heads = f["batch"], f["max_input_len"], f["heads"]
+    q, k, v = cuda(f["query"], f["key"], f["value"])
+    out = F.prompt_flash_attention(q, k, v, None, [mlen] * bs, mlen, heads, heads, 128)
+    close(out, f["out"])
+    out3 = F.prompt_flash_attention(q.view(bs, mlen, -1), k.view(bs, mlen, -1), v.view(bs, mlen, -1), None, [mlen] * bs, mlen, heads, heads, 128)
+    assert torch.equal(out3.view_as(out), out)
+
+
+@pytest.mark.parametrize("dtype,dim", [(torch.float16, 128), (torch.bfloat16, 128), (torch.float32, 64)])
+def test_prompt_flash_attention_grouped_heads(F, dtype, dim):
+    g = torch.Generator().manual_seed(17)
+    bs, mlen, heads, kv_heads = 2, 200, 8, 2
+    q = (torch.randn(bs * mlen, heads * dim, generator=g) * 0.3).to(dtype)
+    k = (torch.randn(bs * mlen, kv_heads * dim, generator=g) * 0.3).to(dtype)
+    v = torch.randn(bs * mlen, kv_heads * dim, generator=g).to(dtype)
+    want = golden.prompt_flash_attention(q, k, v, None, [mlen] * bs, mlen, heads, kv_heads, dim, upcast=True)
+    out = F.prompt_flash_attention(q.cuda(), k.cuda(), v.cuda(), None, [mlen] * bs, mlen, heads, kv_heads, dim)
+    close(out, want, dtype)
+
+
+# ------------------------------------------------------------------ decode over a block-paged cache (BSH)
+@pytest.mark.parametrize("name", fixture_names("paged_attention"))
+def test_paged_attention_fixture(F, name):
+    f = load_fixture(name)
+    heads = f["heads"]
+    table = torch.tensor([[0, 1]], dtype=torch.int32).cuda()
+    out = F.paged_attention(f["query"].cuda(), f["key"].cuda(), f["value"].cuda(), None, [5], heads, heads, 128, table, 128)
+    close(out, f["out"])
+
+
+@pytest.mark.parametrize("dtype,heads,kv_heads,dim,block", [(torch.float16, 32, 32, 128, 16), (torch.bfloat16, 8, 8, 64, 128), (torch.float16, 8, 2, 128, 16),
+                                                            (torch.float32, 4, 1, 64, 7)])
+def test_paged_attention_batches(F, dtype, heads, kv_heads, dim, block):
+    g = torch.Generator().manual_seed(heads * 7 + block)
+    lens = [1, 3 * block, 0, 5 * block + 3, block - 1 if block > 1 else 1]
+    B = len(lens)
+    nblocks = sum((L + block - 1) // block for L in lens) + 3
+    rows = nblocks * block
+    k = (torch.randn(rows, kv_heads * dim, generator=g) * 0.5).to(dtype)
+    v = torch.randn(rows, kv_heads * dim, generator=g).to(dtype)
+    q = torch.randn(B, heads * dim, generator=g).to(dtype)
+    perm = torch.randperm(nblocks, generator=g)
+    width = max((L + block - 1) // block for L in lens)
+    table = torch.zeros(B, width, dtype=torch.int32)
+    used = 0
+    for i, L in enumerate(lens):
+        nb = (L + block - 1) // block
+        table[i, :nb] = perm[used:used + nb].to(torch.int32)
+        used += nb
+    want = golden.paged_attention(q, k, v, None, lens, heads, kv_heads, dim, table, block, upcast=True)
+    out = F.paged_attention(q.cuda(), k.cuda(), v.cuda(), None, lens, heads, kv_heads, dim, table.cuda(), block)
+    close(out, want, dtype)
+    assert torch.count_nonzero(out[2]) == 0   # the empty request
+    out64 = F.paged_attention(q.cuda(), k.cuda(), v.cuda(), None, lens, heads, kv_heads, dim, table.long().cuda(), block)
+    assert torch.equal(out64, out)

@@ -115,3 +115,19 @@ def test_rms_norm(name):
     f = load_fixture(name)
     got = golden.rms_norm(f["x"], tuple(f["normalized_shape"].tolist()), f["weight"], f.get("bias"), f["eps"])
     close(got, f["out"])
+
+
+@pytest.mark.parametrize("name", fixture_names("prompt_flash_attention"))
+def test_prompt_flash_attention(name):
+    f = load_fixture(name)
+    bs, mlen, heads = f["batch"], f["max_input_len"], f["heads"]
+    got = golden.prompt_flash_attention(f["query"], f["key"], f["value"], None, [mlen] * bs, mlen, heads, heads, 128)
+    close(got, f["out"])
+
+
+@pytest.mark.parametrize("name", fixture_names("paged_attention"))
+def test_paged_attention(name):
+    f = load_fixture(name)
+    heads = f["heads"]
+    got = golden.paged_attention(f["query"], f["key"], f["value"], None, [5], heads, heads, 128, torch.tensor([[0, 1]], dtype=torch.int32), 128)
+    close(got, f["out"])

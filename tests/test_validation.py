@@ -112,6 +112,26 @@ def test_v2_validation(F):
     fails(ERROR_OCCURRED, F.apply_penalty_v2, lg, pen.half(), pen, pen, ids, ids, match="share a dtype")
 
 
+def test_prompt_flash_attention_validation(F):
+    q = torch.zeros(6, 4 * 16, dtype=torch.float16)
+    kv = torch.zeros(6, 2 * 16, dtype=torch.float16)
+    fails(ERROR_OCCURRED, F.prompt_flash_attention, q, kv, kv, None, [3, 3], 3, 4, 3, 16, match="multiple of num_kv_heads")
+    fails(ERROR_OCCURRED, F.prompt_flash_attention, q, kv, kv, None, [3, 3], 4, 4, 2, 16, match="rows; expected")
+    fails(ERROR_OCCURRED, F.prompt_flash_attention, q, kv[:, :16], kv, None, [3, 3], 3, 4, 2, 16, match="last dim of 'key'")
+    fails(DTYPE_NOT_SUPPORTED, F.prompt_flash_attention, q.double(), kv.double(), kv.double(), None, [3, 3], 3, 4, 2, 16)
+
+
+def test_paged_attention_validation(F):
+    q = torch.zeros(2, 4 * 16, dtype=torch.float16)
+    kv = torch.zeros(64, 4 * 16, dtype=torch.float16)
+    tbl = torch.zeros(2, 2, dtype=torch.int32)
+    fails(ERROR_OCCURRED, F.paged_attention, q, kv, kv, None, [3, 3], 4, 3, 16, tbl, 16, match="multiple of num_kv_heads")
+    fails(ERROR_OCCURRED, F.paged_attention, q, kv, kv, None, [3, 40], 4, 4, 16, tbl, 16, match="block table covers")
+    fails(ERROR_OCCURRED, F.paged_attention, q, kv, kv, None, [3, 3], 4, 4, 16, tbl, 0, match="block_size")
+    fails(ERROR_OCCURRED, F.paged_attention, q, kv, kv, None, [3, 3, 3], 4, 4, 16, tbl, 16, match="'q' must be")
+    fails(DTYPE_NOT_SUPPORTED, F.paged_attention, q, kv, kv, None, [3, 3], 4, 4, 16, tbl.float(), 16, match="int32 or int64")
+
+
 def test_context_attention_validation(F):
     q = torch.zeros(8, 2, 16, dtype=torch.float16)
     st, ln = torch.zeros(2, dtype=torch.int32), torch.zeros(2, dtype=torch.int32)
