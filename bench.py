@@ -36,9 +36,9 @@ METRIC = "token_attn_decode_hbm_gbs"
 NOMINAL_HBM_GBS = 8000.0
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum per token of one decode_split_kernel launch, from the ncu capture
-# of the quarter-size case summarised in profiles/decode_split_kernel_cfg2.md (660.2 MB for 40 019 tokens); the
+# of the quarter-size case summarised in profiles/decode_split_kernel_cfg2.md (660.0 MB for 40 019 tokens); the
 # traffic of a launch grows with its token count, so it is scaled by the workload's tokens.
-NCU_TRAFFIC_BYTES_PER_TOKEN = 660.196e6 / 40019
+NCU_TRAFFIC_BYTES_PER_TOKEN = 659.979e6 / 40019
 
 
 def measured_peak():
