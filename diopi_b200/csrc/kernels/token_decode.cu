@@ -29,6 +29,7 @@
 // rows are not 16-byte aligned/dense or D*e/16 is not 8, 16 or 32.
 #include <cfloat>
 #include <cstdlib>
+#include <type_traits>
 #include <mutex>
 
 #include "dev_util.cuh"
@@ -176,6 +177,28 @@ __device__ __forceinline__ int request_len(const DecodeArgs& a, int i) {
     L = L < 0 ? 0 : L;
     L = L > a.max_input_len ? a.max_input_len : L;
     return static_cast<int>(L);
+}
+
+// Sums v[u] over the LPH lanes of a head (lanes lih = 0..LPH-1, LPH-aligned in the warp). On return lane lih holds
+// the total of token group lih % TPG. Recursive halving: each step hands half of the values to the partner lane, so
+// TPG - 1 + log2(LPH / TPG) shuffles do what TPG butterflies of log2(LPH) steps would.
+template <int TPG, int LPH>
+__device__ __forceinline__ float head_reduce_scatter(float (&v)[TPG], int lih) {
+    static_assert(LPH >= TPG, "a head has at least as many lanes as a tile has token groups");
+#pragma unroll
+    for (int o = TPG >> 1; o > 0; o >>= 1) {  // bit o of the lane picks the half it keeps
+        const bool upper = (lih & o) != 0;
+#pragma unroll
+        for (int i = 0; i < o; ++i) {
+            const float send = upper ? v[i] : v[i + o];
+            const float keep = upper ? v[i + o] : v[i];
+            v[i] = keep + __shfl_xor_sync(0xffffffffu, send, o);
+        }
+    }
+    float r = v[0];
+#pragma unroll
+    for (int o = TPG; o < LPH; o <<= 1) r += __shfl_xor_sync(0xffffffffu, r, o);
+    return r;
 }
 
 template <typename T, int LPH, int MODE, int TPG>
@@ -353,6 +376,30 @@ __global__ void __launch_bounds__(kThreads, 1) decode_split_kernel(const DecodeA
         int64_t att_col0 = 0;
         uint32_t red_phase = 0;
 
+        // PV mode reads the stored logits one tile ahead of their use (a second walk over the same tiles)
+        StageWalk ahead;
+        int lg_req = 0, lg_j0 = 0, lg_cnt = 0, lg_cur_req = -1;
+        bool lg_last = false, lg_have = false;
+        int64_t lg_col0 = 0;
+        float lg_next = -INFINITY;
+        auto fetch_logit = [&]() -> float {
+            if (lg_req != lg_cur_req) {
+                lg_cur_req = lg_req;
+                lg_col0 = load_index(a.b_start, lg_req);
+            }
+            const int t = g + lih * p.G;
+            const int64_t col = lg_col0 + lg_j0 + t;
+            float v = -INFINITY;
+            if (lih < TPG && t < lg_cnt && col >= 0 && col < a.att_cols)
+                v = Cvt<T>::to_f(static_cast<const T*>(a.att)[static_cast<int64_t>(h) * a.att_s0 + col * a.att_s1]) * kLog2e;
+            return v;
+        };
+        if (!kHasK) {
+            ahead.init(pre, a.B, t0, t1);
+            lg_have = ahead.next(TT, lg_req, lg_j0, lg_cnt, lg_last);
+            if (lg_have) lg_next = fetch_logit();
+        }
+
         StageWalk walk;
         walk.init(pre, a.B, t0, t1);
         int req, j0, cnt;
@@ -378,75 +425,86 @@ __global__ void __launch_bounds__(kThreads, 1) decode_split_kernel(const DecodeA
                         for (int e = 0; e < EPC; ++e) qreg[e] = Cvt<T>::to_f(qp[e]) * qscale;
                     }
                 }
-                if (!kFused) att_col0 = load_index(a.b_start, req);
+                if (MODE == static_cast<int>(DecodeMode::QK)) att_col0 = load_index(a.b_start, req);
             }
 
             float sc[TPG];
             if (!kHasK) {
-                // Stored logits: fetch them before blocking on the V rows.
+                // Stored logits: lane u of a head holds token group u of this tile (loaded a tile ago); hand them
+                // round the head's lanes, then start the load for the next tile so that it flies during this one.
+                const float lg_cur = lg_next;
+                lg_have = ahead.next(TT, lg_req, lg_j0, lg_cnt, lg_last);
+                if (lg_have) lg_next = fetch_logit();
 #pragma unroll
-                for (int u = 0; u < TPG; ++u) {
-                    const int t = g + u * p.G;
-                    const int64_t col = att_col0 + j0 + t;
-                    sc[u] = -INFINITY;
-                    if (t < cnt && col >= 0 && col < a.att_cols)
-                        sc[u] = Cvt<T>::to_f(static_cast<const T*>(a.att)[static_cast<int64_t>(h) * a.att_s0 + col * a.att_s1]) * kLog2e;
-                }
+                for (int u = 0; u < TPG; ++u) sc[u] = __shfl_sync(0xffffffffu, lg_cur, (lane & ~(LPH - 1)) + u);
             }
             // token group u sits in ring slot u / ups; a slot is waited for right before its first use
             const unsigned char* slot_ptr[TPG];
             uint32_t empty_bar[TPG];
+            const bool full_tile = cnt == TT;  // every token group of the tile holds a token (all but a request's last tile)
+            // K: this thread's 16 bytes of each row against its 16 bytes of q. A full tile has no per-token test,
+            // so the TPG loads and dot products are independent straight-line code.
+            auto dots = [&](auto full_c) {
+                constexpr bool kFull = decltype(full_c)::value;
 #pragma unroll
-            for (int u = 0; u < TPG; ++u) {
-                if ((u & ups_mask) == 0) {
-                    const int s = ring;
-                    const uint32_t parity = ring_phase;
-                    if (++ring == p.nstages) {
-                        ring = 0;
-                        ring_phase ^= 1u;
+                for (int u = 0; u < TPG; ++u) {
+                    if ((u & ups_mask) == 0) {
+                        const int s = ring;
+                        const uint32_t parity = ring_phase;
+                        if (++ring == p.nstages) {
+                            ring = 0;
+                            ring_phase ^= 1u;
+                        }
+                        slot_ptr[u] = smem + static_cast<size_t>(s) * p.stage_bytes + my_off;
+                        empty_bar[u] = smem_u32(&bars[p.nstages + s]);
+                        if (ok && !mbar_wait(smem_u32(&bars[s]), parity, give_up)) ok = false;
+                    } else {
+                        slot_ptr[u] = slot_ptr[u - 1] + group_step;
+                        empty_bar[u] = empty_bar[u - 1];
                     }
-                    slot_ptr[u] = smem + static_cast<size_t>(s) * p.stage_bytes + my_off;
-                    empty_bar[u] = smem_u32(&bars[p.nstages + s]);
-                    if (ok && !mbar_wait(smem_u32(&bars[s]), parity, give_up)) ok = false;
-                } else {
-                    slot_ptr[u] = slot_ptr[u - 1] + group_step;
-                    empty_bar[u] = empty_bar[u - 1];
-                }
-                if (kHasK) {
-                    const int t = g + u * p.G;
-                    float part = 0.f;
-                    if (ok && t < cnt) {
-                        const uint4 kv = *reinterpret_cast<const uint4*>(slot_ptr[u]);
-                        float f[EPC];
-                        unpack16<T>(kv, f);
+                    if (kHasK) {
+                        float part = 0.f;
+                        if (kFull || (ok && g + u * p.G < cnt)) {
+                            const uint4 kv = *reinterpret_cast<const uint4*>(slot_ptr[u]);
+                            float f[EPC];
+                            unpack16<T>(kv, f);
 #pragma unroll
-                        for (int e = 0; e < EPC; ++e) part = fmaf(qreg[e], f[e], part);
+                            for (int e = 0; e < EPC; ++e) part = fmaf(qreg[e], f[e], part);
+                        }
+                        sc[u] = part;
                     }
-#pragma unroll
-                    for (int o = LPH / 2; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
-                    sc[u] = (t < cnt) ? part : -INFINITY;
                 }
-            }
+            };
+            if (full_tile) dots(std::true_type{}); else dots(std::false_type{});
             ok = __all_sync(0xffffffffu, ok ? 1 : 0) != 0;  // the whole warp leaves together
             if (!ok) break;
 
-            if (MODE == static_cast<int>(DecodeMode::QK)) {
-                if (real && lih == 0) {
-#pragma unroll
-                    for (int u = 0; u < TPG; ++u) {
-                        const int t = g + u * p.G;
+            if (kHasK) {
+                // lane lih of a head now holds the finished sum of token group lih % TPG
+                const float mine = head_reduce_scatter<TPG, LPH>(sc, lih);
+                if (MODE == static_cast<int>(DecodeMode::QK)) {
+                    // the TPG stores of a head are one instruction, and with one token group per tile one run of columns
+                    if (real && lih < TPG) {
+                        const int t = g + lih * p.G;
                         const int64_t col = att_col0 + j0 + t;
                         if (t < cnt && col >= 0 && col < a.att_cols)
-                            static_cast<T*>(a.att)[static_cast<int64_t>(h) * a.att_s0 + col * a.att_s1] = Cvt<T>::from_f(sc[u] / sqrt_d);
+                            static_cast<T*>(a.att)[static_cast<int64_t>(h) * a.att_s0 + col * a.att_s1] = Cvt<T>::from_f(mine / sqrt_d);
+                    }
+                    __syncwarp();
+                    if (lane == 0) {
+#pragma unroll
+                        for (int u = 0; u < TPG; ++u)
+                            if ((u & ups_mask) == ups_mask) mbar_arrive(empty_bar[u]);
+                    }
+                } else {
+#pragma unroll
+                    for (int u = 0; u < TPG; ++u) {
+                        const float all = __shfl_sync(0xffffffffu, mine, (lane & ~(LPH - 1)) + u);
+                        sc[u] = (full_tile || g + u * p.G < cnt) ? all : -INFINITY;
                     }
                 }
-                __syncwarp();
-                if (lane == 0) {
-#pragma unroll
-                    for (int u = 0; u < TPG; ++u)
-                        if ((u & ups_mask) == ups_mask) mbar_arrive(empty_bar[u]);
-                }
-            } else {
+            }
+            if (kHasV) {
                 float m_new = m;
 #pragma unroll
                 for (int u = 0; u < TPG; ++u) m_new = fmaxf(m_new, sc[u]);
@@ -455,24 +513,27 @@ __global__ void __launch_bounds__(kThreads, 1) decode_split_kernel(const DecodeA
                 l *= alpha;
 #pragma unroll
                 for (int e = 0; e < EPC; ++e) acc[e] *= alpha;
+                auto weighted_v = [&](auto full_c) {
+                    constexpr bool kFull = decltype(full_c)::value;
 #pragma unroll
-                for (int u = 0; u < TPG; ++u) {
-                    const int t = g + u * p.G;
-                    if (t < cnt) {
-                        const float pr = exp2f(sc[u] - m_ref);
-                        l += pr;
-                        const uint4 vv = *reinterpret_cast<const uint4*>(slot_ptr[u] + v_off);
-                        float f[EPC];
-                        unpack16<T>(vv, f);
+                    for (int u = 0; u < TPG; ++u) {
+                        if (kFull || g + u * p.G < cnt) {
+                            const float pr = exp2f(sc[u] - m_ref);
+                            l += pr;
+                            const uint4 vv = *reinterpret_cast<const uint4*>(slot_ptr[u] + v_off);
+                            float f[EPC];
+                            unpack16<T>(vv, f);
 #pragma unroll
-                        for (int e = 0; e < EPC; ++e) acc[e] = fmaf(pr, f[e], acc[e]);
+                            for (int e = 0; e < EPC; ++e) acc[e] = fmaf(pr, f[e], acc[e]);
+                        }
+                        // last token group of a ring slot: the slot is done for the whole warp, hand it back
+                        if ((u & ups_mask) == ups_mask) {
+                            __syncwarp();
+                            if (lane == 0) mbar_arrive(empty_bar[u]);
+                        }
                     }
-                    // last token group of a ring slot: the slot is done for the whole warp, hand it back
-                    if ((u & ups_mask) == ups_mask) {
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive(empty_bar[u]);
-                    }
-                }
+                };
+                if (full_tile) weighted_v(std::true_type{}); else weighted_v(std::false_type{});
                 m = m_new;
             }
 
