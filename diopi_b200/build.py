@@ -37,6 +37,7 @@ IMPL_SOURCES = [
     "kernels/dest_index_copy.cu",
     "kernels/token_decode.cu",
     "kernels/rms_norm.cu",
+    "kernels/rms_norm_backward.cu",
     "kernels/rotary.cu",
     "kernels/apply_penalty.cu",
     "kernels/context_attention.cu",

@@ -415,6 +415,65 @@ B200_EXPORT diopiError_t diopiRMSNorm(diopiContextHandle_t ctx, diopiTensorHandl
     });
 }
 
+// diopiRMSNormBackward (proto/include/diopi/functions_ext.h:62-65). `eps` and `bias` carry no information the
+// derivative needs (inv_rms is given); grad_bias may be null when the forward call had no bias.
+B200_EXPORT diopiError_t diopiRMSNormBackward(diopiContextHandle_t ctx, diopiTensorHandle_t grad_input, diopiTensorHandle_t grad_weight,
+                                              diopiTensorHandle_t grad_bias, diopiConstTensorHandle_t grad_output, diopiConstTensorHandle_t input,
+                                              diopiConstTensorHandle_t weight, diopiConstTensorHandle_t bias, diopiConstTensorHandle_t inv_rms,
+                                              diopiSize_t normalized_shape, double /*eps*/) {
+    return guard("diopiRMSNormBackward", [&] {
+        TensorView dx = view_of(grad_input, "grad_input"), dw = view_of(grad_weight, "grad_weight"), gv = view_of(grad_output, "grad_output");
+        TensorView xv = view_of(input, "input"), wv = view_of(weight, "weight"), iv = view_of(inv_rms, "inv_rms");
+        TensorView db = view_of(grad_bias, "grad_bias", /*optional=*/true), bv = view_of(bias, "bias", /*optional=*/true);
+        k::RmsNormBwdArgs a{};
+        a.dt = float_dt(xv, "input", true);
+        same_dtype(dx, "grad_input", xv, "input");
+        same_dtype(gv, "grad_output", xv, "input");
+        same_dtype(wv, "weight", xv, "input");
+        same_dtype(dw, "grad_weight", xv, "input");
+        if (db.defined) same_dtype(db, "grad_bias", xv, "input");
+        B200_REQUIRE(normalized_shape.len >= 1 && normalized_shape.len <= xv.ndim && normalized_shape.data != nullptr,
+                     "normalized_shape must name between 1 and %d trailing dims", xv.ndim);
+        int64_t n2 = 1;
+        for (int64_t i = 0; i < normalized_shape.len; ++i) {
+            const int64_t want = normalized_shape.data[i];
+            const int64_t have = xv.shape[xv.ndim - normalized_shape.len + i];
+            B200_REQUIRE(want == have, "normalized_shape[%ld] = %ld does not match the input's trailing dim %ld", (long)i, (long)want, (long)have);
+            n2 *= want;
+        }
+        a.n2 = n2;
+        a.n1 = n2 > 0 ? xv.numel / n2 : 0;
+        B200_REQUIRE(dx.numel == xv.numel && gv.numel == xv.numel, "'grad_input' and 'grad_output' must have the shape of 'input'");
+        B200_REQUIRE(wv.numel == n2 && dw.numel == n2, "'weight' and 'grad_weight' must have %ld elements (normalized_shape)", (long)n2);
+        if (db.defined) B200_REQUIRE(db.numel == n2, "'grad_bias' must have %ld elements (normalized_shape), got %ld", (long)n2, (long)db.numel);
+        if (bv.defined) B200_REQUIRE(bv.numel == n2, "'bias' must have %ld elements (normalized_shape), got %ld", (long)n2, (long)bv.numel);
+        if (n2 == 0) return;
+        B200_REQUIRE(iv.numel == a.n1, "'inv_rms' must have one element per normalised row (%ld), got %ld", (long)a.n1, (long)iv.numel);
+        B200_REQUIRE(xv.contiguous() && gv.contiguous() && dx.contiguous() && wv.contiguous() && dw.contiguous() && iv.contiguous() &&
+                         (!db.defined || db.contiguous()),
+                     "grad_input, grad_weight, grad_bias, grad_output, input, weight and inv_rms must be contiguous");
+        if (iv.dtype == diopi_dtype_float32)
+            a.inv_dt = k::Dt::F32;
+        else if (iv.dtype == xv.dtype)
+            a.inv_dt = a.dt;
+        else
+            fail(diopiDtypeNotSupported, "'inv_rms' has dtype %s; expected float32 or the input's dtype (%s)", dtype_name(iv.dtype), dtype_name(xv.dtype));
+        a.g = gv.data;
+        a.x = xv.data;
+        a.weight = wv.data;
+        a.inv_rms = iv.data;
+        a.dx = dx.data;
+        a.dw = dw.data;
+        a.db = db.defined ? db.data : nullptr;
+        cudaStream_t st = stream_of(ctx);
+        const DeviceInfo& di = device_info();
+        a.parts = k::rms_norm_bwd_parts(a, di.sm_count);
+        if (a.parts > 0) a.ws = static_cast<float*>(workspace(ctx, static_cast<int64_t>(2) * a.parts * a.n2 * static_cast<int64_t>(sizeof(float))));
+        k::launch_rms_norm_bwd(a, st);
+        B200_CUDA(cudaGetLastError());
+    });
+}
+
 // ---------------------------------------------------------------------------------------------
 // The fused decode step for callers that cannot hand out scratch memory.
 //

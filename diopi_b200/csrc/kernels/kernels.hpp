@@ -78,6 +78,24 @@ struct RmsNormArgs {
 };
 void launch_rms_norm(const RmsNormArgs& a, int sm_count, cudaStream_t st);
 
+struct RmsNormBwdArgs {
+    Dt dt;
+    const void* g;        // grad_output [n1, n2] dense
+    const void* x;        // input       [n1, n2] dense
+    const void* weight;   // [n2]
+    const void* inv_rms;  // [n1], saved by the forward call
+    Dt inv_dt;            // F32, F64, or the input's half type
+    void* dx;             // grad_input  [n1, n2]
+    void* dw;             // grad_weight [n2]
+    void* db;             // grad_bias   [n2] or null
+    int64_t n1, n2;
+    float* ws;            // 2 * parts * n2 floats of scratch (partial column sums), or null
+    int parts;            // CTAs of the rows kernel; 0 = the scalar kernels, which need no scratch
+};
+// Number of partial rows the vector path wants for these arguments (0: not eligible, no scratch needed).
+int rms_norm_bwd_parts(const RmsNormBwdArgs& a, int sm_count);
+void launch_rms_norm_bwd(const RmsNormBwdArgs& a, cudaStream_t st);
+
 // ---- rotary embedding -------------------------------------------------------
 constexpr int kRopeMaxDims = 6;
 struct RopeArgs {

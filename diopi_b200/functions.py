@@ -149,3 +149,13 @@ def rms_norm(input, normalized_shape, weight, bias, eps, *, return_inv_rms=False
     tw, tb = _t(weight, as_device), _t(bias, as_device)
     _call("diopiRMSNorm", ctx, _h(ts[0]), _h(ts[1]), _h(ts[2]), Sizes(normalized_shape), _h(tw), _h(tb), float(eps))
     return (out, inv_rms) if return_inv_rms else out
+
+
+def rms_norm_backward(grad_output, input, weight, bias, inv_rms, normalized_shape, eps, *, ctx=None, as_device=None):
+    """Returns (grad_input, grad_weight, grad_bias or None) from the inv_rms a forward call saved."""
+    grad_input = torch.empty_like(input)
+    grad_weight = torch.empty_like(weight)
+    grad_bias = torch.empty_like(bias) if bias is not None else None
+    ts = [_t(x, as_device) for x in (grad_input, grad_weight, grad_bias, grad_output, input, weight, bias, inv_rms)]
+    _call("diopiRMSNormBackward", ctx, *[_h(t) for t in ts], Sizes(normalized_shape), float(eps))
+    return grad_input, grad_weight, grad_bias

@@ -67,7 +67,7 @@ def time_op(fn, iters, warmup, flush):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--op", required=True, choices=["prefill", "rms_norm", "rotary", "penalty", "copy_kv", "qk", "pv", "decode"])
+    ap.add_argument("--op", required=True, choices=["prefill", "rms_norm", "rms_norm_bwd", "rotary", "penalty", "copy_kv", "qk", "pv", "decode"])
     ap.add_argument("--size", default="full", choices=["full", "small"])
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
@@ -85,7 +85,7 @@ def main():
         tf = pf["flops"] / med / 1e9
         rec.update(ms=med, ms_best=best, flops=pf["flops"], tflops=tf, frac_of_burst_peak=tf / tf_burst, frac_of_sustained_peak=tf / tf_sust,
                    lens=pf["lens"].tolist(), unit="TFLOP/s (causal-only FLOPs, fp16)")
-    elif args.op in ("rms_norm", "rotary"):
+    elif args.op in ("rms_norm", "rms_norm_bwd", "rotary"):
         tokens = 8192 if args.size == "full" else 1024
         p = workloads.prenorm(tokens=tokens)
         from .runtime import Sizes, Tensor
@@ -101,6 +101,23 @@ def main():
             invs = [Tensor(torch.empty(tokens, dtype=torch.float32, device="cuda")) for _ in range(sets)]
             wt, ns = Tensor(p["weight"]), Sizes((4096,))
             fns = [(lambda i=i: impl.diopiRMSNorm(ctx.handle, outs[i].handle, invs[i].handle, xs[i].handle, ns, wt.handle, None, 1e-6)) for i in range(sets)]
+        elif args.op == "rms_norm_bwd":
+            x = p["x"]
+            nbytes = 3 * x.numel() * 2 + tokens * 4 + 2 * 4096 * 2
+            _, inv = F.rms_norm(x, (4096,), p["weight"], None, p["eps"], return_inv_rms=True, ctx=ctx)
+            g = torch.randn_like(x)
+            med, best = time_op(lambda: F.rms_norm_backward(g, x, p["weight"], None, inv, (4096,), p["eps"], ctx=ctx), args.iters, args.warmup, flush)
+            ctx.release()
+            xs = [Tensor(x.clone()) for _ in range(sets)]
+            gs = [Tensor(g.clone()) for _ in range(sets)]
+            dxs = [Tensor(torch.empty_like(x)) for _ in range(sets)]
+            dws = [Tensor(torch.empty_like(p["weight"])) for _ in range(sets)]
+            wt, it, ns = Tensor(p["weight"]), Tensor(inv), Sizes((4096,))
+
+            def bwd(i):
+                impl.diopiRMSNormBackward(ctx.handle, dxs[i].handle, dws[i].handle, None, gs[i].handle, xs[i].handle, wt.handle, None, it.handle, ns, 1e-6)
+                ctx.release()
+            fns = [(lambda i=i: bwd(i)) for i in range(sets)]
         else:
             x = p["k_in"].view(tokens, p["heads"], p["head_dim"])
             out = torch.empty_like(x)

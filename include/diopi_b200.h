@@ -182,6 +182,15 @@ diopiError_t diopiRotaryEmbedding(diopiContextHandle_t ctx, diopiTensorHandle_t 
 diopiError_t diopiRMSNorm(diopiContextHandle_t ctx, diopiTensorHandle_t out, diopiTensorHandle_t inv_rms, diopiConstTensorHandle_t input,
                           diopiSize_t normalized_shape, diopiConstTensorHandle_t weight, diopiConstTensorHandle_t bias, double eps);
 
+/* Derivative of diopiRMSNorm given the inv_rms it saved, in fp32 with one rounding at the end:
+ * grad_input = inv_rms * (g * weight) - x * inv_rms^3 * mean(g * weight * x),
+ * grad_weight = sum over rows of g * x * inv_rms, grad_bias = sum over rows of g (grad_bias may be null).
+ * Column sums are added in a fixed order (no atomics). Replaces functions_ext.h:62-65. */
+diopiError_t diopiRMSNormBackward(diopiContextHandle_t ctx, diopiTensorHandle_t grad_input, diopiTensorHandle_t grad_weight,
+                                  diopiTensorHandle_t grad_bias, diopiConstTensorHandle_t grad_output, diopiConstTensorHandle_t input,
+                                  diopiConstTensorHandle_t weight, diopiConstTensorHandle_t bias, diopiConstTensorHandle_t inv_rms,
+                                  diopiSize_t normalized_shape, double eps);
+
 /* In-place rotary embedding on query and key [tokens, heads*dim] in the rotate-half form with cos/sin
  * as wide as a head: x = x*cos + (-x2, x1)*sin, each operation rounded in the tensors' dtype.
  * Replaces functions_ext.h:649-650. */

@@ -166,6 +166,33 @@ def rms_norm(input, normalized_shape, weight, bias=None, eps=1e-6, return_inv_rm
     return y
 
 
+def rms_norm_backward(grad_output, input, weight, normalized_shape, inv_rms=None, eps=1e-6, with_bias=False):
+    """Derivative of rms_norm above in closed form, in fp32 (fp64 for fp64 input) with one rounding at the end:
+    gw = g * weight; grad_input = inv * gw - x * inv^3 * mean(gw * x); grad_weight = sum_rows(g * x * inv);
+    grad_bias = sum_rows(g). The reference's harness obtains the same quantities by torch.autograd.grad on the golden
+    forward function (diopi_test/python/conformance/gen_output.py:172-204); its CUDA path is
+    impl/torch/functions/functions_ext/layer_norm_cuda_kernel.cu:452-717. Returns (grad_input, grad_weight, grad_bias|None)."""
+    acc = torch.float64 if input.dtype == torch.float64 else torch.float32
+    k = len(normalized_shape)
+    n2 = 1
+    for d in normalized_shape:
+        n2 *= int(d)
+    x = input.reshape(-1, n2).to(acc)
+    g = grad_output.reshape(-1, n2).to(acc)
+    w = weight.reshape(1, n2).to(acc)
+    if inv_rms is None:
+        inv = torch.rsqrt(x.pow(2).mean(1, keepdim=True) + eps)
+    else:
+        inv = inv_rms.reshape(-1, 1).to(acc)
+    gw = g * w
+    dx = inv * gw - x * inv.pow(3) * (gw * x).mean(1, keepdim=True)
+    dw = (g * x * inv).sum(0)
+    db = g.sum(0) if with_bias else None
+    shape_w = tuple(input.shape[input.dim() - k:])
+    return (dx.reshape(input.shape).to(input.dtype), dw.reshape(shape_w).to(input.dtype),
+            db.reshape(shape_w).to(input.dtype) if with_bias else None)
+
+
 def rotary_emb_v2(query, key, cos, sin, dim):
     """Rotate-half form on [tokens, heads*dim] query and key with cos/sin as wide as a head, in the
     dtype of the tensors (customized_test.py:843-852). Returns new (query, key)."""

@@ -205,3 +205,26 @@ for tag, dt in DT.items():
     k, v = randn(1026, heads * 128, dtype=dt)[:300], randn(1026, heads * 128, dtype=dt)[:300]   # only rows < 256 are addressable
     out = G.paged_attention(q, k, v, torch.zeros(1, 1, 5, dtype=torch.bool), [5], heads, heads, 128, torch.tensor([[0, 1]], dtype=torch.int32), 128)
     save(f"paged_attention_config_{tag}", query=q, key=k[:8], value=v[:8], heads=np.array(heads), out=out)
+
+# ---- rms_norm backward: the conformance harness takes torch.autograd.grad of the golden forward function
+# (diopi_test/python/conformance/gen_output.py:172-204) with grad_outputs of ones; a seeded random grad_output is
+# stored as well. Shapes follow diopi_configs.py:9137-9263 (leading extents cut down). Own generator, so that the
+# files above do not depend on this section.
+gen_b = torch.Generator().manual_seed(20240608)
+rms_b = [((16,), (16,), 1e-4, False), ((5, 5), (5,), 1e-6, False), ((7, 25, 32), (32,), 1e-6, True), ((3, 64, 64), (64, 64), 1e-6, False),
+         ((3, 2, 4, 7, 8), (7, 8), 1e-2, True), ((9, 256), (256,), 1e-6, True), ((2, 2048), (2048,), 1e-6, False)]
+for tag, dt in {**DT, "f64": torch.float64, "bf16": torch.bfloat16}.items():
+    for case, (xs, ns, eps, with_bias) in enumerate(rms_b):
+        def rb(*shape):
+            return torch.randn(*shape, generator=gen_b).to(dt)
+        x, w = rb(*xs).requires_grad_(True), (1 + 0.1 * torch.randn(*ns, generator=gen_b)).to(dt).requires_grad_(True)
+        b = rb(*ns).requires_grad_(True) if with_bias else None
+        leaves = [x, w] + ([b] if with_bias else [])
+        out = G.rms_norm(x, ns, w, b, eps)
+        ones = torch.autograd.grad([out], leaves, [torch.ones_like(out)], retain_graph=True)
+        g = rb(*xs)
+        rnd = torch.autograd.grad([out], leaves, [g])
+        save(f"rms_norm_backward_config{case}_{tag}", x=x.detach(), weight=w.detach(), bias=b.detach() if with_bias else None, eps=np.array(eps),
+             normalized_shape=np.array(ns), grad_output=g,
+             ones_grad_input=ones[0], ones_grad_weight=ones[1], ones_grad_bias=ones[2] if with_bias else None,
+             grad_input=rnd[0], grad_weight=rnd[1], grad_bias=rnd[2] if with_bias else None)
