@@ -43,6 +43,7 @@ OPS = {
     "diopiApplyPenaltyV2": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
     "diopiRotaryEmbedding": [c_void_p, c_void_p, c_void_p, c_void_p, c_bool, c_bool],
     "diopiRMSNorm": [c_void_p, c_void_p, c_void_p, diopiSize_t, c_void_p, c_void_p, c_double],
+    "diopiRotaryEmbeddingCopyKV": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_bool],
     "diopiRMSNormBackward": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, diopiSize_t, c_double],
 }
 INFO = ["diopiGetVendorName", "diopiGetImplVersion", "diopiGetLastErrorString"]

@@ -415,6 +415,93 @@ B200_EXPORT diopiError_t diopiRMSNorm(diopiContextHandle_t ctx, diopiTensorHandl
     });
 }
 
+// The step in front of decode attention as one call (an addition to the reference's operator set):
+//   diopiRotaryEmbedding(q_out, q, cos, sin, conj, false);
+//   diopiRotaryEmbedding(tmp, k, cos, sin, conj, false); diopiDestIndexCopyKV(k_pool, tmp, dest_loc);
+//   diopiDestIndexCopyKV(v_pool, v, dest_loc);            (skipped when v and v_pool are null)
+// with bit-identical results. Dense [tokens, heads, head_dim] rows with one cos/sin row of head_dim/2 per token run
+// as one kernel that never materialises the rotated key; anything else runs the calls above on context scratch.
+B200_EXPORT diopiError_t diopiRotaryEmbeddingCopyKV(diopiContextHandle_t ctx, diopiTensorHandle_t q_out, diopiTensorHandle_t k_pool, diopiTensorHandle_t v_pool,
+                                                    diopiConstTensorHandle_t q, diopiConstTensorHandle_t kh, diopiConstTensorHandle_t vh,
+                                                    diopiConstTensorHandle_t cos, diopiConstTensorHandle_t sin, diopiConstTensorHandle_t dest_loc, bool conj) {
+    bool composed = false;
+    diopiError_t rc = guard("diopiRotaryEmbeddingCopyKV", [&] {
+        TensorView qo = view_of(q_out, "q_out"), kp = view_of(k_pool, "k_pool"), qv = view_of(q, "q"), kv = view_of(kh, "k");
+        TensorView cv = view_of(cos, "cos"), sv = view_of(sin, "sin"), d = view_of(dest_loc, "dest_loc");
+        TensorView vp = view_of(v_pool, "v_pool", /*optional=*/true), vv = view_of(vh, "v", /*optional=*/true);
+        B200_REQUIRE(vp.defined == vv.defined, "'v' and 'v_pool' must be given together or both be null");
+        k::RopeStoreArgs a{};
+        a.dt = float_dt(qv, "q", true);
+        same_dtype(qo, "q_out", qv, "q");
+        same_dtype(kv, "k", qv, "q");
+        same_dtype(kp, "k_pool", qv, "q");
+        same_dtype(cv, "cos", qv, "q");
+        same_dtype(sv, "sin", qv, "q");
+        if (vv.defined) {
+            same_dtype(vv, "v", qv, "q");
+            same_dtype(vp, "v_pool", qv, "q");
+        }
+        B200_REQUIRE(qv.ndim == 3 && kv.ndim == 3 && qo.ndim == 3 && kp.ndim == 3, "'q', 'q_out', 'k' and 'k_pool' must be [rows, head_num, head_dim]");
+        const int64_t T = qv.shape[0], D = qv.shape[2];
+        B200_REQUIRE(kv.shape[0] == T && kv.shape[2] == D && kp.shape[2] == D && kp.shape[1] == kv.shape[1], "'k' must be [%ld, kv_heads, %ld] and 'k_pool' [slots, kv_heads, %ld]",
+                     (long)T, (long)D, (long)D);
+        for (int i = 0; i < 3; ++i) B200_REQUIRE(qo.shape[i] == qv.shape[i], "'q_out' must have the shape of 'q'");
+        if (vv.defined) {
+            B200_REQUIRE(vv.ndim == 3 && vp.ndim == 3, "'v' and 'v_pool' must be [rows, head_num, head_dim]");
+            for (int i = 0; i < 3; ++i) B200_REQUIRE(vv.shape[i] == kv.shape[i], "'v' must have the shape of 'k'");
+            for (int i = 0; i < 3; ++i) B200_REQUIRE(vp.shape[i] == kp.shape[i], "'v_pool' must have the shape of 'k_pool'");
+        }
+        B200_REQUIRE(D % 2 == 0, "head_dim (%ld) must be even", (long)D);
+        a.dest = index_arg(d, "dest_loc", 1);
+        B200_REQUIRE(d.shape[0] == T, "'dest_loc' has %ld entries for %ld rows", (long)d.shape[0], (long)T);
+        if (T == 0 || D == 0) return;
+        B200_REQUIRE(kp.shape[0] > 0, "'k_pool' has no slots");
+        auto dense = [](const TensorView& t) { return (t.shape[2] == 1 || t.stride[2] == 1) && (t.shape[1] == 1 || t.stride[1] == t.shape[2]); };
+        // cos/sin: exactly one row of D/2 per token ([T, D/2] or [T, 1, D/2]), last dim dense
+        auto table = [&](const TensorView& t, int64_t& s0) {
+            if (t.numel != T * (D / 2) || t.shape[t.ndim - 1] != D / 2 || t.shape[0] != T) return false;
+            if (D / 2 > 1 && t.stride[t.ndim - 1] != 1) return false;
+            s0 = t.stride[0];
+            return true;
+        };
+        const bool one_kernel = dense(qv) && dense(qo) && dense(kv) && dense(kp) && (!vv.defined || (dense(vv) && dense(vp))) && table(cv, a.c_s0) &&
+                                table(sv, a.s_s0);
+        if (one_kernel) {
+            a.q = qv.data; a.q_out = qo.data; a.k = kv.data; a.k_pool = kp.data;
+            a.v = vv.defined ? vv.data : nullptr;
+            a.v_pool = vp.defined ? vp.data : nullptr;
+            a.cos = cv.data; a.sin = sv.data;
+            a.T = T; a.Hq = qv.shape[1]; a.Hk = kv.shape[1]; a.D = D; a.slots = kp.shape[0];
+            a.q_s0 = qv.stride[0]; a.qo_s0 = qo.stride[0]; a.k_s0 = kv.stride[0]; a.kp_s0 = kp.stride[0];
+            a.v_s0 = vv.defined ? vv.stride[0] : 0;
+            a.vp_s0 = vp.defined ? vp.stride[0] : 0;
+            a.conj = conj;
+            a.status = async_status_device_ptr();
+            cudaStream_t st = stream_of(ctx);
+            if (k::launch_rope_store_kv(a, st)) {
+                B200_CUDA(cudaGetLastError());
+                return;
+            }
+        }
+        composed = true;
+    });
+    if (rc != diopiSuccess || !composed) return rc;
+    // The separate calls, each with its own checks and error text.
+    rc = diopiRotaryEmbedding(ctx, q_out, q, cos, sin, conj, false);
+    if (rc != diopiSuccess) return rc;
+    diopiTensorHandle_t tmp = nullptr;
+    diopiSize_t shape{nullptr, 0};
+    diopiDtype_t dt;
+    if (diopiGetTensorShape(kh, &shape) != diopiSuccess || diopiGetTensorDtype(kh, &dt) != diopiSuccess ||
+        diopiRequireTensor(ctx, &tmp, &shape, nullptr, dt, diopi_device) != diopiSuccess || tmp == nullptr)
+        return guard("diopiRotaryEmbeddingCopyKV", [&] { fail(diopiErrorOccurred, "the consumer could not provide a scratch tensor for the rotated key"); });
+    rc = diopiRotaryEmbedding(ctx, tmp, kh, cos, sin, conj, false);
+    if (rc != diopiSuccess) return rc;
+    rc = diopiDestIndexCopyKV(ctx, k_pool, tmp, dest_loc);
+    if (rc != diopiSuccess || vh == nullptr) return rc;
+    return diopiDestIndexCopyKV(ctx, v_pool, vh, dest_loc);
+}
+
 // diopiRMSNormBackward (proto/include/diopi/functions_ext.h:62-65). `eps` and `bias` carry no information the
 // derivative needs (inv_rms is given); grad_bias may be null when the forward call had no bias.
 B200_EXPORT diopiError_t diopiRMSNormBackward(diopiContextHandle_t ctx, diopiTensorHandle_t grad_input, diopiTensorHandle_t grad_weight,

@@ -111,6 +111,21 @@ struct RopeArgs {
 };
 void launch_rope(const RopeArgs& a, cudaStream_t st);
 
+// rope(q) -> q_out, rope(k) -> k_pool[dest], v -> v_pool[dest] in one launch. Rows are dense ([heads, D] contiguous),
+// cos/sin hold one row of D/2 values per token. v and v_pool may both be null.
+struct RopeStoreArgs {
+    Dt dt;
+    const void* q; void* q_out; const void* k; void* k_pool; const void* v; void* v_pool;
+    const void* cos; const void* sin;
+    IndexArg dest;                 // [T]
+    int64_t T, Hq, Hk, D, slots;
+    int64_t q_s0, qo_s0, k_s0, kp_s0, v_s0, vp_s0, c_s0, s_s0;  // stride of dim 0, in elements
+    bool conj;
+    int* status;
+};
+// Returns false (nothing launched) when the arguments do not qualify for the one-launch kernel.
+bool launch_rope_store_kv(const RopeStoreArgs& a, cudaStream_t st);
+
 // In-place rotate-half form on [T, H*dim] query and key with full-width cos/sin (diopiRotaryEmbeddingV2).
 struct RopeV2Args {
     Dt dt;

@@ -34,7 +34,7 @@ __device__ __forceinline__ float load_inv(const void* inv_rms, Dt inv_dt, int64_
 }
 
 template <typename T, int THREADS, int VPT, bool HAS_DB>
-__global__ void __launch_bounds__(THREADS) rms_bwd_rows_kernel(RmsNormBwdArgs a, int n_vec) {
+__global__ void __launch_bounds__(THREADS, (THREADS * VPT * Vec16<T>::N <= 4096 && THREADS == 512) ? 2 : 1) rms_bwd_rows_kernel(RmsNormBwdArgs a, int n_vec) {
     constexpr int N = Vec16<T>::N;
     constexpr int W = THREADS / 32;
     __shared__ float s_part[2][W];
@@ -54,16 +54,27 @@ __global__ void __launch_bounds__(THREADS) rms_bwd_rows_kernel(RmsNormBwdArgs a,
     }
     const float inv_n2 = 1.0f / static_cast<float>(a.n2);
     int buf = 0;
-    for (int64_t row = blockIdx.x; row < a.n1; row += gridDim.x) {
+    // The next row's vectors are requested before this row's reduction, so that loads stay in flight throughout.
+    uint4 xnext[VPT], gnext[VPT];
+    auto fetch = [&](int64_t row) {
         const uint4* x4 = reinterpret_cast<const uint4*>(static_cast<const T*>(a.x) + row * a.n2);
         const uint4* g4 = reinterpret_cast<const uint4*>(static_cast<const T*>(a.g) + row * a.n2);
-        uint4 xraw[VPT], graw[VPT];
 #pragma unroll
         for (int v = 0; v < VPT; ++v) {
             const int idx = threadIdx.x + v * THREADS;
-            xraw[v] = idx < n_vec ? __ldcs(x4 + idx) : make_uint4(0, 0, 0, 0);
-            graw[v] = idx < n_vec ? __ldcs(g4 + idx) : make_uint4(0, 0, 0, 0);
+            xnext[v] = idx < n_vec ? __ldcs(x4 + idx) : make_uint4(0, 0, 0, 0);
+            gnext[v] = idx < n_vec ? __ldcs(g4 + idx) : make_uint4(0, 0, 0, 0);
         }
+    };
+    if (blockIdx.x < a.n1) fetch(blockIdx.x);
+    for (int64_t row = blockIdx.x; row < a.n1; row += gridDim.x) {
+        uint4 xraw[VPT], graw[VPT];
+#pragma unroll
+        for (int v = 0; v < VPT; ++v) {
+            xraw[v] = xnext[v];
+            graw[v] = gnext[v];
+        }
+        if (row + gridDim.x < a.n1) fetch(row + gridDim.x);
         const float inv = load_inv<T>(a.inv_rms, a.inv_dt, row);
         float c = 0.f;
 #pragma unroll
@@ -123,6 +134,7 @@ __global__ void __launch_bounds__(256) rms_bwd_colsum_kernel(RmsNormBwdArgs a, i
     const int64_t col = static_cast<int64_t>(blockIdx.x) * 32 + lane;
     const float* src = a.ws + static_cast<size_t>(blockIdx.y) * parts * a.n2;
     float acc = 0.f;
+    asm volatile("griddepcontrol.wait;" ::: "memory");  // no-op for a plain launch
     if (col < a.n2) {
 #pragma unroll 4
         for (int p = warp; p < parts; p += 8) acc += src[static_cast<size_t>(p) * a.n2 + col];
@@ -261,8 +273,18 @@ void launch_typed(const RmsNormBwdArgs& a, cudaStream_t st) {
     if (a.parts > 0 && a.ws != nullptr && rows_config<T>(a, c)) {
         const int n_vec = static_cast<int>(a.n2 / Vec16<T>::N);
         rows_kernel<T>(c, a.db != nullptr)<<<a.parts, c.threads, 0, st>>>(a, n_vec);
-        dim3 grid(static_cast<unsigned>((a.n2 + 31) / 32), a.db ? 2 : 1);
-        rms_bwd_colsum_kernel<T><<<grid, 256, 0, st>>>(a, a.parts);
+        // Programmatic dependent launch: the column-sum kernel's launch overlaps the rows kernel; it waits for the
+        // rows kernel's writes before its first load.
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(static_cast<unsigned>((a.n2 + 31) / 32), a.db ? 2 : 1);
+        cfg.blockDim = dim3(256);
+        cfg.stream = st;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        cudaLaunchKernelEx(&cfg, rms_bwd_colsum_kernel<T>, a, a.parts);
         return;
     }
     rms_bwd_dx_scalar_kernel<T, float><<<static_cast<unsigned>((a.n1 + 7) / 8), 256, 0, st>>>(a);

@@ -221,6 +221,86 @@ __global__ void __launch_bounds__(256) rope_v2_f64_kernel(RopeV2Args a, int64_t 
     }
 }
 
+// The step in front of decode attention in one launch: q_out = rope(q); k_pool[dest_loc[t]] = rope(k[t]);
+// v_pool[dest_loc[t]] = v[t]. The same arithmetic as rope_vec_kernel and the same slot rule as the row scatter
+// (negative slots count from the end, out-of-range slots are reported and skipped), so the result equals the
+// four separate calls bit for bit; the rotated key is never written to a tensor of its own.
+// One thread per 16-byte vector pair (q, k) or per 16-byte vector (v).
+template <typename T>
+__global__ void __launch_bounds__(256) rope_store_kv_kernel(RopeStoreArgs a, uint32_t vph, uint32_t per_token, uint32_t total) {
+    constexpr int N = Vec16<T>::N;
+    const uint32_t wq = static_cast<uint32_t>(a.Hq) * vph, wk = static_cast<uint32_t>(a.Hk) * vph;
+    const uint32_t stride = gridDim.x * blockDim.x;
+    for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+        const uint32_t t = i / per_token;
+        uint32_t r = i - t * per_token;
+        const T* src;
+        T* dst;
+        if (r < wq) {
+            const uint32_t h = r / vph;
+            r -= h * vph;
+            src = static_cast<const T*>(a.q) + static_cast<int64_t>(t) * a.q_s0 + static_cast<int64_t>(h) * a.D;
+            dst = static_cast<T*>(a.q_out) + static_cast<int64_t>(t) * a.qo_s0 + static_cast<int64_t>(h) * a.D;
+        } else {
+            int64_t slot = load_index(a.dest, t);
+            if (slot < 0) slot += a.slots;
+            if (slot < 0 || slot >= a.slots) {
+                if (r == wq) report_status(a.status, 1);
+                continue;
+            }
+            r -= wq;
+            if (r >= wk) {  // a vector of the value row: plain copy
+                r -= wk;
+                const uint4* vs = reinterpret_cast<const uint4*>(static_cast<const T*>(a.v) + static_cast<int64_t>(t) * a.v_s0) + r;
+                uint4* vd = reinterpret_cast<uint4*>(static_cast<T*>(a.v_pool) + slot * a.vp_s0) + r;
+                *vd = __ldcs(vs);
+                continue;
+            }
+            const uint32_t h = r / vph;
+            r -= h * vph;
+            src = static_cast<const T*>(a.k) + static_cast<int64_t>(t) * a.k_s0 + static_cast<int64_t>(h) * a.D;
+            dst = static_cast<T*>(a.k_pool) + slot * a.kp_s0 + static_cast<int64_t>(h) * a.D;
+        }
+        const int64_t half = a.D / 2;
+        const uint4 r1 = __ldcs(reinterpret_cast<const uint4*>(src) + r);
+        const uint4 r2 = __ldcs(reinterpret_cast<const uint4*>(src + half) + r);
+        const uint4 rc = __ldg(reinterpret_cast<const uint4*>(static_cast<const T*>(a.cos) + static_cast<int64_t>(t) * a.c_s0) + r);
+        const uint4 rs = __ldg(reinterpret_cast<const uint4*>(static_cast<const T*>(a.sin) + static_cast<int64_t>(t) * a.s_s0) + r);
+        float x1[N], x2[N], c[N], sn[N], o1[N], o2[N];
+        unpack16<T>(r1, x1);
+        unpack16<T>(r2, x2);
+        unpack16<T>(rc, c);
+        unpack16<T>(rs, sn);
+#pragma unroll
+        for (int e = 0; e < N; ++e) {
+            if (sizeof(T) == 2)
+                rotate16(x1[e], x2[e], c[e], sn[e], a.conj, o1[e], o2[e]);
+            else
+                rotate(x1[e], x2[e], c[e], sn[e], a.conj, o1[e], o2[e]);
+        }
+        *(reinterpret_cast<uint4*>(dst) + r) = pack16<T>(o1);
+        *(reinterpret_cast<uint4*>(dst + half) + r) = pack16<T>(o2);
+    }
+}
+
+template <typename T>
+bool launch_store_typed(const RopeStoreArgs& a, cudaStream_t st) {
+    constexpr int N = Vec16<T>::N;
+    const int e = static_cast<int>(sizeof(T));
+    if (a.D % (2 * N) != 0) return false;
+    auto al = [&](const void* p, int64_t s0) { return p == nullptr || (reinterpret_cast<uintptr_t>(p) % 16 == 0 && (s0 * e) % 16 == 0); };
+    if (!al(a.q, a.q_s0) || !al(a.q_out, a.qo_s0) || !al(a.k, a.k_s0) || !al(a.k_pool, a.kp_s0) || !al(a.v, a.v_s0) || !al(a.v_pool, a.vp_s0) ||
+        !al(a.cos, a.c_s0) || !al(a.sin, a.s_s0))
+        return false;
+    const int64_t vph = a.D / 2 / N;
+    const int64_t per_token = (a.Hq + a.Hk) * vph + (a.v ? a.Hk * 2 * vph : 0);
+    const int64_t total = a.T * per_token;
+    if (total >= (1ll << 31)) return false;
+    const unsigned blocks = static_cast<unsigned>(std::min<int64_t>((total + 255) / 256, 148ll * 64));
+    rope_store_kv_kernel<T><<<blocks, 256, 0, st>>>(a, static_cast<uint32_t>(vph), static_cast<uint32_t>(per_token), static_cast<uint32_t>(total));
+    return true;
+}
+
 }  // namespace
 
 void launch_rope_v2(const RopeV2Args& a, cudaStream_t st) {
@@ -232,6 +312,16 @@ void launch_rope_v2(const RopeV2Args& a, cudaStream_t st) {
         case Dt::BF16: rope_v2_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>(a, total); break;
         case Dt::F32: rope_v2_kernel<float><<<blocks, 256, 0, st>>>(a, total); break;
         case Dt::F64: rope_v2_f64_kernel<<<blocks, 256, 0, st>>>(a, total); break;
+    }
+}
+
+bool launch_rope_store_kv(const RopeStoreArgs& a, cudaStream_t st) {
+    if (a.T == 0 || a.D == 0) return true;
+    switch (a.dt) {
+        case Dt::F16: return launch_store_typed<__half>(a, st);
+        case Dt::BF16: return launch_store_typed<__nv_bfloat16>(a, st);
+        case Dt::F32: return launch_store_typed<float>(a, st);
+        default: return false;
     }
 }
 

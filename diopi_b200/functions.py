@@ -151,6 +151,14 @@ def rms_norm(input, normalized_shape, weight, bias, eps, *, return_inv_rms=False
     return (out, inv_rms) if return_inv_rms else out
 
 
+def rotary_emb_copy_kv(q, k, v, cos, sin, dest_loc, k_pool, v_pool, conj=False, *, q_out=None, ctx=None, as_device=None):
+    """q_out = rope(q); k_pool[dest_loc] = rope(k); v_pool[dest_loc] = v (v and v_pool may be None). Returns q_out."""
+    q_out = torch.empty_like(q) if q_out is None else q_out
+    ts = [_t(x, as_device) for x in (q_out, k_pool, v_pool, q, k, v, cos, sin, dest_loc)]
+    _call("diopiRotaryEmbeddingCopyKV", ctx, *[_h(t) for t in ts], bool(conj))
+    return q_out
+
+
 def rms_norm_backward(grad_output, input, weight, bias, inv_rms, normalized_shape, eps, *, ctx=None, as_device=None):
     """Returns (grad_input, grad_weight, grad_bias or None) from the inv_rms a forward call saved."""
     grad_input = torch.empty_like(input)

@@ -67,7 +67,7 @@ def time_op(fn, iters, warmup, flush):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--op", required=True, choices=["prefill", "rms_norm", "rms_norm_bwd", "rotary", "penalty", "copy_kv", "qk", "pv", "decode"])
+    ap.add_argument("--op", required=True, choices=["prefill", "rms_norm", "rms_norm_bwd", "rotary", "rope_copy_kv", "penalty", "copy_kv", "qk", "pv", "decode"])
     ap.add_argument("--size", default="full", choices=["full", "small"])
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
@@ -85,7 +85,7 @@ def main():
         tf = pf["flops"] / med / 1e9
         rec.update(ms=med, ms_best=best, flops=pf["flops"], tflops=tf, frac_of_burst_peak=tf / tf_burst, frac_of_sustained_peak=tf / tf_sust,
                    lens=pf["lens"].tolist(), unit="TFLOP/s (causal-only FLOPs, fp16)")
-    elif args.op in ("rms_norm", "rms_norm_bwd", "rotary"):
+    elif args.op in ("rms_norm", "rms_norm_bwd", "rotary", "rope_copy_kv"):
         tokens = 8192 if args.size == "full" else 1024
         p = workloads.prenorm(tokens=tokens)
         from .runtime import Sizes, Tensor
@@ -118,6 +118,32 @@ def main():
                 impl.diopiRMSNormBackward(ctx.handle, dxs[i].handle, dws[i].handle, None, gs[i].handle, xs[i].handle, wt.handle, None, it.handle, ns, 1e-6)
                 ctx.release()
             fns = [(lambda i=i: bwd(i)) for i in range(sets)]
+        elif args.op == "rope_copy_kv":
+            # prefill-sized pre-attention step: rope(q), rope(k) into the pool, v into the pool, in one launch; the
+            # separate calls it replaces move 8 * numel * e bytes (k is written and read once more), this one 6
+            H, D = p["heads"], p["head_dim"]
+            sets = 3
+            q = p["x"].view(tokens, H, D)
+            kk = p["k_in"].view(tokens, H, D)
+            nbytes = 6 * q.numel() * 2 + 2 * p["cos"].numel() * 2 + tokens * 4
+            dest = torch.randperm(tokens, device="cuda").to(torch.int32)
+            qs = [Tensor(q.clone()) for _ in range(sets)]
+            ks = [Tensor(kk.clone()) for _ in range(sets)]
+            vs = [Tensor(kk.clone()) for _ in range(sets)]
+            qo = [Tensor(torch.empty_like(q)) for _ in range(sets)]
+            kp = [Tensor(torch.empty_like(q)) for _ in range(sets)]
+            vp = [Tensor(torch.empty_like(q)) for _ in range(sets)]
+            ct, st_, dt_ = Tensor(p["cos"]), Tensor(p["sin"]), Tensor(dest)
+            fns = [(lambda i=i: impl.diopiRotaryEmbeddingCopyKV(ctx.handle, qo[i].handle, kp[i].handle, vp[i].handle, qs[i].handle, ks[i].handle, vs[i].handle,
+                                                                   ct.handle, st_.handle, dt_.handle, False)) for i in range(sets)]
+
+            def separate(i):
+                impl.diopiRotaryEmbedding(ctx.handle, qo[i].handle, qs[i].handle, ct.handle, st_.handle, False, False)
+                impl.diopiRotaryEmbedding(ctx.handle, ks[i].handle, ks[i].handle, ct.handle, st_.handle, False, False)
+                impl.diopiDestIndexCopyKV(ctx.handle, kp[i].handle, ks[i].handle, dt_.handle)
+                impl.diopiDestIndexCopyKV(ctx.handle, vp[i].handle, vs[i].handle, dt_.handle)
+            rec["ms_separate_calls"] = time_rotating([(lambda i=i: separate(i)) for i in range(sets)], rounds=10, warmup=1)
+            med = time_rotating(fns[:1], rounds=1, warmup=1)
         else:
             x = p["k_in"].view(tokens, p["heads"], p["head_dim"])
             out = torch.empty_like(x)

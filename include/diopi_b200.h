@@ -228,6 +228,15 @@ diopiError_t diopiTokenDecodeAttentionInference(diopiContextHandle_t ctx, diopiT
                                                 diopiConstTensorHandle_t v, diopiConstTensorHandle_t b_loc, diopiConstTensorHandle_t b_start_loc,
                                                 diopiConstTensorHandle_t b_seq_len, int max_input_len);
 
+/* Extension (not in the DIOPI headers): the step in front of decode attention as one call. Equivalent, bit for bit, to
+ * diopiRotaryEmbedding(q_out, q, cos, sin, conj, false), then diopiRotaryEmbedding into a temporary for k and
+ * diopiDestIndexCopyKV(k_pool, temporary, dest_loc), then diopiDestIndexCopyKV(v_pool, v, dest_loc)
+ * (functions_ext.h:31-32 and :563). q/q_out [T, heads, D], k/v [T, kv_heads, D], pools [slots, kv_heads, D],
+ * cos/sin one row of D/2 per token; v and v_pool may both be null; q_out may be q. */
+diopiError_t diopiRotaryEmbeddingCopyKV(diopiContextHandle_t ctx, diopiTensorHandle_t q_out, diopiTensorHandle_t k_pool, diopiTensorHandle_t v_pool,
+                                        diopiConstTensorHandle_t q, diopiConstTensorHandle_t k, diopiConstTensorHandle_t v, diopiConstTensorHandle_t cos,
+                                        diopiConstTensorHandle_t sin, diopiConstTensorHandle_t dest_loc, bool conj);
+
 /* Extension with no counterpart in the reference: the same fused decode step for callers that
  * cannot provide scratch memory (an engine whose HBM all went to the KV pool and whose context has
  * no allocator; a harness whose diopiRequireTensor fails). It never calls diopiRequireBuffer /
