@@ -2,7 +2,10 @@
 // stream of the caller's context. No host synchronisation, no per-request host loop; lengths,
 // start offsets and slot tables are read on the device.
 #include <cmath>
+#include <cstdlib>
 #include <cstring>
+#include <mutex>
+#include <unordered_map>
 
 #include "../kernels/kernels.hpp"
 #include "common.hpp"
@@ -45,7 +48,7 @@ void same_dtype(const TensorView& a, const char* an, const TensorView& b, const 
 
 // Common checks and argument packing of the three decode entry points.
 void run_decode(diopiContextHandle_t ctx, k::DecodeMode mode, const TensorView* out, const TensorView* att, const TensorView* q, const TensorView* kmat,
-                const TensorView* vmat, const TensorView& b_loc, const TensorView& b_start, const TensorView& b_len, int max_input_len) {
+                const TensorView* vmat, const TensorView& b_loc, const TensorView& b_start, const TensorView& b_len, int max_input_len, bool launch = true) {
     k::DecodeArgs a{};
     a.mode = mode;
     const TensorView& pool = kmat ? *kmat : *vmat;
@@ -106,6 +109,7 @@ void run_decode(diopiContextHandle_t ctx, k::DecodeMode mode, const TensorView* 
     }
     if (a.B == 0 || a.H == 0 || a.D == 0) return;
     B200_REQUIRE(a.slots > 0 || max_input_len == 0, "the K/V pool has no slots");
+    if (!launch) return;  // checks only
     cudaStream_t st = stream_of(ctx);
     if (max_input_len == 0 || a.slots == 0) {
         // Every request is empty: no logits to write, zeros for the attention output.
@@ -123,6 +127,53 @@ void run_decode(diopiContextHandle_t ctx, k::DecodeMode mode, const TensorView* 
          (ws_bytes > 0 || mode == k::DecodeMode::QK) ? "split or plain" : "plain");
     k::launch_decode(a, ws, di.sm_count, di.max_smem_optin, st);
     B200_CUDA(cudaGetLastError());
+}
+
+// ---- the two-call decode run as one kernel (opt-in) ------------------------------------------------
+// With DIOPI_B200_FUSE_TOKEN_ATTENTION=1 in the environment, diopiTokenAttentionInference checks its arguments and
+// records them instead of launching. If the next call of this library on the same context is
+// diopiTokenSoftmaxReduceVInference on the same logits tensor and the same index tensors, the pair runs as the
+// fused kernel and the logits tensor is never written. Any other call of this library on that context first
+// launches the recorded logits kernel, so the logits are in memory whenever this library reads them. What the
+// library cannot see is the caller reading the logits itself, or freeing q/k/the index tensors between the two
+// calls: hence opt-in. The entry point that allocates nothing does not look at the record.
+struct PendingQK {
+    TensorView att, q, k, b_loc, b_start, b_len;
+    int max_input_len = 0;
+};
+std::mutex g_pending_mu;
+std::unordered_map<diopiContextHandle_t, PendingQK> g_pending;
+
+bool fuse_pair_enabled() {
+    const char* v = std::getenv("DIOPI_B200_FUSE_TOKEN_ATTENTION");
+    return v != nullptr && v[0] != '\0' && v[0] != '0';
+}
+
+bool take_pending(diopiContextHandle_t ctx, PendingQK& out) {
+    std::lock_guard<std::mutex> lock(g_pending_mu);
+    auto it = g_pending.find(ctx);
+    if (it == g_pending.end()) return false;
+    out = it->second;
+    g_pending.erase(it);
+    return true;
+}
+
+// Launches the recorded logits kernel of this context, if there is one. Called first by every other entry point.
+void flush_pending(diopiContextHandle_t ctx) {
+    {
+        std::lock_guard<std::mutex> lock(g_pending_mu);
+        if (g_pending.empty()) return;
+    }
+    PendingQK p;
+    if (!take_pending(ctx, p)) return;
+    run_decode(ctx, k::DecodeMode::QK, nullptr, &p.att, &p.q, &p.k, nullptr, p.b_loc, p.b_start, p.b_len, p.max_input_len);
+}
+
+bool same_tensor(const TensorView& a, const TensorView& b) {
+    if (a.data != b.data || a.dtype != b.dtype || a.ndim != b.ndim) return false;
+    for (int i = 0; i < a.ndim; ++i)
+        if (a.shape[i] != b.shape[i] || a.stride[i] != b.stride[i]) return false;
+    return true;
 }
 
 }  // namespace
@@ -143,6 +194,7 @@ B200_EXPORT const char* diopiGetLastErrorString() { return last_error_cstr(); }
 // ---------------------------------------------------------------------------------------------
 B200_EXPORT diopiError_t diopiDestIndexCopyKV(diopiContextHandle_t ctx, diopiTensorHandle_t out, diopiConstTensorHandle_t kh, diopiConstTensorHandle_t dest_loc) {
     return guard("diopiDestIndexCopyKV", [&] {
+        flush_pending(ctx);
         TensorView o = view_of(out, "out"), src = view_of(kh, "k"), d = view_of(dest_loc, "dest_loc");
         same_dtype(o, "out", src, "k");
         B200_REQUIRE(dtype_size(src.dtype) > 0, "'k' has an unsupported dtype");
@@ -180,6 +232,16 @@ B200_EXPORT diopiError_t diopiTokenAttentionInference(diopiContextHandle_t ctx, 
     return guard("diopiTokenAttentionInference", [&] {
         TensorView att = view_of(token_attention_out, "token_attention_out"), qv = view_of(q, "q"), kv = view_of(kh, "k");
         TensorView bl = view_of(b_loc, "b_loc"), bs = view_of(b_start_loc, "b_start_loc"), bn = view_of(b_seq_len, "b_seq_len");
+        flush_pending(ctx);
+        if (fuse_pair_enabled()) {
+            run_decode(ctx, k::DecodeMode::QK, nullptr, &att, &qv, &kv, nullptr, bl, bs, bn, max_input_len, /*launch=*/false);
+            PendingQK p;
+            p.att = att; p.q = qv; p.k = kv; p.b_loc = bl; p.b_start = bs; p.b_len = bn;
+            p.max_input_len = max_input_len;
+            std::lock_guard<std::mutex> lock(g_pending_mu);
+            g_pending[ctx] = p;
+            return;
+        }
         run_decode(ctx, k::DecodeMode::QK, nullptr, &att, &qv, &kv, nullptr, bl, bs, bn, max_input_len);
     });
 }
@@ -190,6 +252,15 @@ B200_EXPORT diopiError_t diopiTokenSoftmaxReduceVInference(diopiContextHandle_t 
     return guard("diopiTokenSoftmaxReduceVInference", [&] {
         TensorView o = view_of(out, "out"), att = view_of(logics, "logics"), vv = view_of(v, "v");
         TensorView bl = view_of(b_loc, "b_loc"), bs = view_of(b_start_loc, "b_start_loc"), bn = view_of(b_seq_len, "b_seq_len");
+        PendingQK p;
+        if (take_pending(ctx, p)) {
+            if (same_tensor(p.att, att) && same_tensor(p.b_loc, bl) && same_tensor(p.b_start, bs) && same_tensor(p.b_len, bn) &&
+                p.max_input_len == max_input_len) {
+                run_decode(ctx, k::DecodeMode::FUSED, &o, nullptr, &p.q, &p.k, &vv, bl, bs, bn, max_input_len);
+                return;
+            }
+            run_decode(ctx, k::DecodeMode::QK, nullptr, &p.att, &p.q, &p.k, nullptr, p.b_loc, p.b_start, p.b_len, p.max_input_len);
+        }
         run_decode(ctx, k::DecodeMode::PV, &o, &att, nullptr, nullptr, &vv, bl, bs, bn, max_input_len);
     });
 }
@@ -198,6 +269,7 @@ B200_EXPORT diopiError_t diopiTokenDecodeAttentionInference(diopiContextHandle_t
                                                             diopiConstTensorHandle_t kh, diopiConstTensorHandle_t v, diopiConstTensorHandle_t b_loc,
                                                             diopiConstTensorHandle_t b_start_loc, diopiConstTensorHandle_t b_seq_len, int max_input_len) {
     return guard("diopiTokenDecodeAttentionInference", [&] {
+        flush_pending(ctx);
         TensorView o = view_of(out, "out"), qv = view_of(q, "q"), kv = view_of(kh, "k"), vv = view_of(v, "v");
         TensorView bl = view_of(b_loc, "b_loc"), bs = view_of(b_start_loc, "b_start_loc"), bn = view_of(b_seq_len, "b_seq_len");
         run_decode(ctx, k::DecodeMode::FUSED, &o, nullptr, &qv, &kv, &vv, bl, bs, bn, max_input_len);
@@ -208,6 +280,7 @@ B200_EXPORT diopiError_t diopiContextAttentionInference(diopiContextHandle_t ctx
                                                         diopiConstTensorHandle_t kh, diopiConstTensorHandle_t v, diopiConstTensorHandle_t b_start_loc,
                                                         diopiConstTensorHandle_t b_seq_len, int max_input_len) {
     return guard("diopiContextAttentionInference", [&] {
+        flush_pending(ctx);
         TensorView o = view_of(context_attention_out, "context_attention_out"), qv = view_of(q, "q"), kv = view_of(kh, "k"), vv = view_of(v, "v");
         TensorView bs = view_of(b_start_loc, "b_start_loc"), bn = view_of(b_seq_len, "b_seq_len");
         k::PrefillArgs a{};
@@ -255,6 +328,7 @@ B200_EXPORT diopiError_t diopiApplyPenalty(diopiContextHandle_t ctx, diopiTensor
                                            diopiConstTensorHandle_t frequency_penalty, diopiConstTensorHandle_t p_token_ids,
                                            diopiConstTensorHandle_t p_token_counts, diopiConstTensorHandle_t p_cumsum_seq_len, int /*p_max_len_in_batch*/) {
     return guard("diopiApplyPenalty", [&] {
+        flush_pending(ctx);
         TensorView lg = view_of(logits, "logits"), pp = view_of(presence_penalty, "presence_penalty"), fp = view_of(frequency_penalty, "frequency_penalty");
         TensorView ids = view_of(p_token_ids, "p_token_ids"), cnt = view_of(p_token_counts, "p_token_counts"), cum = view_of(p_cumsum_seq_len, "p_cumsum_seq_len");
         k::PenaltyArgs a{};
@@ -289,6 +363,7 @@ B200_EXPORT diopiError_t diopiApplyPenalty(diopiContextHandle_t ctx, diopiTensor
 B200_EXPORT diopiError_t diopiRotaryEmbedding(diopiContextHandle_t ctx, diopiTensorHandle_t out, diopiConstTensorHandle_t x, diopiConstTensorHandle_t cos,
                                               diopiConstTensorHandle_t sin, const bool conj, const bool interleaved) {
     return guard("diopiRotaryEmbedding", [&] {
+        flush_pending(ctx);
         if (interleaved) fail(diopiNoImplement, "interleaved rotary embedding is not implemented (nor is it in the reference's CUDA backend)");
         TensorView o = view_of(out, "out"), xv = view_of(x, "x"), cv = view_of(cos, "cos"), sv = view_of(sin, "sin");
         k::RopeArgs a{};
@@ -371,6 +446,7 @@ B200_EXPORT diopiError_t diopiRotaryEmbedding(diopiContextHandle_t ctx, diopiTen
 B200_EXPORT diopiError_t diopiRMSNorm(diopiContextHandle_t ctx, diopiTensorHandle_t out, diopiTensorHandle_t inv_rms, diopiConstTensorHandle_t input,
                                       diopiSize_t normalized_shape, diopiConstTensorHandle_t weight, diopiConstTensorHandle_t bias, double eps) {
     return guard("diopiRMSNorm", [&] {
+        flush_pending(ctx);
         TensorView o = view_of(out, "out"), iv = view_of(inv_rms, "inv_rms"), xv = view_of(input, "input"), wv = view_of(weight, "weight");
         TensorView bv = view_of(bias, "bias", /*optional=*/true);
         k::RmsNormArgs a{};
@@ -426,6 +502,7 @@ B200_EXPORT diopiError_t diopiRotaryEmbeddingCopyKV(diopiContextHandle_t ctx, di
                                                     diopiConstTensorHandle_t cos, diopiConstTensorHandle_t sin, diopiConstTensorHandle_t dest_loc, bool conj) {
     bool composed = false;
     diopiError_t rc = guard("diopiRotaryEmbeddingCopyKV", [&] {
+        flush_pending(ctx);
         TensorView qo = view_of(q_out, "q_out"), kp = view_of(k_pool, "k_pool"), qv = view_of(q, "q"), kv = view_of(kh, "k");
         TensorView cv = view_of(cos, "cos"), sv = view_of(sin, "sin"), d = view_of(dest_loc, "dest_loc");
         TensorView vp = view_of(v_pool, "v_pool", /*optional=*/true), vv = view_of(vh, "v", /*optional=*/true);
@@ -509,6 +586,7 @@ B200_EXPORT diopiError_t diopiRMSNormBackward(diopiContextHandle_t ctx, diopiTen
                                               diopiConstTensorHandle_t weight, diopiConstTensorHandle_t bias, diopiConstTensorHandle_t inv_rms,
                                               diopiSize_t normalized_shape, double /*eps*/) {
     return guard("diopiRMSNormBackward", [&] {
+        flush_pending(ctx);
         TensorView dx = view_of(grad_input, "grad_input"), dw = view_of(grad_weight, "grad_weight"), gv = view_of(grad_output, "grad_output");
         TensorView xv = view_of(input, "input"), wv = view_of(weight, "weight"), iv = view_of(inv_rms, "inv_rms");
         TensorView db = view_of(grad_bias, "grad_bias", /*optional=*/true), bv = view_of(bias, "bias", /*optional=*/true);
@@ -655,6 +733,7 @@ B200_EXPORT diopiError_t diopiTokenDecodeAttentionInferenceNoAlloc(diopiContextH
 B200_EXPORT diopiError_t diopiRotaryEmbeddingV2(diopiContextHandle_t ctx, diopiTensorHandle_t query, diopiTensorHandle_t key, diopiConstTensorHandle_t cos,
                                                 diopiConstTensorHandle_t sin, int64_t dim) {
     return guard("diopiRotaryEmbeddingV2", [&] {
+        flush_pending(ctx);
         TensorView qv = view_of(query, "query"), kv = view_of(key, "key"), cv = view_of(cos, "cos"), sv = view_of(sin, "sin");
         k::RopeV2Args a{};
         a.dt = float_dt(qv, "query", true);
@@ -701,6 +780,7 @@ B200_EXPORT diopiError_t diopiApplyPenaltyV2(diopiContextHandle_t ctx, diopiTens
                                              diopiConstTensorHandle_t frequency_penalty, diopiConstTensorHandle_t repetition_penalty,
                                              diopiConstTensorHandle_t p_token_ids, diopiConstTensorHandle_t p_token_counts) {
     return guard("diopiApplyPenaltyV2", [&] {
+        flush_pending(ctx);
         TensorView lg = view_of(logits, "logits"), pp = view_of(presence_penalty, "presence_penalty"), fp = view_of(frequency_penalty, "frequency_penalty");
         TensorView rp = view_of(repetition_penalty, "repetition_penalty"), ids = view_of(p_token_ids, "p_token_ids"), cnt = view_of(p_token_counts, "p_token_counts");
         k::PenaltyV2Args a{};
@@ -741,6 +821,7 @@ B200_EXPORT diopiError_t diopiPromptFlashAttention(diopiContextHandle_t ctx, dio
                                                    diopiSize_t actual_seq_lengths, int64_t max_input_len, int64_t num_heads, int64_t num_kv_heads,
                                                    int64_t dim) {
     return guard("diopiPromptFlashAttention", [&] {
+        flush_pending(ctx);
         TensorView o = view_of(out, "out"), qv = view_of(query, "query"), kv = view_of(key, "key"), vv = view_of(value, "value");
         k::PrefillArgs a{};
         a.dt = float_dt(qv, "query", false);
@@ -802,6 +883,7 @@ B200_EXPORT diopiError_t diopiPagedAttention(diopiContextHandle_t ctx, diopiTens
                                              int64_t num_heads, int64_t num_kv_heads, int64_t dim, diopiConstTensorHandle_t block_table,
                                              int64_t block_size) {
     return guard("diopiPagedAttention", [&] {
+        flush_pending(ctx);
         TensorView o = view_of(out, "out"), qv = view_of(q, "q"), kv = view_of(kh, "k"), vv = view_of(v, "v"), bt = view_of(block_table, "block_table");
         k::DecodeArgs a{};
         a.mode = k::DecodeMode::FUSED;

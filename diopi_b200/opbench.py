@@ -67,7 +67,7 @@ def time_op(fn, iters, warmup, flush):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--op", required=True, choices=["prefill", "rms_norm", "rms_norm_bwd", "rotary", "rope_copy_kv", "penalty", "copy_kv", "qk", "pv", "decode"])
+    ap.add_argument("--op", required=True, choices=["prefill", "rms_norm", "rms_norm_bwd", "rotary", "rope_copy_kv", "penalty", "copy_kv", "qk", "pv", "pair", "decode"])
     ap.add_argument("--size", default="full", choices=["full", "small"])
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
@@ -170,6 +170,10 @@ def main():
             "copy_kv": (lambda: F.destindex_copy_kv(w.k_new, w.dest_loc, w.k_pool, ctx=ctx), w.copy_bytes() // 2),
             "qk": (lambda: F.token_attention(w.q, w.k_pool, att, w.b_loc, w.b_start_loc, w.b_seq_len, w.max_input_len, ctx=ctx), w.fused_bytes() // 2),
             "pv": (lambda: F.token_softmax_reducev(att, w.v_pool, out, w.b_loc, w.b_start_loc, w.b_seq_len, w.max_input_len, 0, ctx=ctx), w.fused_bytes() // 2),
+            # the two calls of the unchanged header one after the other; with DIOPI_B200_FUSE_TOKEN_ATTENTION=1 in the
+            # environment they run as the fused kernel (algorithmic bytes of the pair: K, V and the logits both ways)
+            "pair": (lambda: (F.token_attention(w.q, w.k_pool, att, w.b_loc, w.b_start_loc, w.b_seq_len, w.max_input_len, ctx=ctx),
+                              F.token_softmax_reducev(att, w.v_pool, out, w.b_loc, w.b_start_loc, w.b_seq_len, w.max_input_len, 0, ctx=ctx)), w.fused_bytes()),
             "decode": (lambda: F.token_decode_attention(w.q, w.k_pool, w.v_pool, out, w.b_loc, w.b_start_loc, w.b_seq_len, w.max_input_len, ctx=ctx), w.fused_bytes()),
         }
         fn, nbytes = fns[args.op]

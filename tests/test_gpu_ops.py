@@ -318,6 +318,57 @@ def test_decode_cfg2_full_size(F, cfg2):
     assert torch.equal(moved, fused)
 
 
+# ------------------------------------------------------------------ the pair of decode calls run as one kernel (opt-in)
+def test_token_attention_pair_runs_fused_when_asked(F, monkeypatch):
+    """With DIOPI_B200_FUSE_TOKEN_ATTENTION=1 the logits call is recorded and the softmax-reduce call that follows on
+    the same tensors runs the fused kernel: same output as the fused entry point, the logits tensor is not written.
+    Any other call in between launches the recorded logits kernel first."""
+    c = make_decode_case(5, 8, 128, torch.float16, [300, 17, 0, 1024, 77], seed=77)
+    d = {k: (v.cuda() if isinstance(v, torch.Tensor) else v) for k, v in c.items()}
+    idx = (d["b_loc"], d["b_start_loc"], d["b_seq_len"], d["max_input_len"])
+    total = int(c["b_seq_len"].sum())
+    fused = torch.empty_like(d["q"])
+    F.token_decode_attention(d["q"], d["k"], d["v"], fused, *idx)
+    plain_att = torch.zeros(8, total, dtype=torch.float16, device="cuda")
+    F.token_attention(d["q"], d["k"], plain_att, *idx)
+    plain_out = torch.empty_like(d["q"])
+    F.token_softmax_reducev(plain_att, d["v"], plain_out, *idx, 0)
+
+    monkeypatch.setenv("DIOPI_B200_FUSE_TOKEN_ATTENTION", "1")
+    att = torch.full((8, total), 7.0, dtype=torch.float16, device="cuda")
+    out = torch.empty_like(d["q"])
+    F.token_attention(d["q"], d["k"], att, *idx)
+    F.token_softmax_reducev(att, d["v"], out, *idx, 0)
+    torch.cuda.synchronize()
+    assert torch.equal(out, fused)
+    assert bool((att == 7.0).all())  # never written
+    close(out, plain_out, torch.float16)
+
+    # another op of the library between the two calls: the logits are written before it runs, then the plain second half
+    F.token_attention(d["q"], d["k"], att, *idx)
+    F.rms_norm(torch.ones(4, 64, device="cuda"), (64,), torch.ones(64, device="cuda"), None, 1e-6)
+    torch.cuda.synchronize()
+    assert torch.equal(att, plain_att)
+    F.token_softmax_reducev(att, d["v"], out, *idx, 0)
+    assert torch.equal(out, plain_out)
+
+    # the second call names another logits tensor: both halves run on their own
+    att2 = torch.zeros_like(att)
+    F.token_attention(d["q"], d["k"], att2, *idx)
+    F.token_softmax_reducev(plain_att, d["v"], out, *idx, 0)
+    torch.cuda.synchronize()
+    assert torch.equal(att2, plain_att) and torch.equal(out, plain_out)
+
+    # bad arguments are still refused at the first call
+    from diopi_b200.runtime import DiopiError
+    with pytest.raises(DiopiError):
+        F.token_attention(d["q"][:, :4], d["k"], att, *idx)
+    monkeypatch.delenv("DIOPI_B200_FUSE_TOKEN_ATTENTION")
+    F.token_attention(d["q"], d["k"], att2.zero_(), *idx)
+    torch.cuda.synchronize()
+    assert torch.equal(att2, plain_att)
+
+
 # ------------------------------------------------------------------ status word, streams
 def test_out_of_range_slot_is_reported(F):
     c = make_decode_case(2, 8, 128, torch.float16, [20, 40], seed=2)
