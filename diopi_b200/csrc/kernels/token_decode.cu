@@ -122,6 +122,14 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t
                  : "memory");
 }
 
+// 2^x by the special-function unit alone (ex2.approx.ftz): -inf gives 0, tiny results flush to 0, and there is no
+// range fix-up code around it as there is around exp2f. Used in the streaming loop only.
+__device__ __forceinline__ float ex2_fast(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 // ---------------------------------------------------------------------------
 // Walks the stages of one CTA's token range. Producer and consumers run the same
 // walk, so nothing but the data itself has to be handed over.
@@ -376,28 +384,41 @@ __global__ void __launch_bounds__(kThreads, 1) decode_split_kernel(const DecodeA
         int64_t att_col0 = 0;
         uint32_t red_phase = 0;
 
-        // PV mode reads the stored logits one tile ahead of their use (a second walk over the same tiles)
+        // PV mode reads the stored logits in groups of four tiles (a request's next 4 * TT tokens), one group ahead
+        // of their use: under a saturated memory system an ordinary load queues behind the bulk copies for several
+        // microseconds, more than one tile lasts. Entry i = 8 * tile + token group of a group is loaded by lane
+        // i % LPH of the head into register i / LPH, and handed round with a shuffle when its tile comes up.
+        constexpr int kLgTiles = 4;
+        constexpr int kLgRegs = kLgTiles * TPG / LPH > 0 ? kLgTiles * TPG / LPH : 1;
         StageWalk ahead;
-        int lg_req = 0, lg_j0 = 0, lg_cnt = 0, lg_cur_req = -1;
-        bool lg_last = false, lg_have = false;
+        float lg_cur[kLgRegs], lg_nxt[kLgRegs];
+        int lg_nxt_cnt = 0, lg_left = 0, lg_k = 0, lg_cur_req = -1;
         int64_t lg_col0 = 0;
-        float lg_next = -INFINITY;
-        auto fetch_logit = [&]() -> float {
-            if (lg_req != lg_cur_req) {
-                lg_cur_req = lg_req;
-                lg_col0 = load_index(a.b_start, lg_req);
+        auto fetch_logits = [&]() {
+            int r, j, n;
+            bool l_;
+            lg_nxt_cnt = 0;
+#pragma unroll
+            for (int i = 0; i < kLgRegs; ++i) lg_nxt[i] = -INFINITY;
+            if (!ahead.next(kLgTiles * TT, r, j, n, l_)) return;
+            lg_nxt_cnt = n;
+            if (r != lg_cur_req) {
+                lg_cur_req = r;
+                lg_col0 = load_index(a.b_start, r);
             }
-            const int t = g + lih * p.G;
-            const int64_t col = lg_col0 + lg_j0 + t;
-            float v = -INFINITY;
-            if (lih < TPG && t < lg_cnt && col >= 0 && col < a.att_cols)
-                v = Cvt<T>::to_f(static_cast<const T*>(a.att)[static_cast<int64_t>(h) * a.att_s0 + col * a.att_s1]) * kLog2e;
-            return v;
+#pragma unroll
+            for (int i = 0; i < kLgRegs; ++i) {
+                const int e = lih + i * LPH;                          // entry of the group
+                const int off = (e >> 3) * TT + g + (e & 7) * p.G;    // its token, counted from the group's first
+                const int64_t col = lg_col0 + j + off;
+                if (e < kLgTiles * TPG && off < n && col >= 0 && col < a.att_cols)
+                    lg_nxt[i] = Cvt<T>::to_f(static_cast<const T*>(a.att)[static_cast<int64_t>(h) * a.att_s0 + col * a.att_s1]) * kLog2e;
+            }
         };
         if (!kHasK) {
+            static_assert(kHasK || TPG == 8, "the logits groups assume eight token groups per tile");
             ahead.init(pre, a.B, t0, t1);
-            lg_have = ahead.next(TT, lg_req, lg_j0, lg_cnt, lg_last);
-            if (lg_have) lg_next = fetch_logit();
+            fetch_logits();
         }
 
         StageWalk walk;
@@ -430,13 +451,24 @@ __global__ void __launch_bounds__(kThreads, 1) decode_split_kernel(const DecodeA
 
             float sc[TPG];
             if (!kHasK) {
-                // Stored logits: lane u of a head holds token group u of this tile (loaded a tile ago); hand them
-                // round the head's lanes, then start the load for the next tile so that it flies during this one.
-                const float lg_cur = lg_next;
-                lg_have = ahead.next(TT, lg_req, lg_j0, lg_cnt, lg_last);
-                if (lg_have) lg_next = fetch_logit();
+                // Stored logits: when a group of tiles is used up, the group loaded meanwhile takes its place and the
+                // load of the one after it starts.
+                if (lg_left == 0) {
 #pragma unroll
-                for (int u = 0; u < TPG; ++u) sc[u] = __shfl_sync(0xffffffffu, lg_cur, (lane & ~(LPH - 1)) + u);
+                    for (int i = 0; i < kLgRegs; ++i) lg_cur[i] = lg_nxt[i];
+                    lg_left = (lg_nxt_cnt + TT - 1) / TT;
+                    lg_k = 0;
+                    fetch_logits();
+                }
+                const int e0 = lg_k * TPG;  // first entry of this tile; all its entries sit in register e0 / LPH
+                float mine = lg_cur[0];
+#pragma unroll
+                for (int i = 1; i < kLgRegs; ++i)
+                    if (i == e0 / LPH) mine = lg_cur[i];
+#pragma unroll
+                for (int u = 0; u < TPG; ++u) sc[u] = __shfl_sync(0xffffffffu, mine, (lane & ~(LPH - 1)) + ((e0 + u) & (LPH - 1)));
+                ++lg_k;
+                --lg_left;
             }
             // token group u sits in ring slot u / ups; a slot is waited for right before its first use
             const unsigned char* slot_ptr[TPG];
@@ -509,7 +541,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_split_kernel(const DecodeA
 #pragma unroll
                 for (int u = 0; u < TPG; ++u) m_new = fmaxf(m_new, sc[u]);
                 const float m_ref = (m_new == -INFINITY) ? 0.f : m_new;
-                const float alpha = exp2f(m - m_ref);
+                const float alpha = ex2_fast(m - m_ref);
                 l *= alpha;
 #pragma unroll
                 for (int e = 0; e < EPC; ++e) acc[e] *= alpha;
@@ -518,7 +550,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_split_kernel(const DecodeA
 #pragma unroll
                     for (int u = 0; u < TPG; ++u) {
                         if (kFull || g + u * p.G < cnt) {
-                            const float pr = exp2f(sc[u] - m_ref);
+                            const float pr = ex2_fast(sc[u] - m_ref);
                             l += pr;
                             const uint4 vv = *reinterpret_cast<const uint4*>(slot_ptr[u] + v_off);
                             float f[EPC];
