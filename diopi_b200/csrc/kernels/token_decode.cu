@@ -650,19 +650,12 @@ __global__ void __launch_bounds__(128) decode_combine_kernel(const DecodeArgs a,
     before = s_part[0][0] + s_part[1][0] + s_part[2][0] + s_part[3][0];
     all = s_part[0][1] + s_part[1][1] + s_part[2][1] + s_part[3][1];
 
-    // Everything above read only the caller's inputs. The partials are written by the split kernel, which may
-    // still be running when this kernel was launched early: wait for it to finish (no-op for a plain launch).
-    asm volatile("griddepcontrol.wait;" ::: "memory");
+    // Which CTAs of the split kernel hold a part of request i: token range [first_token(c), first_token(c + 1)) each.
     const int h = blockIdx.y * 4 + warp;
-    if (h >= a.H) return;
     const int L = request_len(a, i);
-    constexpr int R = 8;  // D <= 256 on this path
-    float acc[R];
-#pragma unroll
-    for (int r = 0; r < R; ++r) acc[r] = 0.f;
-    float M = -INFINITY, Lsum = 0.f;
+    int c_first = 0, c_last = -1;
+    auto first_token = [&](int c) { return static_cast<int>(static_cast<int64_t>(all) * c / n_cta); };
     if (L > 0) {
-        auto first_token = [&](int c) { return static_cast<int>(static_cast<int64_t>(all) * c / n_cta); };
         auto cta_of = [&](int t) {  // largest c with first_token(c) <= t
             int lo = 0, hi = n_cta - 1;
             while (lo < hi) {
@@ -674,22 +667,36 @@ __global__ void __launch_bounds__(128) decode_combine_kernel(const DecodeArgs a,
             }
             return lo;
         };
-        const int c_first = cta_of(before), c_last = cta_of(before + L - 1);
-        for (int c = c_first; c <= c_last; ++c) {
-            if (first_token(c) == first_token(c + 1)) continue;  // an empty range wrote nothing
-            const int64_t slot_id = static_cast<int64_t>(c) + i;
-            const float2 ml = *reinterpret_cast<const float2*>(ws_ml + (slot_id * a.H + h) * 2);
-            if (ml.x == -INFINITY) continue;
-            const float Mn = fmaxf(M, ml.x);
-            const float wo = exp2f(M - Mn), wn = exp2f(ml.x - Mn);
-            Lsum = Lsum * wo + ml.y * wn;
-            const float* src = ws_acc + (slot_id * a.H + h) * a.D;
+        c_first = cta_of(before);
+        c_last = cta_of(before + L - 1);
+    }
+
+    // Everything above read only the caller's inputs. The partials are written by the split kernel, which may
+    // still be running when this kernel was launched early: wait for it to finish (no-op for a plain launch).
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (h >= a.H) return;
+    constexpr int R = 8;  // D <= 256 on this path
+    float acc[R];
 #pragma unroll
-            for (int r = 0; r < R; ++r) {
-                const int d = lane + 32 * r;
-                if (d < a.D) acc[r] = acc[r] * wo + src[d] * wn;
-            }
-            M = Mn;
+    for (int r = 0; r < R; ++r) acc[r] = 0.f;
+    // Two passes with independent loads (one memory latency each): the maximum over the parts, then the weighted sum.
+    float M = -INFINITY, Lsum = 0.f;
+    for (int c = c_first; c <= c_last; ++c) {
+        if (first_token(c) == first_token(c + 1)) continue;  // an empty range wrote nothing
+        M = fmaxf(M, ws_ml[((static_cast<int64_t>(c) + i) * a.H + h) * 2]);
+    }
+    const float Mr = (M == -INFINITY) ? 0.f : M;
+    for (int c = c_first; c <= c_last; ++c) {
+        if (first_token(c) == first_token(c + 1)) continue;
+        const int64_t slot_id = static_cast<int64_t>(c) + i;
+        const float2 ml = *reinterpret_cast<const float2*>(ws_ml + (slot_id * a.H + h) * 2);
+        const float w = exp2f(ml.x - Mr);
+        Lsum = fmaf(ml.y, w, Lsum);
+        const float* src = ws_acc + (slot_id * a.H + h) * a.D;
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            const int d = lane + 32 * r;
+            if (d < a.D) acc[r] = fmaf(src[d], w, acc[r]);
         }
     }
     const float inv = Lsum > 0.f ? 1.f / Lsum : 0.f;
