@@ -23,6 +23,8 @@
 
 #include <mutex>
 
+#include <type_traits>
+
 #include "dev_util.cuh"
 
 namespace b200 {
@@ -34,6 +36,7 @@ constexpr int BM = 128;      // query rows per CTA
 constexpr int BN = 64;       // keys per block
 constexpr int HD = 128;      // head dim
 constexpr int kStages = 2;   // K/V ring
+constexpr int kDefaultPolyEvery = 8;  // share of the exponentials computed on the fma pipe (see prefill_tc_kernel)
 constexpr int kThreads = 192;
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;
 constexpr float kLog2e = 1.4426950408889634f;
@@ -205,6 +208,57 @@ __device__ __forceinline__ float fast_exp2(float x) {
     return y;
 }
 
+// Two fp32 operations per instruction (fma.rn.f32x2 / add.rn.f32x2 on 64-bit register pairs): the soft-max warps are
+// bound by instruction issue next to the special-function unit, and these halve the scale-and-shift and row-sum work.
+__device__ __forceinline__ void ffma2(float& d0, float& d1, float a0, float a1, float b, float c) {
+    uint64_t ra, rb, rc, rd;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(ra) : "f"(a0), "f"(a1));
+    asm("mov.b64 %0, {%1, %1};" : "=l"(rb) : "f"(b));
+    asm("mov.b64 %0, {%1, %1};" : "=l"(rc) : "f"(c));
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(rd) : "l"(ra), "l"(rb), "l"(rc));
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(d0), "=f"(d1) : "l"(rd));
+}
+__device__ __forceinline__ void fadd2(float& d0, float& d1, float a0, float a1) {
+    uint64_t ra, rd;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(ra) : "f"(a0), "f"(a1));
+    asm("mov.b64 %0, {%1, %2};" : "=l"(rd) : "f"(d0), "f"(d1));
+    asm("add.rn.f32x2 %0, %0, %1;" : "+l"(rd) : "l"(ra));
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(d0), "=f"(d1) : "l"(rd));
+}
+// 2^x for a pair of values on the fma pipe (no special-function unit): x = j + f with j = round(x), f in
+// [-0.5, 0.5]; 2^f by a cubic (relative error 7.5e-5, a third of the rounding step of an fp16 probability), 2^j by
+// adding j to the exponent field. The special-function unit does 16 ex2 per clock and SM, which for head_dim 128 takes
+// as long as the two matrix products of a tile; moving part of the exponentials here shortens the longest stage.
+// x <= -125 (masked scores are -inf) gives 2^-125, which is nothing in the row sum and packs to 0.
+__device__ __forceinline__ void poly_exp2_pair(float& a, float& b) {
+    constexpr float kMagic = 12582912.f;  // 1.5 * 2^23: the low mantissa bits of x + kMagic hold round(x)
+    uint64_t x, t, j, f, pz, cm, cnm, c1, c2, c3, c0;
+    const float xa = fmaxf(a, -125.f), xb = fmaxf(b, -125.f);
+    asm("mov.b64 %0, {%1, %2};" : "=l"(x) : "f"(xa), "f"(xb));
+    asm("mov.b64 %0, {%1, %1};" : "=l"(cm) : "f"(kMagic));
+    asm("mov.b64 %0, {%1, %1};" : "=l"(cnm) : "f"(-kMagic));
+    asm("mov.b64 %0, {%1, %1};" : "=l"(c0) : "f"(0.9999280571937561f));
+    asm("mov.b64 %0, {%1, %1};" : "=l"(c1) : "f"(0.6932609677314758f));
+    asm("mov.b64 %0, {%1, %1};" : "=l"(c2) : "f"(0.2426111251115799f));
+    asm("mov.b64 %0, {%1, %1};" : "=l"(c3) : "f"(0.0551716648042202f));
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(t) : "l"(x), "l"(cm));
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(j) : "l"(t), "l"(cnm));
+    asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(f) : "l"(x), "l"(j));
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(pz) : "l"(c3), "l"(f), "l"(c2));
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(pz) : "l"(pz), "l"(f), "l"(c1));
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(pz) : "l"(pz), "l"(f), "l"(c0));
+    float pa, pb, ta, tb;
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(pa), "=f"(pb) : "l"(pz));
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(ta), "=f"(tb) : "l"(t));
+    a = __int_as_float(__float_as_int(pa) + (__float_as_int(ta) << 23));
+    b = __int_as_float(__float_as_int(pb) + (__float_as_int(tb) << 23));
+}
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+
 template <bool BF16>
 __device__ __forceinline__ uint32_t pack2(float a, float b) {
     if (BF16) {
@@ -215,7 +269,9 @@ __device__ __forceinline__ uint32_t pack2(float a, float b) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
-template <bool BF16>
+// kPolyEvery: of every kPolyEvery groups of four scores, one computes two of its exponentials on the fma pipe
+// (1: half of all exponentials, 2: a quarter, 4: an eighth, 8: a sixteenth, 0: none).
+template <bool BF16, int kPolyEvery>
 __global__ void __launch_bounds__(kThreads, 2) prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                                                                    const __grid_constant__ CUtensorMap map_v, const TcParams p) {
     extern __shared__ __align__(1024) unsigned char smem[];
@@ -404,13 +460,14 @@ __global__ void __launch_bounds__(kThreads, 2) prefill_tc_kernel(const __grid_co
                 for (int c = 0; c < BN; ++c)
                     if (c > lim) sc[c] = -INFINITY;
             }
-            float mx0 = sc[0], mx1 = sc[1], mx2 = sc[2], mx3 = sc[3];
+            // three-input maximum: 32 instructions for 64 values, in four independent chains
+            float mx0 = fmaxf(sc[0], sc[1]), mx1 = fmaxf(sc[2], sc[3]), mx2 = fmaxf(sc[4], sc[5]), mx3 = fmaxf(sc[6], sc[7]);
 #pragma unroll
-            for (int c = 4; c < BN; c += 4) {
-                mx0 = fmaxf(mx0, sc[c]);
-                mx1 = fmaxf(mx1, sc[c + 1]);
-                mx2 = fmaxf(mx2, sc[c + 2]);
-                mx3 = fmaxf(mx3, sc[c + 3]);
+            for (int c = 8; c < BN; c += 8) {
+                mx0 = fmax3(mx0, sc[c], sc[c + 1]);
+                mx1 = fmax3(mx1, sc[c + 2], sc[c + 3]);
+                mx2 = fmax3(mx2, sc[c + 4], sc[c + 5]);
+                mx3 = fmax3(mx3, sc[c + 6], sc[c + 7]);
             }
             const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * p.scale_log2;  // scale > 0: max commutes with it
             // Lazy maximum: keep the old reference while the new maximum is within 2^8 of it.
@@ -440,15 +497,23 @@ __global__ void __launch_bounds__(kThreads, 2) prefill_tc_kernel(const __grid_co
                 m_used = m_next;
             }
             const float neg_m = (m_used == -INFINITY) ? 0.f : -m_used;
-            float rs0 = 0.f, rs1 = 0.f;
+            float rs0 = 0.f, rs1 = 0.f, rs2 = 0.f, rs3 = 0.f;
 #pragma unroll
-            for (int c = 0; c < BN; c += 2) {
-                sc[c] = fast_exp2(fmaf(sc[c], p.scale_log2, neg_m));
-                sc[c + 1] = fast_exp2(fmaf(sc[c + 1], p.scale_log2, neg_m));
-                rs0 += sc[c];
-                rs1 += sc[c + 1];
+            for (int c = 0; c < BN; c += 4) {
+                ffma2(sc[c], sc[c + 1], sc[c], sc[c + 1], p.scale_log2, neg_m);
+                ffma2(sc[c + 2], sc[c + 3], sc[c + 2], sc[c + 3], p.scale_log2, neg_m);
+                sc[c] = fast_exp2(sc[c]);
+                sc[c + 1] = fast_exp2(sc[c + 1]);
+                if (kPolyEvery > 0 && (c / 4) % (kPolyEvery > 0 ? kPolyEvery : 1) == 0) {
+                    poly_exp2_pair(sc[c + 2], sc[c + 3]);
+                } else {
+                    sc[c + 2] = fast_exp2(sc[c + 2]);
+                    sc[c + 3] = fast_exp2(sc[c + 3]);
+                }
+                fadd2(rs0, rs1, sc[c], sc[c + 1]);
+                fadd2(rs2, rs3, sc[c + 2], sc[c + 3]);
             }
-            l += rs0 + rs1;
+            l += (rs0 + rs1) + (rs2 + rs3);
             // P_j over the S cells this thread just consumed: cell c holds keys 2c (low half) and 2c + 1
             uint32_t pk[32];
 #pragma unroll
@@ -568,13 +633,26 @@ void launch_prefill_tc(const PrefillArgs& a, int /*sm_count*/, int max_smem, cud
     p.uniform_len = a.uniform_len;
     p.kv_group = a.kv_group;
     dim3 grid(p.n_tiles_max, a.H, 1);
-    if (bf16) {
-        cudaFuncSetAttribute(prefill_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
-        prefill_tc_kernel<true><<<grid, kThreads, kSmemBytes, st>>>(mq, mk, mv, p);
-    } else {
-        cudaFuncSetAttribute(prefill_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
-        prefill_tc_kernel<false><<<grid, kThreads, kSmemBytes, st>>>(mq, mk, mv, p);
-    }
+    int poly = kDefaultPolyEvery;
+    if (const char* v = std::getenv("DIOPI_B200_PREFILL_POLY_EVERY")) poly = std::atoi(v);
+    auto go = [&](auto kern) {
+        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+        kern<<<grid, kThreads, kSmemBytes, st>>>(mq, mk, mv, p);
+    };
+    auto pick = [&](auto bf) {
+        constexpr bool B = decltype(bf)::value;
+        switch (poly) {
+            case 1: go(prefill_tc_kernel<B, 1>); break;
+            case 2: go(prefill_tc_kernel<B, 2>); break;
+            case 4: go(prefill_tc_kernel<B, 4>); break;
+            case 8: go(prefill_tc_kernel<B, 8>); break;
+            default: go(prefill_tc_kernel<B, 0>); break;
+        }
+    };
+    if (bf16)
+        pick(std::true_type{});
+    else
+        pick(std::false_type{});
     *taken = true;
 }
 
