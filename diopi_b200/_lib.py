@@ -44,9 +44,16 @@ OPS = {
     "diopiRotaryEmbedding": [c_void_p, c_void_p, c_void_p, c_void_p, c_bool, c_bool],
     "diopiRMSNorm": [c_void_p, c_void_p, c_void_p, diopiSize_t, c_void_p, c_void_p, c_double],
     "diopiRotaryEmbeddingCopyKV": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_bool],
+    "diopiMatmulAllReduce": [c_void_p, c_void_p, c_void_p, c_void_p, c_char_p, c_char_p, c_int64, c_int64],
     "diopiRMSNormBackward": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, diopiSize_t, c_double],
 }
 INFO = ["diopiGetVendorName", "diopiGetImplVersion", "diopiGetLastErrorString"]
+# set-up calls that take no context handle
+GROUP = {
+    "diopiB200GroupCreate": [c_char_p, c_int, c_int, c_int64, c_void_p],
+    "diopiB200GroupConnect": [c_char_p, c_void_p],
+    "diopiB200GroupDestroy": [c_char_p],
+}
 
 
 def load() -> _Libs:
@@ -85,6 +92,10 @@ def load() -> _Libs:
         fn = getattr(impl, name)
         fn.restype = c_int
         fn.argtypes = [c_void_p] + args
+    for name, args in GROUP.items():
+        fn = getattr(impl, name)
+        fn.restype = c_int
+        fn.argtypes = args
     for name in INFO:
         fn = getattr(impl, name)
         fn.restype = c_char_p

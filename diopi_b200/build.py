@@ -34,6 +34,7 @@ COMMON = [
 IMPL_SOURCES = [
     "abi/common.cpp",
     "abi/exports.cpp",
+    "abi/tp_group.cpp",
     "kernels/dest_index_copy.cu",
     "kernels/token_decode.cu",
     "kernels/rms_norm.cu",
@@ -42,6 +43,7 @@ IMPL_SOURCES = [
     "kernels/apply_penalty.cu",
     "kernels/context_attention.cu",
     "kernels/context_attention_sm100.cu",
+    "kernels/matmul_allreduce.cu",
 ]
 RT_SOURCES = ["rt/testrt.cpp"]
 

@@ -26,11 +26,14 @@
 #include <type_traits>
 
 #include "dev_util.cuh"
+#include "sm100_ptx.cuh"
 
 namespace b200 {
 namespace k {
 
 namespace {
+
+using namespace sm100;  // NOLINT
 
 constexpr int BM = 128;      // query rows per CTA
 constexpr int BN = 64;       // keys per block
@@ -38,7 +41,6 @@ constexpr int HD = 128;      // head dim
 constexpr int kStages = 2;   // K/V ring
 constexpr int kDefaultPolyEvery = 8;  // share of the exponentials computed on the fma pipe (see prefill_tc_kernel)
 constexpr int kThreads = 192;
-constexpr unsigned long long kWaitLimitNs = 2000000000ull;
 constexpr float kLog2e = 1.4426950408889634f;
 
 // shared memory map (bytes); every operand tile starts on a 1024-byte boundary (128-byte swizzle atoms)
@@ -72,134 +74,6 @@ struct TcParams {
     int64_t uniform_len;   // > 0: request i owns rows [i * uniform_len, (i + 1) * uniform_len)
     int kv_group;          // query heads per K/V head
 };
-
-// ---------------------------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) { asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory"); }
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) { asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory"); }
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-// Non-blocking probe of a phase (try_wait may park the thread for a while; this never does).
-__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n.reg .pred p;\nmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-__device__ __forceinline__ unsigned long long global_ns() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* give_up) {
-    if (mbar_try_wait(bar, parity)) return true;
-    const unsigned long long t0 = global_ns();
-    uint32_t spins = 0;
-    while (!mbar_try_wait(bar, parity)) {
-        if ((++spins & 0x3fu) == 0) {
-            if (*give_up) return false;
-            if (global_ns() - t0 > kWaitLimitNs) {
-                *give_up = 1;
-                return false;
-            }
-        }
-    }
-    return true;
-}
-
-// Warp-uniform form for code that goes on to warp-collective tcgen05.ld/st: all lanes agree on the outcome.
-__device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, volatile int* give_up) {
-    return __all_sync(0xffffffffu, mbar_wait(bar, parity, give_up) ? 1 : 0) != 0;
-}
-
-__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, uint32_t bar) {
-    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];" ::"r"(dst),
-                 "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(c2), "r"(bar)
-                 : "memory");
-}
-
-// Shared-memory matrix descriptor for tcgen05.mma, 128-byte swizzle.
-//   bits  0-13  start address >> 4          bits 16-29  leading-dimension byte offset >> 4
-//   bits 32-45  stride byte offset >> 4     bits 46-47  descriptor version (1 on sm_100)
-//   bits 61-63  swizzle mode (2 = 128-byte)
-__device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
-    uint64_t d = 0;
-    d |= static_cast<uint64_t>((smem_addr & 0x3ffffu) >> 4);
-    d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3fffu) << 16;
-    d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3fffu) << 32;
-    d |= 1ull << 46;
-    d |= 2ull << 61;
-    return d;
-}
-
-// Instruction descriptor, kind::f16, fp32 accumulate.
-//   bits 4-5 D format (1 = f32)   bits 7-9 A format, 10-12 B format (0 = f16, 1 = bf16)
-//   bit 15 A major, bit 16 B major (0 = K-major, 1 = MN-major)   bits 17-22 N>>3   bits 24-28 M>>4
-__device__ __forceinline__ uint32_t make_idesc(int m, int n, int bf16, int b_mn_major) {
-    uint32_t d = 0;
-    d |= 1u << 4;
-    d |= static_cast<uint32_t>(bf16 ? 1 : 0) << 7;
-    d |= static_cast<uint32_t>(bf16 ? 1 : 0) << 10;
-    d |= static_cast<uint32_t>(b_mn_major ? 1 : 0) << 16;
-    d |= static_cast<uint32_t>(n >> 3) << 17;
-    d |= static_cast<uint32_t>(m >> 4) << 24;
-    return d;
-}
-
-__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(tmem_d),
-        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-// Same, A operand read from TMEM (for 16-bit types one 32-bit cell holds two consecutive K elements of a row).
-__device__ __forceinline__ void umma_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n" ::"r"(tmem_d),
-        "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]),
-          "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
-          "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]),
-          "=r"(r[31])
-        : "r"(taddr)
-        : "memory");
-}
-__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
-    asm volatile(
-        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
-        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};" ::"r"(taddr),
-        "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]),
-        "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]),
-        "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
-        : "memory");
-}
-__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 // 2^x by the special-function unit alone (ex2.approx.ftz): -inf gives 0, no range fix-up code around it.
 __device__ __forceinline__ float fast_exp2(float x) {

@@ -175,5 +175,29 @@ struct PrefillArgs {
 };
 void launch_prefill(const PrefillArgs& a, int sm_count, int max_smem, cudaStream_t st);
 
+// ---- matmul + all-reduce over a tensor-parallel group --------------------------------------
+constexpr int kMaxGroupRanks = 8;
+struct MatmulAllReduceArgs {
+    Dt dt;                    // F16 or BF16
+    const void* x1;           // [M, K] row-major, x1_ld elements between rows
+    const void* x2;           // [K, N] row-major (x2_kmajor = false, x2_ld between k rows) or stored as [N, K] (x2_kmajor = true, x2_ld between n rows)
+    const void* bias;         // [N] or null
+    void* out;                // [M, N], out_s0 elements between rows
+    int64_t x1_ld, x2_ld, out_s0;
+    bool x2_kmajor;
+    int M, N, K;
+    int rank, world, max_tiles;
+    uint32_t epoch;           // sequence number of this call on the group (never 0)
+    int buf;                  // which half of the staging area this call uses (epoch & 1)
+    float* peer_stage[kMaxGroupRanks];      // staging area of every rank (own included), as mapped into this process
+    uint32_t* peer_flag[kMaxGroupRanks];    // flag words of every rank
+    int* status;
+};
+int matmul_allreduce_tiles(int64_t M, int64_t N);
+size_t matmul_allreduce_stage_bytes(int world, int max_tiles);
+size_t matmul_allreduce_flag_bytes(int world, int max_tiles);
+// Returns null after a launch, else the reason why these arguments cannot run.
+const char* launch_matmul_allreduce(const MatmulAllReduceArgs& a, int sm_count, int max_smem, cudaStream_t st);
+
 }  // namespace k
 }  // namespace b200

@@ -167,3 +167,12 @@ def rms_norm_backward(grad_output, input, weight, bias, inv_rms, normalized_shap
     ts = [_t(x, as_device) for x in (grad_input, grad_weight, grad_bias, grad_output, input, weight, bias, inv_rms)]
     _call("diopiRMSNormBackward", ctx, *[_h(t) for t in ts], Sizes(normalized_shape), float(eps))
     return grad_input, grad_weight, grad_bias
+
+
+def matmul_all_reduce(x1, x2, bias, group, *, out=None, reduce_op="sum", comm_turn=0, stream_mode=1, ctx=None, as_device=None):
+    """out = sum over the ranks of `group` of (x1 @ x2 + bias); `group` is the name given to tp_group.create."""
+    if out is None:
+        out = torch.empty(tuple(x1.shape[:-1]) + (x2.shape[1],), dtype=x1.dtype, device=x1.device)
+    ts = [_t(x, as_device) for x in (out, x1, x2, bias)]
+    _call("diopiMatmulAllReduce", ctx, *[_h(t) for t in ts], group.encode(), reduce_op.encode(), int(comm_turn), int(stream_mode))
+    return out

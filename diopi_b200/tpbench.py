@@ -1,0 +1,123 @@
+"""diopiMatmulAllReduce on N GPUs, one process each (start with torchrun; a plain `python -m diopi_b200.tpbench` is a
+group of one):
+
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \\
+        -m diopi_b200.tpbench [--m 64 --k-total 4096 --n 4096] [--check] [--iters 50]
+
+Every rank holds x1 [M, K_total / N] and x2 [K_total / N, n] of a row-parallel linear layer. Rank 0 prints one JSON line:
+the time per call of the fused kernel (CUDA events, max over ranks) beside the same product done as torch.matmul
+followed by an NCCL all-reduce, and with --check the comparison of every rank's result with the sum the CPU oracle
+forms from all ranks' inputs (inputs are seeded per rank, so every rank can rebuild all of them).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+from pathlib import Path
+
+import torch
+import torch.distributed as dist
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def inputs(rank, M, K, N, dtype, device):
+    g = torch.Generator().manual_seed(4000 + rank)
+    x1 = torch.randn(M, K, generator=g).to(dtype)
+    x2 = (torch.randn(K, N, generator=g) * (K ** -0.5)).to(dtype)
+    bias = torch.randn(N, generator=g).to(dtype) if rank == 0 else None   # as a row-parallel layer does: bias once
+    return x1.to(device), x2.to(device), (bias.to(device) if bias is not None else None)
+
+
+def timed(fn, iters, warmup):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    if dist.is_initialized():
+        dist.barrier()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(iters):
+        fn()
+    b.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([a.elapsed_time(b) / iters], device="cuda")
+    if dist.is_initialized():
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--m", type=int, default=64)
+    ap.add_argument("--k-total", type=int, default=4096)
+    ap.add_argument("--n", type=int, default=4096)
+    ap.add_argument("--dtype", default="bf16", choices=["bf16", "f16"])
+    ap.add_argument("--iters", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--check", action="store_true")
+    args = ap.parse_args()
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    from . import functions as F
+    from . import tp_group
+    from .runtime import Context
+    dtype = torch.bfloat16 if args.dtype == "bf16" else torch.float16
+    M, N, K = args.m, args.n, args.k_total // world
+    tiles = ((M + 127) // 128) * ((N + 127) // 128)
+    tp_group.create("tp", max_tiles=tiles)
+    ctx = Context()
+    x1, x2, bias = inputs(rank, M, K, N, dtype, "cuda")
+    out = torch.empty(M, N, dtype=dtype, device="cuda")
+    rec = {"op": "matmul_all_reduce", "world": world, "M": M, "N": N, "K_per_rank": K, "dtype": args.dtype}
+
+    def fused():
+        F.matmul_all_reduce(x1, x2, bias, "tp", out=out, ctx=ctx)
+
+    if args.check:
+        sys.path.insert(0, str(ROOT))
+        from oracle import golden
+        fused()
+        torch.cuda.synchronize()
+        cpu = [inputs(r, M, K, N, dtype, "cpu") for r in range(world)]
+        want = golden.matmul_all_reduce([c[0] for c in cpu], [c[1] for c in cpu], [c[2] for c in cpu])
+        err = float((out.cpu().float() - want.float()).abs().max())
+        ok = torch.allclose(out.cpu().float(), want.float(), rtol=1e-2, atol=1e-2)
+        same = True
+        if world > 1:
+            gathered = [torch.empty_like(out) for _ in range(world)]
+            dist.all_gather(gathered, out)
+            same = all(torch.equal(g, gathered[0]) for g in gathered)
+            flag = torch.tensor([int(ok and same)], device="cuda")
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+            ok = bool(flag.item())
+        rec.update(parity="ok" if (ok and same) else "MISMATCH", max_abs_err=err, ranks_identical=bool(same))
+
+    rec["fused_ms"] = timed(fused, args.iters, args.warmup)
+
+    def unfused():
+        torch.matmul(x1, x2, out=out)
+        if bias is not None:
+            out.add_(bias)
+        if world > 1:
+            dist.all_reduce(out)
+    rec["matmul_plus_nccl_allreduce_ms"] = timed(unfused, args.iters, args.warmup)
+    flops = 2.0 * M * N * K
+    rec["gemm_tflops_per_rank_in_fused_call"] = flops / rec["fused_ms"] / 1e9
+    rec["nvlink_bytes_sent_per_rank"] = (world - 1) * M * N * 4
+    if rank == 0:
+        print(json.dumps(rec), flush=True)
+    tp_group.destroy("tp")
+    if world > 1:
+        dist.destroy_process_group()
+    return 0 if rec.get("parity", "ok") == "ok" else 1
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -237,6 +237,23 @@ diopiError_t diopiRotaryEmbeddingCopyKV(diopiContextHandle_t ctx, diopiTensorHan
                                         diopiConstTensorHandle_t q, diopiConstTensorHandle_t k, diopiConstTensorHandle_t v, diopiConstTensorHandle_t cos,
                                         diopiConstTensorHandle_t sin, diopiConstTensorHandle_t dest_loc, bool conj);
 
+/* out [.., N] = sum over the ranks of `group` of (x1 [.., K] @ x2 [K, N] + bias [N]): the row-parallel linear layer of a
+ * tensor-parallel model as one kernel per rank (tcgen05 GEMM whose epilogue stores the fp32 partial tiles into every
+ * rank's staging area over NVLink; each rank then adds the partials in rank order, so all ranks hold identical bits).
+ * float16/bfloat16; x2 row-major or the transposed view of an [N, K] weight; reduce_op "sum"; comm_turn and stream_mode
+ * are not read. The group must have been set up with the two calls below. Replaces functions_ext.h:664-665. */
+diopiError_t diopiMatmulAllReduce(diopiContextHandle_t ctx, diopiTensorHandle_t out, diopiConstTensorHandle_t x1, diopiConstTensorHandle_t x2,
+                                  diopiConstTensorHandle_t bias, const char* group, const char* reduce_op, int64_t comm_turn, int64_t stream_mode);
+
+/* Extensions with no counterpart in the reference (there the group string names an HCCL communicator made elsewhere):
+ * set-up of a tensor-parallel group of up to 8 ranks, one process and one GPU each. Create allocates this rank's staging
+ * area for outputs of at most max_tiles tiles of 128 x 128 (2 * world * max_tiles * 64 KiB) and writes its 64-byte CUDA
+ * IPC handle to local_handle; the caller exchanges the handles (rank order) and passes all of them to Connect, which
+ * maps the peers' areas. A group of one rank is usable after Create. Destroy unmaps and frees. */
+diopiError_t diopiB200GroupCreate(const char* group, int rank, int world, int64_t max_tiles, void* local_handle);
+diopiError_t diopiB200GroupConnect(const char* group, const void* handles);
+diopiError_t diopiB200GroupDestroy(const char* group);
+
 /* Extension with no counterpart in the reference: the same fused decode step for callers that
  * cannot provide scratch memory (an engine whose HBM all went to the KV pool and whose context has
  * no allocator; a harness whose diopiRequireTensor fails). It never calls diopiRequireBuffer /

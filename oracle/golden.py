@@ -251,3 +251,19 @@ def paged_attention(query, key, value, atten_mask, actual_seq_lengths, num_heads
     out = torch.zeros(B, num_heads, dim, dtype=torch.float32 if upcast else query.dtype)
     token_decode_attention(q, k, v, out, b_loc, start, lens, mx, upcast=upcast)
     return out.reshape(B, num_heads * dim)
+
+
+def matmul_all_reduce(x1s, x2s, biases=None):
+    """out = sum over ranks r of (x1s[r] @ x2s[r] + biases[r]), products and sums in fp32 in rank order, one rounding
+    to the input dtype at the end. The reference only forwards diopiMatmulAllReduce to the vendor's
+    aclnnMatmulAllReduce (impl/ascend/functions_ext/matmul_all_reduce.cpp:13-17), a closed third-party library (CANN,
+    version not pinned in the tree) that is absent here, and holds no golden function, config or test for it: parity
+    of this function against the reference is unpinned. The formula is the one the vendor documents for that call
+    (matrix product plus bias on every rank, then a sum all-reduce)."""
+    total = None
+    for r, (a, b) in enumerate(zip(x1s, x2s)):
+        part = a.reshape(-1, a.shape[-1]).float() @ b.float()
+        if biases is not None and biases[r] is not None:
+            part = part + biases[r].float()
+        total = part if total is None else total + part
+    return total.to(x1s[0].dtype).reshape(tuple(x1s[0].shape[:-1]) + (x2s[0].shape[1],))

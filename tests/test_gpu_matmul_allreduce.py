@@ -1,0 +1,95 @@
+"""diopiMatmulAllReduce through the C ABI. A group of one rank runs the whole kernel (TMA, tcgen05 product, staging,
+flags, reduction) on one GPU; the multi-rank test starts one process per GPU and needs at least two."""
+import json
+import os
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+
+from oracle import golden
+
+pytestmark = pytest.mark.gpu
+ROOT = Path(__file__).resolve().parent.parent
+
+
+@pytest.fixture(scope="module")
+def F(built_libs):
+    assert torch.cuda.is_available(), "these tests need a CUDA device"
+    from diopi_b200 import functions, tp_group
+    tp_group.create("solo", max_tiles=64, rank=0, world=1)
+    yield functions
+    tp_group.destroy("solo")
+
+
+def rand(shape, dtype, seed, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(*shape, generator=g) * scale).to(dtype)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("shape", [(64, 512, 4096), (5, 72, 136), (300, 256, 520), (128, 64, 128), (129, 1024, 264)])
+def test_one_rank_matches_oracle(F, dtype, shape):
+    M, K, N = shape
+    x1, x2, b = rand((M, K), dtype, 1), rand((K, N), dtype, 2, K ** -0.5), rand((N,), dtype, 3)
+    want = golden.matmul_all_reduce([x1], [x2], [b])
+    got = F.matmul_all_reduce(x1.cuda(), x2.cuda(), b.cuda(), "solo")
+    # fp32 accumulation in both; the products are added in another order, the result is rounded once
+    torch.testing.assert_close(got.cpu().float(), want.float(), rtol=1e-2, atol=1e-2)
+    got2 = F.matmul_all_reduce(x1.cuda(), x2.cuda(), None, "solo")
+    torch.testing.assert_close(got2.cpu().float(), golden.matmul_all_reduce([x1], [x2]).float(), rtol=1e-2, atol=1e-2)
+
+
+def test_transposed_weight_and_stacked_rows(F):
+    dtype = torch.bfloat16
+    x1 = rand((2, 70, 128), dtype, 4)
+    w = rand((264, 128), dtype, 5, 128 ** -0.5)          # [N, K] as torch.nn.Linear keeps it
+    want = golden.matmul_all_reduce([x1], [w.t()])
+    got = F.matmul_all_reduce(x1.cuda(), w.cuda().t(), None, "solo")
+    assert got.shape == (2, 70, 264)
+    torch.testing.assert_close(got.cpu().float(), want.float(), rtol=1e-2, atol=1e-2)
+    same = F.matmul_all_reduce(x1.cuda(), w.t().contiguous().cuda(), None, "solo")
+    assert torch.equal(got, same)   # the two layouts of x2 give the same bits
+
+
+def test_calls_in_a_row_use_both_staging_halves(F):
+    x1, x2 = rand((64, 256), torch.float16, 6), rand((256, 512), torch.float16, 7, 1 / 16)
+    a, b = x1.cuda(), x2.cuda()
+    first = F.matmul_all_reduce(a, b, None, "solo").clone()
+    for i in range(5):
+        # another product in between, so that a stale staging half would show
+        F.matmul_all_reduce(a * 2, b, None, "solo")
+        assert torch.equal(F.matmul_all_reduce(a, b, None, "solo"), first)
+    torch.testing.assert_close(first.cpu().float(), golden.matmul_all_reduce([x1], [x2]).float(), rtol=1e-2, atol=1e-2)
+
+
+def test_refusals(F):
+    from diopi_b200.runtime import DiopiError, FunctionNotImplementedError
+    a, b = torch.zeros(8, 64, dtype=torch.float16, device="cuda"), torch.zeros(64, 64, dtype=torch.float16, device="cuda")
+    with pytest.raises(DiopiError, match="no group named"):
+        F.matmul_all_reduce(a, b, None, "nobody")
+    with pytest.raises(FunctionNotImplementedError):
+        F.matmul_all_reduce(a, b, None, "solo", reduce_op="max")
+    with pytest.raises(DiopiError, match="tiles"):
+        F.matmul_all_reduce(torch.zeros(1024, 64, dtype=torch.float16, device="cuda"), torch.zeros(64, 4096, dtype=torch.float16, device="cuda"), None, "solo")
+    with pytest.raises(DiopiError):
+        F.matmul_all_reduce(a.float(), b.float(), None, "solo")
+    with pytest.raises(DiopiError, match="16 bytes"):   # a row pitch of 132 elements is not a multiple of 16 bytes
+        F.matmul_all_reduce(a, torch.zeros(64, 132, dtype=torch.float16, device="cuda"), None, "solo")
+    assert F.matmul_all_reduce(a[:0], b, None, "solo").shape == (0, 64)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_two_ranks_match_oracle():
+    """One process per GPU under torchrun: every rank's result equals the oracle's sum over both ranks, and the two
+    ranks hold identical bits."""
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1", "--master-port", "29617",
+           "-m", "diopi_b200.tpbench", "--check", "--iters", "3"]
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    res = subprocess.run(cmd, cwd=ROOT, env=env, capture_output=True, text=True, timeout=600)
+    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-2000:]
+    line = [l for l in res.stdout.splitlines() if l.startswith("{")][-1]
+    rec = json.loads(line)
+    assert rec["parity"] == "ok" and rec["world"] == 2

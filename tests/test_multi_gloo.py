@@ -82,3 +82,51 @@ def test_shard_rule_covers_all_heads():
                 assert a[1] == b[0]
             sizes = [b - a for a, b in ranges]
             assert max(sizes) - min(sizes) <= 1
+
+
+def tp_worker(rank, world, port, results):
+    sys.path.insert(0, str(ROOT))
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from diopi_b200 import tp_group
+        from oracle import golden
+        # the handle exchange of the matmul + all-reduce group: every rank ends with all handles in rank order
+        mine = bytes([rank + 1]) * tp_group.HANDLE_BYTES
+        allh = tp_group.exchange(mine)
+        ok = allh == b"".join(bytes([r + 1]) * tp_group.HANDLE_BYTES for r in range(world))
+        try:
+            tp_group.exchange(b"short")
+            ok = False
+        except ValueError:
+            pass
+        # the arithmetic of the op across ranks, with the oracle standing in for the kernel: every rank's partial
+        # product gathered and added in rank order equals the oracle's result for the whole group
+        g = torch.Generator().manual_seed(11)
+        x1 = [torch.randn(6, 16, generator=g).to(torch.bfloat16) for _ in range(world)]
+        x2 = [torch.randn(16, 24, generator=g).to(torch.bfloat16) for _ in range(world)]
+        bias = [torch.randn(24, generator=g).to(torch.bfloat16) for _ in range(world)]
+        want = golden.matmul_all_reduce(x1, x2, bias)
+        part = x1[rank].float() @ x2[rank].float() + bias[rank].float()
+        parts = [torch.empty_like(part) for _ in range(world)]
+        dist.all_gather(parts, part)
+        total = parts[0].clone()
+        for p in parts[1:]:
+            total += p
+        ok = ok and torch.equal(total.to(torch.bfloat16), want)
+        results[rank] = bool(ok)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_tp_group_exchange_two_ranks():
+    world = 2
+    ctx = mp.get_context("spawn")
+    with ctx.Manager() as mgr:
+        results = mgr.dict()
+        port = free_port()
+        procs = [ctx.Process(target=tp_worker, args=(r, world, port, results)) for r in range(world)]
+        [p.start() for p in procs]
+        [p.join(120) for p in procs]
+        assert all(p.exitcode == 0 for p in procs), [p.exitcode for p in procs]
+        assert dict(results) == {0: True, 1: True}
