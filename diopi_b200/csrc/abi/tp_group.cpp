@@ -28,7 +28,6 @@ struct Group {
     void* mapped[k::kMaxGroupRanks] = {nullptr}; // peers' areas as opened here (null for the own rank)
     float* stage[k::kMaxGroupRanks] = {nullptr};
     uint32_t* flag[k::kMaxGroupRanks] = {nullptr};
-    uint32_t epoch = 0;
 };
 
 std::mutex g_mu;
@@ -191,10 +190,7 @@ B200_EXPORT diopiError_t diopiMatmulAllReduce(diopiContextHandle_t ctx, diopiTen
             a.rank = g.rank;
             a.world = g.world;
             a.max_tiles = g.max_tiles;
-            g.epoch += 1;
-            if (g.epoch == 0) g.epoch = 1;   // 0 is what fresh flag words hold
-            a.epoch = g.epoch;
-            a.buf = static_cast<int>(g.epoch & 1u);
+            a.ctrl = g.flag[g.rank] + k::matmul_allreduce_flag_words(g.world, g.max_tiles);
             for (int r = 0; r < g.world; ++r) {
                 a.peer_stage[r] = g.stage[r];
                 a.peer_flag[r] = g.flag[r];

@@ -187,14 +187,14 @@ struct MatmulAllReduceArgs {
     bool x2_kmajor;
     int M, N, K;
     int rank, world, max_tiles;
-    uint32_t epoch;           // sequence number of this call on the group (never 0)
-    int buf;                  // which half of the staging area this call uses (epoch & 1)
+    uint32_t* ctrl;           // this rank's two control words: calls finished so far, CTAs of the running call that left
     float* peer_stage[kMaxGroupRanks];      // staging area of every rank (own included), as mapped into this process
     uint32_t* peer_flag[kMaxGroupRanks];    // flag words of every rank
     int* status;
 };
 int matmul_allreduce_tiles(int64_t M, int64_t N);
 size_t matmul_allreduce_stage_bytes(int world, int max_tiles);
+size_t matmul_allreduce_flag_words(int world, int max_tiles);
 size_t matmul_allreduce_flag_bytes(int world, int max_tiles);
 // Returns null after a launch, else the reason why these arguments cannot run.
 const char* launch_matmul_allreduce(const MatmulAllReduceArgs& a, int sm_count, int max_smem, cudaStream_t st);

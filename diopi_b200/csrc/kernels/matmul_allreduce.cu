@@ -18,7 +18,8 @@
 // This is the one-shot form (each rank receives world x the output in fp32): right for decode-sized outputs, where
 // latency counts; the staging area fixes the largest output (tiles) a group can take.
 //
-// Waiting on another rank's kernel: flags carry the call's sequence number (no reset between calls) and the staging
+// Waiting on another rank's kernel: flags carry the call's sequence number (kept in device memory, no reset between
+// calls, nothing per call from the host: a captured launch can be replayed) and the staging
 // area is double-buffered; a rank cannot run two calls ahead of a peer, because it needs that peer's flags of the
 // call in between. A wait that runs out (a peer that never calls) raises the status word (code 3) and the kernel
 // returns with TMEM freed.
@@ -72,6 +73,11 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_allreduce_kernel(const __g
     const int tiles_n = (a.N + TN - 1) / TN;
     const int n_tiles = ((a.M + TM - 1) / TM) * tiles_n;
     const int kblocks = (a.K + TK - 1) / TK;
+    // The call's sequence number lives in device memory (the number of calls this group has finished, plus one) and is
+    // advanced by the last CTA to leave: the host passes nothing that changes from call to call, so a captured launch
+    // can be replayed. Every CTA reads it here, before any CTA of this launch can have left.
+    const uint32_t epoch = *reinterpret_cast<volatile const uint32_t*>(a.ctrl) + 1u;
+    const int buf = static_cast<int>(epoch & 1u);   // which half of the staging area this call uses
 
     if (tid == 0) {
         for (int s = 0; s < kStages; ++s) {
@@ -153,7 +159,7 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_allreduce_kernel(const __g
         const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
         float* tbuf = reinterpret_cast<float*>(smem + kOffT) + quarter * 32 * kRowPad;
         const size_t tile_floats = static_cast<size_t>(TM) * TN;
-        const size_t src_off = (static_cast<size_t>(a.buf) * a.world + a.rank) * a.max_tiles; // tile slots of (buf, src = this rank)
+        const size_t src_off = (static_cast<size_t>(buf) * a.world + a.rank) * a.max_tiles; // tile slots of (buf, src = this rank)
         bool ok = true;
         int nt = 0;
         for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x, ++nt) {
@@ -207,7 +213,7 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_allreduce_kernel(const __g
             __threadfence_system();
             __syncwarp();
             if (lane < a.world)
-                st_release_sys(a.peer_flag[lane] + ((static_cast<size_t>(a.buf) * a.world + a.rank) * a.max_tiles + tile) * 4 + quarter, a.epoch);
+                st_release_sys(a.peer_flag[lane] + ((static_cast<size_t>(buf) * a.world + a.rank) * a.max_tiles + tile) * 4 + quarter, epoch);
         }
 
         // ---- second pass over this CTA's tiles: add the partials of all ranks, write out ------------------------
@@ -218,11 +224,11 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_allreduce_kernel(const __g
             // lane r waits for rank r's flag of this warp's quarter of the tile
             bool mine = true;
             if (lane < a.world) {
-                const uint32_t* f = my_flag + ((static_cast<size_t>(a.buf) * a.world + lane) * a.max_tiles + tile) * 4 + quarter;
-                if (ld_acquire_sys(f) != a.epoch) {
+                const uint32_t* f = my_flag + ((static_cast<size_t>(buf) * a.world + lane) * a.max_tiles + tile) * 4 + quarter;
+                if (ld_acquire_sys(f) != epoch) {
                     const unsigned long long t0 = global_ns();
                     uint32_t spins = 0;
-                    while (ld_acquire_sys(f) != a.epoch) {
+                    while (ld_acquire_sys(f) != epoch) {
                         if ((++spins & 0x3fu) == 0) {
                             if (*give_up || global_ns() - t0 > kWaitLimitNs) {
                                 *give_up = 1;
@@ -244,7 +250,7 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_allreduce_kernel(const __g
                     const int row = quarter * 32 + rr;
                     float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
                     for (int r = 0; r < a.world; ++r) {
-                        const size_t off = ((static_cast<size_t>(a.buf) * a.world + r) * a.max_tiles + tile) * tile_floats + static_cast<size_t>(row) * TN + 4 * lane;
+                        const size_t off = ((static_cast<size_t>(buf) * a.world + r) * a.max_tiles + tile) * tile_floats + static_cast<size_t>(row) * TN + 4 * lane;
                         const float4 v = __ldcg(reinterpret_cast<const float4*>(my_stage + off));
                         sum.x += v.x;
                         sum.y += v.y;
@@ -269,6 +275,14 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_allreduce_kernel(const __g
     }
 
     __syncthreads();
+    if (tid == 0) {
+        __threadfence();
+        if (atomicAdd(a.ctrl + 1, 1u) == gridDim.x - 1) {   // the last CTA of this launch
+            a.ctrl[1] = 0;
+            *reinterpret_cast<volatile uint32_t*>(a.ctrl) = epoch;
+            __threadfence();
+        }
+    }
     if (*give_up) {
         if (tid == 0) report_status(a.status, 3);
         const unsigned long long t_begin = global_ns();
@@ -317,7 +331,9 @@ int matmul_allreduce_tiles(int64_t M, int64_t N) { return static_cast<int>(((M +
 size_t matmul_allreduce_stage_bytes(int world, int max_tiles) {
     return static_cast<size_t>(2) * world * max_tiles * TM * TN * sizeof(float);
 }
-size_t matmul_allreduce_flag_bytes(int world, int max_tiles) { return static_cast<size_t>(2) * world * max_tiles * 4 * sizeof(uint32_t); }
+// flag words of the two staging halves, then two control words (calls finished, CTAs of the running call that left)
+size_t matmul_allreduce_flag_words(int world, int max_tiles) { return static_cast<size_t>(2) * world * max_tiles * 4; }
+size_t matmul_allreduce_flag_bytes(int world, int max_tiles) { return (matmul_allreduce_flag_words(world, max_tiles) + 2) * sizeof(uint32_t); }
 
 const char* launch_matmul_allreduce(const MatmulAllReduceArgs& a, int sm_count, int max_smem, cudaStream_t st) {
     if (a.M == 0 || a.N == 0) return nullptr;

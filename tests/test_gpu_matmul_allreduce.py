@@ -93,3 +93,25 @@ def test_two_ranks_match_oracle():
     line = [l for l in res.stdout.splitlines() if l.startswith("{")][-1]
     rec = json.loads(line)
     assert rec["parity"] == "ok" and rec["world"] == 2
+
+
+def test_replay_from_a_cuda_graph(F):
+    """Nothing the host passes changes from call to call (the sequence number lives in device memory), so a captured
+    call can be replayed."""
+    from diopi_b200.runtime import Context
+    x1, x2 = rand((64, 256), torch.bfloat16, 8).cuda(), rand((256, 384), torch.bfloat16, 9, 1 / 16).cuda()
+    want = F.matmul_all_reduce(x1, x2, None, "solo").clone()
+    out = torch.zeros_like(want)
+    side = torch.cuda.Stream()
+    ctx = Context(stream=side)
+    side.wait_stream(torch.cuda.current_stream())
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+        F.matmul_all_reduce(x1, x2, None, "solo", out=out, ctx=ctx)
+    for i in range(4):
+        out.zero_()
+        graph.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(out, want), i
+    # and plain calls still line up afterwards
+    assert torch.equal(F.matmul_all_reduce(x1, x2, None, "solo"), want)
