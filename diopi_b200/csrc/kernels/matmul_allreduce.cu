@@ -221,10 +221,11 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_allreduce_kernel(const __g
         const uint32_t* my_flag = a.peer_flag[a.rank];
         for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x) {
             const int m0 = (tile / tiles_n) * TM, n0 = (tile % tiles_n) * TN;
-            // lane r waits for rank r's flag of this warp's quarter of the tile
+            // The rows of a tile are dealt out to the four warps whatever quarter sent them, so every warp waits for all
+            // the flags of the tile: lane 4r + q for quarter q of rank r.
             bool mine = true;
-            if (lane < a.world) {
-                const uint32_t* f = my_flag + ((static_cast<size_t>(buf) * a.world + lane) * a.max_tiles + tile) * 4 + quarter;
+            if (lane < 4 * a.world) {
+                const uint32_t* f = my_flag + ((static_cast<size_t>(buf) * a.world + (lane >> 2)) * a.max_tiles + tile) * 4 + (lane & 3);
                 if (ld_acquire_sys(f) != epoch) {
                     const unsigned long long t0 = global_ns();
                     uint32_t spins = 0;
@@ -244,31 +245,47 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_allreduce_kernel(const __g
                 break;
             }
             const int col = n0 + 4 * lane;
-            const int rows_here = min(32, a.M - (m0 + quarter * 32));
+            const int rows_valid = min(TM, a.M - m0);
             if (col < a.N) {
-                for (int rr = 0; rr < rows_here; ++rr) {
-                    const int row = quarter * 32 + rr;
-                    float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+                constexpr int RB = 8;   // rows in flight per warp: 8 independent 16-byte loads per rank
+                for (int row0 = quarter; row0 < rows_valid; row0 += 4 * RB) {
+                    float4 sum[RB];
+#pragma unroll
+                    for (int i = 0; i < RB; ++i) sum[i] = make_float4(0.f, 0.f, 0.f, 0.f);
                     for (int r = 0; r < a.world; ++r) {
-                        const size_t off = ((static_cast<size_t>(buf) * a.world + r) * a.max_tiles + tile) * tile_floats + static_cast<size_t>(row) * TN + 4 * lane;
-                        const float4 v = __ldcg(reinterpret_cast<const float4*>(my_stage + off));
-                        sum.x += v.x;
-                        sum.y += v.y;
-                        sum.z += v.z;
-                        sum.w += v.w;
+                        const float* src = my_stage + ((static_cast<size_t>(buf) * a.world + r) * a.max_tiles + tile) * tile_floats + 4 * lane;
+                        float4 v[RB];
+#pragma unroll
+                        for (int i = 0; i < RB; ++i) {
+                            const int row = row0 + 4 * i;
+                            v[i] = row < rows_valid ? __ldcg(reinterpret_cast<const float4*>(src + static_cast<size_t>(row) * TN)) : make_float4(0.f, 0.f, 0.f, 0.f);
+                        }
+#pragma unroll
+                        for (int i = 0; i < RB; ++i) {
+                            sum[i].x += v[i].x;
+                            sum[i].y += v[i].y;
+                            sum[i].z += v[i].z;
+                            sum[i].w += v[i].w;
+                        }
                     }
-                    unsigned char* dst = static_cast<unsigned char*>(a.out) + (static_cast<int64_t>(m0 + row) * a.out_s0 + col) * 2;
-                    uint2 packed;
-                    if (BF16) {
-                        __nv_bfloat162 lo = __floats2bfloat162_rn(sum.x, sum.y), hi = __floats2bfloat162_rn(sum.z, sum.w);
-                        packed.x = *reinterpret_cast<uint32_t*>(&lo);
-                        packed.y = *reinterpret_cast<uint32_t*>(&hi);
-                    } else {
-                        __half2 lo = __floats2half2_rn(sum.x, sum.y), hi = __floats2half2_rn(sum.z, sum.w);
-                        packed.x = *reinterpret_cast<uint32_t*>(&lo);
-                        packed.y = *reinterpret_cast<uint32_t*>(&hi);
+#pragma unroll
+                    for (int i = 0; i < RB; ++i) {
+                        const int row = row0 + 4 * i;
+                        if (row < rows_valid) {
+                            unsigned char* dst = static_cast<unsigned char*>(a.out) + (static_cast<int64_t>(m0 + row) * a.out_s0 + col) * 2;
+                            uint2 packed;
+                            if (BF16) {
+                                __nv_bfloat162 lo = __floats2bfloat162_rn(sum[i].x, sum[i].y), hi = __floats2bfloat162_rn(sum[i].z, sum[i].w);
+                                packed.x = *reinterpret_cast<uint32_t*>(&lo);
+                                packed.y = *reinterpret_cast<uint32_t*>(&hi);
+                            } else {
+                                __half2 lo = __floats2half2_rn(sum[i].x, sum[i].y), hi = __floats2half2_rn(sum[i].z, sum[i].w);
+                                packed.x = *reinterpret_cast<uint32_t*>(&lo);
+                                packed.y = *reinterpret_cast<uint32_t*>(&hi);
+                            }
+                            *reinterpret_cast<uint2*>(dst) = packed;
+                        }
                     }
-                    *reinterpret_cast<uint2*>(dst) = packed;
                 }
             }
         }
