@@ -9,6 +9,7 @@
 //   diopiB200GroupConnect(name, all_handles)                         on every rank: maps the peers' areas
 // and then calls diopiMatmulAllReduce(..., group = name, ...) like the reference's backend does. These three set-up
 // entry points have no counterpart in the reference.
+#include <cstdlib>
 #include <cstring>
 #include <map>
 #include <mutex>
@@ -24,18 +25,22 @@ namespace {
 struct Group {
     int rank = 0, world = 1, max_tiles = 0, device = 0;
     bool connected = false;
-    void* local = nullptr;                       // staging floats, then the flag words
+    void* local = nullptr;                       // partial tiles, finished tiles, control words
     void* mapped[k::kMaxGroupRanks] = {nullptr}; // peers' areas as opened here (null for the own rank)
-    float* stage[k::kMaxGroupRanks] = {nullptr};
-    uint32_t* flag[k::kMaxGroupRanks] = {nullptr};
+    unsigned char* stage[k::kMaxGroupRanks] = {nullptr};
+    unsigned char* result[k::kMaxGroupRanks] = {nullptr};
+    uint32_t* ctrl = nullptr;
 };
 
 std::mutex g_mu;
 std::map<std::string, Group> g_groups;
 
 void set_pointers(Group& g, int r, void* base) {
-    g.stage[r] = static_cast<float*>(base);
-    g.flag[r] = reinterpret_cast<uint32_t*>(static_cast<char*>(base) + k::matmul_allreduce_stage_bytes(g.world, g.max_tiles));
+    const k::MarLayout l = k::matmul_allreduce_layout(g.world, g.max_tiles);
+    char* b = static_cast<char*>(base);
+    g.stage[r] = reinterpret_cast<unsigned char*>(b + l.stage_off);
+    g.result[r] = reinterpret_cast<unsigned char*>(b + l.result_off);
+    if (r == g.rank) g.ctrl = reinterpret_cast<uint32_t*>(b + l.ctrl_off);
 }
 
 void release(Group& g) {
@@ -74,7 +79,7 @@ B200_EXPORT diopiError_t diopiB200GroupCreate(const char* group, int rank, int w
         g.world = world;
         g.max_tiles = static_cast<int>(max_tiles);
         B200_CUDA(cudaGetDevice(&g.device));
-        const size_t bytes = k::matmul_allreduce_stage_bytes(world, g.max_tiles) + k::matmul_allreduce_flag_bytes(world, g.max_tiles);
+        const size_t bytes = k::matmul_allreduce_layout(world, g.max_tiles).bytes;
         B200_CUDA(cudaMalloc(&g.local, bytes));
         cudaError_t e = cudaMemset(g.local, 0, bytes);
         if (e == cudaSuccess) e = cudaDeviceSynchronize();
@@ -190,10 +195,18 @@ B200_EXPORT diopiError_t diopiMatmulAllReduce(diopiContextHandle_t ctx, diopiTen
             a.rank = g.rank;
             a.world = g.world;
             a.max_tiles = g.max_tiles;
-            a.ctrl = g.flag[g.rank] + k::matmul_allreduce_flag_words(g.world, g.max_tiles);
+            a.ctrl = g.ctrl;
+            // One-shot (every rank receives every partial) for groups of two or three and for outputs of fewer tiles than
+            // ranks; else two-shot (partials to a tile's owner, finished tiles handed round): the second hop costs a
+            // microsecond or two, the one-shot bytes grow with the group. DIOPI_B200_MAR_MODE=1|2 forces a form.
+            a.two_shot = g.world >= 4 && tiles >= g.world;
+            if (const char* v = std::getenv("DIOPI_B200_MAR_MODE")) {
+                if (v[0] == '1') a.two_shot = false;
+                if (v[0] == '2') a.two_shot = g.world > 1;
+            }
             for (int r = 0; r < g.world; ++r) {
                 a.peer_stage[r] = g.stage[r];
-                a.peer_flag[r] = g.flag[r];
+                a.peer_result[r] = g.result[r];
             }
         }
         a.x1 = av.data;

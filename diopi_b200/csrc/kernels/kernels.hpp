@@ -188,14 +188,16 @@ struct MatmulAllReduceArgs {
     int M, N, K;
     int rank, world, max_tiles;
     uint32_t* ctrl;           // this rank's two control words: calls finished so far, CTAs of the running call that left
-    float* peer_stage[kMaxGroupRanks];      // staging area of every rank (own included), as mapped into this process
-    uint32_t* peer_flag[kMaxGroupRanks];    // flag words of every rank
+    unsigned char* peer_stage[kMaxGroupRanks];   // partial-tile area of every rank (own included), as mapped into this process
+    unsigned char* peer_result[kMaxGroupRanks];  // finished-tile area of every rank (two-shot form)
+    bool two_shot;            // partials to the tile's owner only, finished tiles handed round
     int* status;
 };
 int matmul_allreduce_tiles(int64_t M, int64_t N);
-size_t matmul_allreduce_stage_bytes(int world, int max_tiles);
-size_t matmul_allreduce_flag_words(int world, int max_tiles);
-size_t matmul_allreduce_flag_bytes(int world, int max_tiles);
+struct MarLayout {
+    size_t stage_off, result_off, ctrl_off, bytes;   // byte offsets inside one rank's area
+};
+MarLayout matmul_allreduce_layout(int world, int max_tiles);
 // Returns null after a launch, else the reason why these arguments cannot run.
 const char* launch_matmul_allreduce(const MatmulAllReduceArgs& a, int sm_count, int max_smem, cudaStream_t st);
 

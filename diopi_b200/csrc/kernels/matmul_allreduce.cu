@@ -9,18 +9,23 @@
 //                      4-stage ring, 128-byte swizzle, no multicast
 //   warp 1 (one lane)  tcgen05.mma M128 N128 K16, fp32 accumulators in TMEM (two accumulator buffers, so the epilogue
 //                      of one tile overlaps the products of the next)
-//   warps 2-5          epilogue: TMEM -> registers (+ bias) -> shared memory (transpose to whole rows) -> plain 16-byte
-//                      stores of the fp32 partial tile into EVERY rank's staging area over NVLink (peer pointers, this
-//                      rank's own copy included), then one release-store of a flag per destination and warp
-// and, once a CTA has sent all its tiles, the same warps wait for the flags of all ranks for each of those tiles
-// (acquire loads of this rank's own memory, bounded by a time limit), add the partials in rank order in fp32 and
-// write the tile of `out` once. Every rank adds the same numbers in the same order: all ranks get identical bits.
-// This is the one-shot form (each rank receives world x the output in fp32): right for decode-sized outputs, where
-// latency counts; the staging area fixes the largest output (tiles) a group can take.
+//   warps 2-5          epilogue: TMEM -> registers -> shared memory (transpose to whole rows) -> (+ bias) -> 16-byte stores
+//                      of the fp32 partial rows into EVERY rank's staging area over NVLink (peer pointers, this rank's
+//                      own copy included). Every 64-bit word stored is (call number << 32 | payload): the data is its
+//                      own arrival mark, there is no flag to write after it and no fence to wait for.
+// Once a CTA has sent all its tiles, the same warps read, for each of those tiles, the partial rows of all ranks from
+// this rank's own staging area (re-reading a row until every word carries this call's number, bounded by a time limit),
+// add them in rank order in fp32 and write the tile of `out` once. Every rank adds the same numbers in the same
+// order: all ranks get identical bits.
+// That is the one-shot form (each rank receives world x the output): right for decode-sized outputs, where latency
+// counts. In the two-shot form a tile's partials go only to its owner (rank tile % world), which adds them up and
+// writes the finished 16-bit rows (marked the same way) into every rank's result area; every rank then copies the
+// tiles it does not own from its result area to `out`: 1 / world of the one-shot bytes for the partials at the price
+// of a second hop. The staging area fixes the largest output (tiles) a group can take.
 //
-// Waiting on another rank's kernel: flags carry the call's sequence number (kept in device memory, no reset between
+// Waiting on another rank's kernel: the marks are the call's sequence number (kept in device memory, no reset between
 // calls, nothing per call from the host: a captured launch can be replayed) and the staging
-// area is double-buffered; a rank cannot run two calls ahead of a peer, because it needs that peer's flags of the
+// area is double-buffered; a rank cannot run two calls ahead of a peer, because it needs that peer's rows of the
 // call in between. A wait that runs out (a peer that never calls) raises the status word (code 3) and the kernel
 // returns with TMEM freed.
 #include <cuda.h>
@@ -54,11 +59,41 @@ constexpr int kOffFlag = kOffTmemSlot + 8;
 constexpr int kSmemBytes = kOffFlag + 8;
 constexpr uint32_t kTmemCols = 256;           // two accumulators of 128 fp32 columns
 
-__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) { asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory"); }
-__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
-    uint32_t v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
+// Data that carries its own arrival mark: a 64-bit word = (call number << 32) | 32 bits of payload, written and read
+// with single 64-bit accesses (two per 16-byte vector access), which are atomic: a reader that finds this call's number
+// in the upper half has the payload of this call in the lower half. No flag after the data, no fence before a flag:
+// a row is usable the moment it lands. Costs twice the bytes, which at these sizes is cheaper than a fence round trip.
+__device__ __forceinline__ void st_pair(unsigned char* p, uint32_t a, uint32_t b, uint32_t epoch) {
+    const uint64_t hi = static_cast<uint64_t>(epoch) << 32;
+    asm volatile("st.volatile.global.v2.u64 [%0], {%1, %2};" ::"l"(p), "l"(hi | a), "l"(hi | b) : "memory");
+}
+__device__ __forceinline__ bool ld_pair(const unsigned char* p, uint32_t epoch, uint32_t& a, uint32_t& b) {
+    uint64_t x, y;
+    asm volatile("ld.volatile.global.v2.u64 {%0, %1}, [%2];" : "=l"(x), "=l"(y) : "l"(p) : "memory");
+    a = static_cast<uint32_t>(x);
+    b = static_cast<uint32_t>(y);
+    return static_cast<uint32_t>(x >> 32) == epoch && static_cast<uint32_t>(y >> 32) == epoch;
+}
+// Between two polls: starts the clock at the first miss, gives up after the time limit or when another role did.
+__device__ __forceinline__ bool poll_again(unsigned long long& t0, volatile int* give_up) {
+    const unsigned long long now = global_ns();
+    if (t0 == 0) t0 = now;
+    if (*give_up || now - t0 > kWaitLimitNs) {
+        *give_up = 1;
+        return false;
+    }
+    return true;
+}
+
+// Byte offsets inside one rank's area. A partial tile row is 1 KB: words (x, y) of lane l at 16 l, words (z, w) at
+// 512 + 16 l, so that each of the two stores of a warp covers 512 contiguous bytes. A result row is 512 bytes.
+constexpr size_t kPartialRowBytes = 1024, kPartialTileBytes = TM * kPartialRowBytes;
+constexpr size_t kResultRowBytes = 512, kResultTileBytes = TM * kResultRowBytes;
+__device__ __forceinline__ size_t partial_slot(int buf, int world, int src, int max_tiles, int tile) {
+    return ((static_cast<size_t>(buf) * world + src) * max_tiles + tile) * kPartialTileBytes;
+}
+__device__ __forceinline__ size_t result_slot(int buf, int max_tiles, int tile) {
+    return (static_cast<size_t>(buf) * max_tiles + tile) * kResultTileBytes;
 }
 
 template <bool BF16, bool B_KMAJOR>
@@ -158,10 +193,9 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_allreduce_kernel(const __g
         const int quarter = warp & 3;                    // the TMEM lane quarter this warp may touch
         const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
         float* tbuf = reinterpret_cast<float*>(smem + kOffT) + quarter * 32 * kRowPad;
-        const size_t tile_floats = static_cast<size_t>(TM) * TN;
-        const size_t src_off = (static_cast<size_t>(buf) * a.world + a.rank) * a.max_tiles; // tile slots of (buf, src = this rank)
         bool ok = true;
         int nt = 0;
+        // ---- first pass: every tile of this CTA, product -> partial rows into the staging areas -----------------------
         for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x, ++nt) {
             const int acc = nt & 1;
             const int m0 = (tile / tiles_n) * TM, n0 = (tile % tiles_n) * TN;
@@ -197,94 +231,137 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_allreduce_kernel(const __g
                 }
             }
             const int rows_here = min(32, a.M - (m0 + quarter * 32));   // rows of this warp's slab that exist
-            for (int rr = 0; rr < rows_here; ++rr) {
-                float4 v = *reinterpret_cast<const float4*>(tbuf + rr * kRowPad + 4 * lane);
-                v.x += bias4.x;
-                v.y += bias4.y;
-                v.z += bias4.z;
-                v.w += bias4.w;
-                const size_t off = (src_off + tile) * tile_floats + static_cast<size_t>(quarter * 32 + rr) * TN + 4 * lane;
-                if (col < a.N) {
-                    for (int p = 0; p < a.world; ++p) *reinterpret_cast<float4*>(a.peer_stage[p] + off) = v;
+            const size_t slot = partial_slot(buf, a.world, a.rank, a.max_tiles, tile);
+            const int owner = tile % a.world;
+            if (col < a.N) {
+                for (int rr = 0; rr < rows_here; ++rr) {
+                    float4 v = *reinterpret_cast<const float4*>(tbuf + rr * kRowPad + 4 * lane);
+                    v.x += bias4.x;
+                    v.y += bias4.y;
+                    v.z += bias4.z;
+                    v.w += bias4.w;
+                    const size_t off = slot + static_cast<size_t>(quarter * 32 + rr) * kPartialRowBytes + 16 * lane;
+                    if (a.two_shot) {
+                        st_pair(a.peer_stage[owner] + off, __float_as_uint(v.x), __float_as_uint(v.y), epoch);
+                        st_pair(a.peer_stage[owner] + off + 512, __float_as_uint(v.z), __float_as_uint(v.w), epoch);
+                    } else {
+                        for (int p = 0; p < a.world; ++p) {
+                            st_pair(a.peer_stage[p] + off, __float_as_uint(v.x), __float_as_uint(v.y), epoch);
+                            st_pair(a.peer_stage[p] + off + 512, __float_as_uint(v.z), __float_as_uint(v.w), epoch);
+                        }
+                    }
                 }
             }
-            // This warp's 32 rows are on their way: one flag per destination says "rows 32q .. 32q+31 of tile `tile` from
-            // rank `rank` are there". A flag per warp, not per tile, so that no warp ever waits for another here.
-            __threadfence_system();
-            __syncwarp();
-            if (lane < a.world)
-                st_release_sys(a.peer_flag[lane] + ((static_cast<size_t>(buf) * a.world + a.rank) * a.max_tiles + tile) * 4 + quarter, epoch);
+            __syncwarp();   // the transpose buffer is rewritten by the next tile
         }
 
-        // ---- second pass over this CTA's tiles: add the partials of all ranks, write out ------------------------
-        const float* my_stage = a.peer_stage[a.rank];
-        const uint32_t* my_flag = a.peer_flag[a.rank];
+        // ---- second pass: add the partials of all ranks in rank order (two-shot: only for the tiles this rank owns) ----
+        const unsigned char* my_stage = a.peer_stage[a.rank];
+        constexpr int RB = 8;   // rows in flight per warp
         for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x) {
+            if (a.two_shot && tile % a.world != a.rank) continue;
             const int m0 = (tile / tiles_n) * TM, n0 = (tile % tiles_n) * TN;
-            // The rows of a tile are dealt out to the four warps whatever quarter sent them, so every warp waits for all
-            // the flags of the tile: lane 4r + q for quarter q of rank r.
-            bool mine = true;
-            if (lane < 4 * a.world) {
-                const uint32_t* f = my_flag + ((static_cast<size_t>(buf) * a.world + (lane >> 2)) * a.max_tiles + tile) * 4 + (lane & 3);
-                if (ld_acquire_sys(f) != epoch) {
-                    const unsigned long long t0 = global_ns();
-                    uint32_t spins = 0;
-                    while (ld_acquire_sys(f) != epoch) {
-                        if ((++spins & 0x3fu) == 0) {
-                            if (*give_up || global_ns() - t0 > kWaitLimitNs) {
-                                *give_up = 1;
-                                mine = false;
-                                break;
+            const int col = n0 + 4 * lane;
+            const int rows_valid = min(TM, a.M - m0);
+            // the rows of a tile are dealt out to the four warps: row0 = warp's number, then every fourth row
+            for (int row0 = quarter; ok && row0 < rows_valid; row0 += 4 * RB) {
+                float4 sum[RB];
+#pragma unroll
+                for (int i = 0; i < RB; ++i) sum[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+                for (int r = 0; ok && r < a.world; ++r) {
+                    const unsigned char* src = my_stage + partial_slot(buf, a.world, r, a.max_tiles, tile) + 16 * lane;
+                    uint32_t w[RB][4];
+                    unsigned long long t0 = 0;
+                    for (;;) {   // until every word of the batch carries this call's number
+                        bool here = true;
+                        if (col < a.N) {
+#pragma unroll
+                            for (int i = 0; i < RB; ++i) {
+                                const int row = row0 + 4 * i;
+                                if (row < rows_valid) {
+                                    const unsigned char* q = src + static_cast<size_t>(row) * kPartialRowBytes;
+                                    here &= ld_pair(q, epoch, w[i][0], w[i][1]);
+                                    here &= ld_pair(q + 512, epoch, w[i][2], w[i][3]);
+                                }
                             }
+                        }
+                        if (__all_sync(0xffffffffu, here ? 1 : 0)) break;
+                        if (!__all_sync(0xffffffffu, poll_again(t0, give_up) ? 1 : 0)) {   // the warp stops as one
+                            ok = false;
+                            break;
+                        }
+                    }
+                    if (!ok) break;
+#pragma unroll
+                    for (int i = 0; i < RB; ++i) {
+                        if (row0 + 4 * i < rows_valid) {
+                            sum[i].x += __uint_as_float(w[i][0]);
+                            sum[i].y += __uint_as_float(w[i][1]);
+                            sum[i].z += __uint_as_float(w[i][2]);
+                            sum[i].w += __uint_as_float(w[i][3]);
+                        }
+                    }
+                }
+                if (!ok || col >= a.N) continue;
+#pragma unroll
+                for (int i = 0; i < RB; ++i) {
+                    const int row = row0 + 4 * i;
+                    if (row < rows_valid) {
+                        uint2 packed;
+                        if (BF16) {
+                            __nv_bfloat162 lo = __floats2bfloat162_rn(sum[i].x, sum[i].y), hi = __floats2bfloat162_rn(sum[i].z, sum[i].w);
+                            packed.x = *reinterpret_cast<uint32_t*>(&lo);
+                            packed.y = *reinterpret_cast<uint32_t*>(&hi);
+                        } else {
+                            __half2 lo = __floats2half2_rn(sum[i].x, sum[i].y), hi = __floats2half2_rn(sum[i].z, sum[i].w);
+                            packed.x = *reinterpret_cast<uint32_t*>(&lo);
+                            packed.y = *reinterpret_cast<uint32_t*>(&hi);
+                        }
+                        *reinterpret_cast<uint2*>(static_cast<unsigned char*>(a.out) + (static_cast<int64_t>(m0 + row) * a.out_s0 + col) * 2) = packed;
+                        if (a.two_shot) {   // and the finished rows to every other rank's result area
+                            const size_t roff = result_slot(buf, a.max_tiles, tile) + static_cast<size_t>(row) * kResultRowBytes + 16 * lane;
+                            for (int p = 0; p < a.world; ++p)
+                                if (p != a.rank) st_pair(a.peer_result[p] + roff, packed.x, packed.y, epoch);
                         }
                     }
                 }
             }
-            if (!__all_sync(0xffffffffu, mine ? 1 : 0)) {
-                ok = false;
-                break;
-            }
-            const int col = n0 + 4 * lane;
-            const int rows_valid = min(TM, a.M - m0);
-            if (col < a.N) {
-                constexpr int RB = 8;   // rows in flight per warp: 8 independent 16-byte loads per rank
-                for (int row0 = quarter; row0 < rows_valid; row0 += 4 * RB) {
-                    float4 sum[RB];
+        }
+
+        // ---- two-shot only, third pass: the tiles other ranks added up arrive in this rank's result area -----------
+        if (a.two_shot) {
+            const unsigned char* my_result = a.peer_result[a.rank];
+            for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x) {
+                if (tile % a.world == a.rank) continue;   // written straight to out above
+                const int m0 = (tile / tiles_n) * TM, n0 = (tile % tiles_n) * TN;
+                const int col = n0 + 4 * lane;
+                const int rows_valid = min(TM, a.M - m0);
+                const unsigned char* src = my_result + result_slot(buf, a.max_tiles, tile) + 16 * lane;
+                for (int row0 = quarter; ok && row0 < rows_valid; row0 += 4 * RB) {
+                    uint32_t w[RB][2];
+                    unsigned long long t0 = 0;
+                    for (;;) {
+                        bool here = true;
+                        if (col < a.N) {
 #pragma unroll
-                    for (int i = 0; i < RB; ++i) sum[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-                    for (int r = 0; r < a.world; ++r) {
-                        const float* src = my_stage + ((static_cast<size_t>(buf) * a.world + r) * a.max_tiles + tile) * tile_floats + 4 * lane;
-                        float4 v[RB];
-#pragma unroll
-                        for (int i = 0; i < RB; ++i) {
-                            const int row = row0 + 4 * i;
-                            v[i] = row < rows_valid ? __ldcg(reinterpret_cast<const float4*>(src + static_cast<size_t>(row) * TN)) : make_float4(0.f, 0.f, 0.f, 0.f);
+                            for (int i = 0; i < RB; ++i) {
+                                const int row = row0 + 4 * i;
+                                if (row < rows_valid) here &= ld_pair(src + static_cast<size_t>(row) * kResultRowBytes, epoch, w[i][0], w[i][1]);
+                            }
                         }
-#pragma unroll
-                        for (int i = 0; i < RB; ++i) {
-                            sum[i].x += v[i].x;
-                            sum[i].y += v[i].y;
-                            sum[i].z += v[i].z;
-                            sum[i].w += v[i].w;
+                        if (__all_sync(0xffffffffu, here ? 1 : 0)) break;
+                        if (!__all_sync(0xffffffffu, poll_again(t0, give_up) ? 1 : 0)) {   // the warp stops as one
+                            ok = false;
+                            break;
                         }
                     }
+                    if (!ok || col >= a.N) continue;
 #pragma unroll
                     for (int i = 0; i < RB; ++i) {
                         const int row = row0 + 4 * i;
-                        if (row < rows_valid) {
-                            unsigned char* dst = static_cast<unsigned char*>(a.out) + (static_cast<int64_t>(m0 + row) * a.out_s0 + col) * 2;
-                            uint2 packed;
-                            if (BF16) {
-                                __nv_bfloat162 lo = __floats2bfloat162_rn(sum[i].x, sum[i].y), hi = __floats2bfloat162_rn(sum[i].z, sum[i].w);
-                                packed.x = *reinterpret_cast<uint32_t*>(&lo);
-                                packed.y = *reinterpret_cast<uint32_t*>(&hi);
-                            } else {
-                                __half2 lo = __floats2half2_rn(sum[i].x, sum[i].y), hi = __floats2half2_rn(sum[i].z, sum[i].w);
-                                packed.x = *reinterpret_cast<uint32_t*>(&lo);
-                                packed.y = *reinterpret_cast<uint32_t*>(&hi);
-                            }
-                            *reinterpret_cast<uint2*>(dst) = packed;
-                        }
+                        if (row < rows_valid)
+                            *reinterpret_cast<uint2*>(static_cast<unsigned char*>(a.out) + (static_cast<int64_t>(m0 + row) * a.out_s0 + col) * 2) =
+                                make_uint2(w[i][0], w[i][1]);
                     }
                 }
             }
@@ -345,12 +422,21 @@ bool make_map_2d(CUtensorMap* map, const void* base, int64_t inner, int64_t oute
 
 int matmul_allreduce_tiles(int64_t M, int64_t N) { return static_cast<int>(((M + TM - 1) / TM) * ((N + TN - 1) / TN)); }
 
-size_t matmul_allreduce_stage_bytes(int world, int max_tiles) {
-    return static_cast<size_t>(2) * world * max_tiles * TM * TN * sizeof(float);
+// One rank's area: partial tiles [2 halves][world sources][max_tiles] (fp32 with arrival marks, 128 KB each), finished
+// tiles [2][max_tiles] (16-bit with arrival marks, 64 KB each, two-shot form) and two control words (calls finished,
+// CTAs of the running call that have left).
+MarLayout matmul_allreduce_layout(int world, int max_tiles) {
+    MarLayout l;
+    size_t off = 0;
+    l.stage_off = off;
+    off += static_cast<size_t>(2) * world * max_tiles * kPartialTileBytes;
+    l.result_off = off;
+    off += static_cast<size_t>(2) * max_tiles * kResultTileBytes;
+    l.ctrl_off = off;
+    off += 2 * sizeof(uint32_t);
+    l.bytes = (off + 255) / 256 * 256;
+    return l;
 }
-// flag words of the two staging halves, then two control words (calls finished, CTAs of the running call that left)
-size_t matmul_allreduce_flag_words(int world, int max_tiles) { return static_cast<size_t>(2) * world * max_tiles * 4; }
-size_t matmul_allreduce_flag_bytes(int world, int max_tiles) { return (matmul_allreduce_flag_words(world, max_tiles) + 2) * sizeof(uint32_t); }
 
 const char* launch_matmul_allreduce(const MatmulAllReduceArgs& a, int sm_count, int max_smem, cudaStream_t st) {
     if (a.M == 0 || a.N == 0) return nullptr;

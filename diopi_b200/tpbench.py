@@ -79,7 +79,7 @@ def main():
     ctx = Context()
     x1, x2, bias = inputs(rank, M, K, N, dtype, "cuda")
     out = torch.empty(M, N, dtype=dtype, device="cuda")
-    rec = {"op": "matmul_all_reduce", "world": world, "M": M, "N": N, "K_per_rank": K, "dtype": args.dtype}
+    rec = {"op": "matmul_all_reduce", "mode": os.environ.get("DIOPI_B200_MAR_MODE", "auto"), "world": world, "M": M, "N": N, "K_per_rank": K, "dtype": args.dtype}
 
     # handles made once, the entry point called directly: the host side of a call is then a few microseconds, as it is
     # for a C++ consumer, and the figure is the device's

@@ -82,12 +82,13 @@ def test_refusals(F):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_two_ranks_match_oracle():
+@pytest.mark.parametrize("mode", ["1", "2"])
+def test_two_ranks_match_oracle(mode):
     """One process per GPU under torchrun: every rank's result equals the oracle's sum over both ranks, and the two
-    ranks hold identical bits."""
+    ranks hold identical bits; in the one-shot form (1) and in the two-shot form (2)."""
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1", "--master-port", "29617",
-           "-m", "diopi_b200.tpbench", "--check", "--iters", "3"]
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+           "-m", "diopi_b200.tpbench", "--check", "--iters", "3", "--rows", "200", "--cols", "1032"]
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", DIOPI_B200_MAR_MODE=mode)
     res = subprocess.run(cmd, cwd=ROOT, env=env, capture_output=True, text=True, timeout=600)
     assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-2000:]
     line = [l for l in res.stdout.splitlines() if l.startswith("{")][-1]
