@@ -19,7 +19,7 @@ from pathlib import Path
 import numpy as np
 import torch
 
-REF = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+REF = Path(sys.argv[1]) if len(sys.argv) > 1 else Path(__file__).resolve().parents[3] / "reference"   # default: a checkout beside this repository
 sys.path.insert(0, str(REF / "diopi_test" / "python" / "conformance"))
 torch.Tensor.cuda = lambda self, *a, **k: self  # see the module docstring
 from customized_test import CustomizedTest as G  # noqa: E402

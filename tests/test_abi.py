@@ -8,7 +8,7 @@ import pytest
 
 ROOT = Path(__file__).resolve().parent.parent
 HEADER = ROOT / "include" / "diopi_b200.h"
-REFERENCE = Path("/root/reference/proto/include")
+REFERENCE = Path(__file__).resolve().parents[2] / "reference" / "proto" / "include"   # a reference checkout beside this repository, if any
 
 
 def declared_exports():
