@@ -4,10 +4,11 @@
 // impl/ascend_npu/diopi_impl/functions_ext/matmul_all_reduce.cpp:12-17; signature proto/include/diopi/functions_ext.h:664-665);
 // there is no NVIDIA implementation to replace.
 //
-// Per rank, a persistent grid (one CTA per SM at most) walks the 128 x 128 output tiles:
-//   warp 0 (one lane)  TMA: x1 tile [128 x 64] and x2 tile [64 x 128] (or [128 x 64] when x2 is given K-major) into a
-//                      4-stage ring, 128-byte swizzle, no multicast
-//   warp 1 (one lane)  tcgen05.mma M128 N128 K16, fp32 accumulators in TMEM (two accumulator buffers, so the epilogue
+// Per rank, a persistent grid (one CTA per SM at most) walks the 128 x TN output tiles (TN = 128; 64 or 32 for outputs of
+// few rows, so that enough CTAs stream the weights):
+//   warp 0 (one lane)  TMA: x1 tile [128 x 64] and x2 tile [64 x TN] (or [TN x 64] when x2 is given K-major) into a
+//                      ring of 4 to 6 stages, 128-byte swizzle, no multicast
+//   warp 1 (one lane)  tcgen05.mma M128 N<TN> K16, fp32 accumulators in TMEM (two accumulator buffers, so the epilogue
 //                      of one tile overlaps the products of the next)
 //   warps 2-5          epilogue: TMEM -> registers -> shared memory (transpose to whole rows) -> (+ bias) -> 16-byte stores
 //                      of the fp32 partial rows into EVERY rank's staging area over NVLink (peer pointers, this rank's
@@ -30,7 +31,9 @@
 // returns with TMEM freed.
 #include <cuda.h>
 
+#include <cstdlib>
 #include <mutex>
+#include <type_traits>
 
 #include "dev_util.cuh"
 #include "sm100_ptx.cuh"
@@ -42,22 +45,38 @@ namespace {
 
 using namespace sm100;  // NOLINT
 
-constexpr int TM = 128, TN = 128, TK = 64;   // tile of the output, K step of one ring stage
-constexpr int kStages = 4;
+constexpr int TM = 128, TK = 64;              // rows of an output tile, K step of one ring stage
+constexpr int kTileCap = 128;                 // widest tile; a group's capacity is counted in 128 x 128 tiles
+constexpr int kMaxStages = 6;
 constexpr int kThreads = 192;
 constexpr int kABytes = TM * TK * 2;          // 16 KB
-constexpr int kBBytes = TN * TK * 2;          // 16 KB
-constexpr int kRowPad = TN + 4;               // floats per row of the transpose buffer (16-byte stores without bank conflicts)
-constexpr int kOffA = 0;
-constexpr int kOffB = kOffA + kStages * kABytes;
-constexpr int kOffT = kOffB + kStages * kBBytes;               // transpose buffer: 4 warps x 32 rows x kRowPad floats
-constexpr int kTBytes = 4 * 32 * kRowPad * 4;
+constexpr int kRingBytes = 128 * 1024;        // stages of (x1 tile, x2 tile): 4 x 32 KB, 5 x 24 KB or 6 x 20 KB
+constexpr int kRowPadMax = kTileCap + 4;      // floats per row of the transpose buffer (16-byte stores without bank conflicts)
+constexpr int kOffRing = 0;
+constexpr int kOffT = kOffRing + kRingBytes;  // transpose buffer: 4 warps x 32 rows x (TN + 4) floats
+constexpr int kTBytes = 4 * 32 * kRowPadMax * 4;
 constexpr int kOffBar = kOffT + kTBytes;
-enum Bar { FULL = 0, EMPTY = kStages, ACC_FULL = 2 * kStages, ACC_EMPTY = 2 * kStages + 2, kNumBars = 2 * kStages + 4 };
+enum Bar { FULL = 0, EMPTY = kMaxStages, ACC_FULL = 2 * kMaxStages, ACC_EMPTY = 2 * kMaxStages + 2, kNumBars = 2 * kMaxStages + 4 };
 constexpr int kOffTmemSlot = kOffBar + kNumBars * 8;
 constexpr int kOffFlag = kOffTmemSlot + 8;
 constexpr int kSmemBytes = kOffFlag + 8;
-constexpr uint32_t kTmemCols = 256;           // two accumulators of 128 fp32 columns
+constexpr uint32_t kTmemCols = 256;           // two accumulators of up to 128 fp32 columns
+
+// Narrow tiles (TN = 64, 32) exist for outputs of few rows: the product is then bound by streaming the weights, and
+// 128-wide tiles would leave most SMs without work (N = 4096: 32 CTAs at TN = 128, 128 CTAs at TN = 32).
+template <int TN>
+struct Tile {
+    static constexpr int kBBytes = TN * TK * 2;
+    static constexpr int kStageBytes = kABytes + kBBytes;
+    static constexpr int kStages = kRingBytes / kStageBytes;        // 4, 5, 6
+    static constexpr int kRowPad = TN + 4;
+    static constexpr int kLanesPerRow = TN / 4;                     // a lane owns 4 columns
+    static constexpr int kRowsPerInstr = 32 / kLanesPerRow;         // rows one warp-wide access covers: 1, 2, 4
+    static constexpr size_t kPartialRowBytes = TN * 8, kPartialTileBytes = TM * kPartialRowBytes;
+    static constexpr size_t kResultRowBytes = TN * 4, kResultTileBytes = TM * kResultRowBytes;
+};
+constexpr size_t kPartialCapBytes = static_cast<size_t>(TM) * kTileCap * 8;   // room of one 128 x 128 tile of partials
+constexpr size_t kResultCapBytes = static_cast<size_t>(TM) * kTileCap * 4;
 
 // Data that carries its own arrival mark: a 64-bit word = (call number << 32) | 32 bits of payload, written and read
 // with single 64-bit accesses (two per 16-byte vector access), which are atomic: a reader that finds this call's number
@@ -85,20 +104,24 @@ __device__ __forceinline__ bool poll_again(unsigned long long& t0, volatile int*
     return true;
 }
 
-// Byte offsets inside one rank's area. A partial tile row is 1 KB: words (x, y) of lane l at 16 l, words (z, w) at
-// 512 + 16 l, so that each of the two stores of a warp covers 512 contiguous bytes. A result row is 512 bytes.
-constexpr size_t kPartialRowBytes = 1024, kPartialTileBytes = TM * kPartialRowBytes;
-constexpr size_t kResultRowBytes = 512, kResultTileBytes = TM * kResultRowBytes;
+// Byte offsets inside one rank's area. A partial row holds words (x, y) of the lane that owns columns 4c .. 4c+3 at
+// 16 c and its words (z, w) at TN * 4 + 16 c, so that each of a warp's two stores covers whole 512-byte runs. Tiles of
+// any width are packed into regions sized for max_tiles tiles of 128 x 128.
+template <int TN>
 __device__ __forceinline__ size_t partial_slot(int buf, int world, int src, int max_tiles, int tile) {
-    return ((static_cast<size_t>(buf) * world + src) * max_tiles + tile) * kPartialTileBytes;
+    return (static_cast<size_t>(buf) * world + src) * max_tiles * kPartialCapBytes + static_cast<size_t>(tile) * Tile<TN>::kPartialTileBytes;
 }
+template <int TN>
 __device__ __forceinline__ size_t result_slot(int buf, int max_tiles, int tile) {
-    return (static_cast<size_t>(buf) * max_tiles + tile) * kResultTileBytes;
+    return static_cast<size_t>(buf) * max_tiles * kResultCapBytes + static_cast<size_t>(tile) * Tile<TN>::kResultTileBytes;
 }
 
-template <bool BF16, bool B_KMAJOR>
+template <bool BF16, bool B_KMAJOR, int TN>
 __global__ void __launch_bounds__(kThreads, 1) matmul_allreduce_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                                                                         const MatmulAllReduceArgs a) {
+    using TL = Tile<TN>;
+    constexpr int kStages = TL::kStages;
+    static_assert(B_KMAJOR || TN >= 64, "an MN-major x2 tile is made of 64-column boxes");
     extern __shared__ __align__(1024) unsigned char smem[];
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kOffBar);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + kOffTmemSlot);
@@ -145,13 +168,15 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_allreduce_kernel(const __g
                     const int s = it % kStages;
                     const uint32_t ph = static_cast<uint32_t>((it / kStages) & 1);
                     if (!mbar_wait(bar(EMPTY + s), ph ^ 1u, give_up)) goto producer_done;
-                    mbar_expect_tx(bar(FULL + s), kABytes + kBBytes);
-                    tma_load_2d(smem_u32(smem + kOffA + s * kABytes), &map_a, kb * TK, m0, bar(FULL + s));
+                    mbar_expect_tx(bar(FULL + s), TL::kStageBytes);
+                    const uint32_t a_dst = smem_u32(smem + kOffRing + s * TL::kStageBytes), b_dst = a_dst + kABytes;
+                    tma_load_2d(a_dst, &map_a, kb * TK, m0, bar(FULL + s));
                     if (B_KMAJOR) {
-                        tma_load_2d(smem_u32(smem + kOffB + s * kBBytes), &map_b, kb * TK, n0, bar(FULL + s));
-                    } else {  // two boxes of 64 columns x 64 k
-                        tma_load_2d(smem_u32(smem + kOffB + s * kBBytes), &map_b, n0, kb * TK, bar(FULL + s));
-                        tma_load_2d(smem_u32(smem + kOffB + s * kBBytes + TK * 128), &map_b, n0 + 64, kb * TK, bar(FULL + s));
+                        tma_load_2d(b_dst, &map_b, kb * TK, n0, bar(FULL + s));          // [TN rows of x2^T x 64 k]
+                    } else {
+#pragma unroll
+                        for (int nb = 0; nb < TN / 64; ++nb)                              // boxes of 64 columns x 64 k
+                            tma_load_2d(b_dst + nb * TK * 128, &map_b, n0 + nb * 64, kb * TK, bar(FULL + s));
                     }
                 }
             }
@@ -174,13 +199,13 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_allreduce_kernel(const __g
                         break;
                     }
                     tc_fence_after();
-                    const uint32_t a_addr = smem_u32(smem + kOffA + s * kABytes), b_addr = smem_u32(smem + kOffB + s * kBBytes);
+                    const uint32_t a_addr = smem_u32(smem + kOffRing + s * TL::kStageBytes), b_addr = a_addr + kABytes;
 #pragma unroll
                     for (int t = 0; t < TK / 16; ++t) {
                         const uint64_t ad = make_desc(a_addr + t * 32, 0, 1024);   // K-major: 16 k = 32 bytes inside the swizzled row
                         const uint64_t bd = B_KMAJOR ? make_desc(b_addr + t * 32, 0, 1024)
                                                      : make_desc(b_addr + t * 16 * 128, TK * 128, 1024);  // MN-major: 16 k = 16 rows; next 64 columns 8 KB on
-                        umma(tmem_base + acc * TN, ad, bd, idesc, (kb > 0 || t > 0) ? 1u : 0u);
+                        umma(tmem_base + acc * kTileCap, ad, bd, idesc, (kb > 0 || t > 0) ? 1u : 0u);
                     }
                     umma_commit(bar(EMPTY + s));
                 }
@@ -190,9 +215,11 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_allreduce_kernel(const __g
         }
     } else {
         // ================================ epilogue warps ================================
+        constexpr int LPR = TL::kLanesPerRow, RPI = TL::kRowsPerInstr;
         const int quarter = warp & 3;                    // the TMEM lane quarter this warp may touch
+        const int sub = lane / LPR, cl = lane % LPR;     // row inside one warp-wide access, 4-column group inside the row
         const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
-        float* tbuf = reinterpret_cast<float*>(smem + kOffT) + quarter * 32 * kRowPad;
+        float* tbuf = reinterpret_cast<float*>(smem + kOffT) + quarter * 32 * kRowPadMax;
         bool ok = true;
         int nt = 0;
         // ---- first pass: every tile of this CTA, product -> partial rows into the staging areas -----------------------
@@ -207,19 +234,19 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_allreduce_kernel(const __g
 #pragma unroll
             for (int c4 = 0; c4 < TN / 32; ++c4) {
                 uint32_t u[32];
-                tmem_ld32(lane_base + acc * TN + c4 * 32, u);
+                tmem_ld32(lane_base + acc * kTileCap + c4 * 32, u);
                 tmem_wait_ld();
 #pragma unroll
                 for (int c = 0; c < 32; c += 4) {
                     float4 v = make_float4(__uint_as_float(u[c]), __uint_as_float(u[c + 1]), __uint_as_float(u[c + 2]), __uint_as_float(u[c + 3]));
-                    *reinterpret_cast<float4*>(tbuf + lane * kRowPad + c4 * 32 + c) = v;   // thread = row of the tile
+                    *reinterpret_cast<float4*>(tbuf + lane * TL::kRowPad + c4 * 32 + c) = v;   // thread = row of the tile
                 }
             }
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar(ACC_EMPTY + acc));   // the accumulator may be overwritten by the tile after next
-            // whole rows now: lane l owns columns 4l .. 4l+3 of each of this warp's 32 rows
-            const int col = n0 + 4 * lane;
+            // whole rows now: a lane owns columns 4 cl .. 4 cl + 3 of the rows sub, sub + RPI, ... of this warp's slab
+            const int col = n0 + 4 * cl;
             float4 bias4 = make_float4(0.f, 0.f, 0.f, 0.f);
             if (a.bias != nullptr && col < a.N) {
                 if (BF16) {
@@ -231,23 +258,23 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_allreduce_kernel(const __g
                 }
             }
             const int rows_here = min(32, a.M - (m0 + quarter * 32));   // rows of this warp's slab that exist
-            const size_t slot = partial_slot(buf, a.world, a.rank, a.max_tiles, tile);
+            const size_t slot = partial_slot<TN>(buf, a.world, a.rank, a.max_tiles, tile);
             const int owner = tile % a.world;
             if (col < a.N) {
-                for (int rr = 0; rr < rows_here; ++rr) {
-                    float4 v = *reinterpret_cast<const float4*>(tbuf + rr * kRowPad + 4 * lane);
+                for (int rr = sub; rr < rows_here; rr += RPI) {
+                    float4 v = *reinterpret_cast<const float4*>(tbuf + rr * TL::kRowPad + 4 * cl);
                     v.x += bias4.x;
                     v.y += bias4.y;
                     v.z += bias4.z;
                     v.w += bias4.w;
-                    const size_t off = slot + static_cast<size_t>(quarter * 32 + rr) * kPartialRowBytes + 16 * lane;
+                    const size_t off = slot + static_cast<size_t>(quarter * 32 + rr) * TL::kPartialRowBytes + 16 * cl;
                     if (a.two_shot) {
                         st_pair(a.peer_stage[owner] + off, __float_as_uint(v.x), __float_as_uint(v.y), epoch);
-                        st_pair(a.peer_stage[owner] + off + 512, __float_as_uint(v.z), __float_as_uint(v.w), epoch);
+                        st_pair(a.peer_stage[owner] + off + TN * 4, __float_as_uint(v.z), __float_as_uint(v.w), epoch);
                     } else {
                         for (int p = 0; p < a.world; ++p) {
                             st_pair(a.peer_stage[p] + off, __float_as_uint(v.x), __float_as_uint(v.y), epoch);
-                            st_pair(a.peer_stage[p] + off + 512, __float_as_uint(v.z), __float_as_uint(v.w), epoch);
+                            st_pair(a.peer_stage[p] + off + TN * 4, __float_as_uint(v.z), __float_as_uint(v.w), epoch);
                         }
                     }
                 }
@@ -256,20 +283,21 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_allreduce_kernel(const __g
         }
 
         // ---- second pass: add the partials of all ranks in rank order (two-shot: only for the tiles this rank owns) ----
+        // The rows of a tile are dealt out to the four warps: warp q takes rows q, q + 4, q + 8, ...; entry e of that
+        // list is row q + 4 e, and one warp-wide access covers RPI consecutive entries.
         const unsigned char* my_stage = a.peer_stage[a.rank];
-        constexpr int RB = 8;   // rows in flight per warp
+        constexpr int RB = 8;   // accesses in flight per warp
         for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x) {
             if (a.two_shot && tile % a.world != a.rank) continue;
             const int m0 = (tile / tiles_n) * TM, n0 = (tile % tiles_n) * TN;
-            const int col = n0 + 4 * lane;
+            const int col = n0 + 4 * cl;
             const int rows_valid = min(TM, a.M - m0);
-            // the rows of a tile are dealt out to the four warps: row0 = warp's number, then every fourth row
-            for (int row0 = quarter; ok && row0 < rows_valid; row0 += 4 * RB) {
+            for (int e0 = 0; ok && quarter + 4 * e0 < rows_valid; e0 += RB * RPI) {
                 float4 sum[RB];
 #pragma unroll
                 for (int i = 0; i < RB; ++i) sum[i] = make_float4(0.f, 0.f, 0.f, 0.f);
                 for (int r = 0; ok && r < a.world; ++r) {
-                    const unsigned char* src = my_stage + partial_slot(buf, a.world, r, a.max_tiles, tile) + 16 * lane;
+                    const unsigned char* src = my_stage + partial_slot<TN>(buf, a.world, r, a.max_tiles, tile) + 16 * cl;
                     uint32_t w[RB][4];
                     unsigned long long t0 = 0;
                     for (;;) {   // until every word of the batch carries this call's number
@@ -277,11 +305,11 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_allreduce_kernel(const __g
                         if (col < a.N) {
 #pragma unroll
                             for (int i = 0; i < RB; ++i) {
-                                const int row = row0 + 4 * i;
+                                const int row = quarter + 4 * (e0 + i * RPI + sub);
                                 if (row < rows_valid) {
-                                    const unsigned char* q = src + static_cast<size_t>(row) * kPartialRowBytes;
+                                    const unsigned char* q = src + static_cast<size_t>(row) * TL::kPartialRowBytes;
                                     here &= ld_pair(q, epoch, w[i][0], w[i][1]);
-                                    here &= ld_pair(q + 512, epoch, w[i][2], w[i][3]);
+                                    here &= ld_pair(q + TN * 4, epoch, w[i][2], w[i][3]);
                                 }
                             }
                         }
@@ -294,7 +322,7 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_allreduce_kernel(const __g
                     if (!ok) break;
 #pragma unroll
                     for (int i = 0; i < RB; ++i) {
-                        if (row0 + 4 * i < rows_valid) {
+                        if (quarter + 4 * (e0 + i * RPI + sub) < rows_valid) {
                             sum[i].x += __uint_as_float(w[i][0]);
                             sum[i].y += __uint_as_float(w[i][1]);
                             sum[i].z += __uint_as_float(w[i][2]);
@@ -305,7 +333,7 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_allreduce_kernel(const __g
                 if (!ok || col >= a.N) continue;
 #pragma unroll
                 for (int i = 0; i < RB; ++i) {
-                    const int row = row0 + 4 * i;
+                    const int row = quarter + 4 * (e0 + i * RPI + sub);
                     if (row < rows_valid) {
                         uint2 packed;
                         if (BF16) {
@@ -319,7 +347,7 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_allreduce_kernel(const __g
                         }
                         *reinterpret_cast<uint2*>(static_cast<unsigned char*>(a.out) + (static_cast<int64_t>(m0 + row) * a.out_s0 + col) * 2) = packed;
                         if (a.two_shot) {   // and the finished rows to every other rank's result area
-                            const size_t roff = result_slot(buf, a.max_tiles, tile) + static_cast<size_t>(row) * kResultRowBytes + 16 * lane;
+                            const size_t roff = result_slot<TN>(buf, a.max_tiles, tile) + static_cast<size_t>(row) * TL::kResultRowBytes + 16 * cl;
                             for (int p = 0; p < a.world; ++p)
                                 if (p != a.rank) st_pair(a.peer_result[p] + roff, packed.x, packed.y, epoch);
                         }
@@ -334,10 +362,10 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_allreduce_kernel(const __g
             for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x) {
                 if (tile % a.world == a.rank) continue;   // written straight to out above
                 const int m0 = (tile / tiles_n) * TM, n0 = (tile % tiles_n) * TN;
-                const int col = n0 + 4 * lane;
+                const int col = n0 + 4 * cl;
                 const int rows_valid = min(TM, a.M - m0);
-                const unsigned char* src = my_result + result_slot(buf, a.max_tiles, tile) + 16 * lane;
-                for (int row0 = quarter; ok && row0 < rows_valid; row0 += 4 * RB) {
+                const unsigned char* src = my_result + result_slot<TN>(buf, a.max_tiles, tile) + 16 * cl;
+                for (int e0 = 0; ok && quarter + 4 * e0 < rows_valid; e0 += RB * RPI) {
                     uint32_t w[RB][2];
                     unsigned long long t0 = 0;
                     for (;;) {
@@ -345,12 +373,12 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_allreduce_kernel(const __g
                         if (col < a.N) {
 #pragma unroll
                             for (int i = 0; i < RB; ++i) {
-                                const int row = row0 + 4 * i;
-                                if (row < rows_valid) here &= ld_pair(src + static_cast<size_t>(row) * kResultRowBytes, epoch, w[i][0], w[i][1]);
+                                const int row = quarter + 4 * (e0 + i * RPI + sub);
+                                if (row < rows_valid) here &= ld_pair(src + static_cast<size_t>(row) * TL::kResultRowBytes, epoch, w[i][0], w[i][1]);
                             }
                         }
                         if (__all_sync(0xffffffffu, here ? 1 : 0)) break;
-                        if (!__all_sync(0xffffffffu, poll_again(t0, give_up) ? 1 : 0)) {   // the warp stops as one
+                        if (!__all_sync(0xffffffffu, poll_again(t0, give_up) ? 1 : 0)) {
                             ok = false;
                             break;
                         }
@@ -358,7 +386,7 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_allreduce_kernel(const __g
                     if (!ok || col >= a.N) continue;
 #pragma unroll
                     for (int i = 0; i < RB; ++i) {
-                        const int row = row0 + 4 * i;
+                        const int row = quarter + 4 * (e0 + i * RPI + sub);
                         if (row < rows_valid)
                             *reinterpret_cast<uint2*>(static_cast<unsigned char*>(a.out) + (static_cast<int64_t>(m0 + row) * a.out_s0 + col) * 2) =
                                 make_uint2(w[i][0], w[i][1]);
@@ -420,7 +448,8 @@ bool make_map_2d(CUtensorMap* map, const void* base, int64_t inner, int64_t oute
 
 }  // namespace
 
-int matmul_allreduce_tiles(int64_t M, int64_t N) { return static_cast<int>(((M + TM - 1) / TM) * ((N + TN - 1) / TN)); }
+// Capacity is counted in 128 x 128 tiles whatever width the kernel then picks.
+int matmul_allreduce_tiles(int64_t M, int64_t N) { return static_cast<int>(((M + TM - 1) / TM) * ((N + kTileCap - 1) / kTileCap)); }
 
 // One rank's area: partial tiles [2 halves][world sources][max_tiles] (fp32 with arrival marks, 128 KB each), finished
 // tiles [2][max_tiles] (16-bit with arrival marks, 64 KB each, two-shot form) and two control words (calls finished,
@@ -429,9 +458,9 @@ MarLayout matmul_allreduce_layout(int world, int max_tiles) {
     MarLayout l;
     size_t off = 0;
     l.stage_off = off;
-    off += static_cast<size_t>(2) * world * max_tiles * kPartialTileBytes;
+    off += static_cast<size_t>(2) * world * max_tiles * kPartialCapBytes;
     l.result_off = off;
-    off += static_cast<size_t>(2) * max_tiles * kResultTileBytes;
+    off += static_cast<size_t>(2) * max_tiles * kResultCapBytes;
     l.ctrl_off = off;
     off += 2 * sizeof(uint32_t);
     l.bytes = (off + 255) / 256 * 256;
@@ -448,21 +477,40 @@ const char* launch_matmul_allreduce(const MatmulAllReduceArgs& a, int sm_count, 
     if (!al(a.x1, a.x1_ld) || !al(a.x2, a.x2_ld) || !al(a.out, a.out_s0 * 1) || (a.out_s0 * 2) % 8 != 0)
         return "x1, x2 and out need 16-byte aligned bases and row pitches that are multiples of 16 bytes";
     const bool bf16 = a.dt == Dt::BF16;
+    // Tile width: 128 when there are enough 128-wide tiles to occupy the SMs; else narrower, so that more CTAs stream
+    // the weights (32 needs x2 K-major: an MN-major tile is made of 64-column boxes). DIOPI_B200_MAR_TN forces a width.
+    const int64_t row_tiles = (a.M + TM - 1) / TM;
+    int tn = 128;
+    if (row_tiles * ((a.N + 127) / 128) * 2 <= sm_count) tn = (a.x2_kmajor && row_tiles * ((a.N + 63) / 64) * 2 <= sm_count * 2) ? 32 : 64;
+    if (const char* v = std::getenv("DIOPI_B200_MAR_TN")) {
+        const int f = std::atoi(v);
+        if (f == 128 || f == 64 || (f == 32 && a.x2_kmajor)) tn = f;
+    }
     CUtensorMap ma, mb;
     if (!make_map_2d(&ma, a.x1, a.K, a.M, a.x1_ld, TM, bf16)) return "cuTensorMapEncodeTiled failed for x1";
-    const bool okb = a.x2_kmajor ? make_map_2d(&mb, a.x2, a.K, a.N, a.x2_ld, TN, bf16) : make_map_2d(&mb, a.x2, a.N, a.K, a.x2_ld, TK, bf16);
+    const bool okb = a.x2_kmajor ? make_map_2d(&mb, a.x2, a.K, a.N, a.x2_ld, tn, bf16) : make_map_2d(&mb, a.x2, a.N, a.K, a.x2_ld, TK, bf16);
     if (!okb) return "cuTensorMapEncodeTiled failed for x2";
-    const int n_tiles = matmul_allreduce_tiles(a.M, a.N);
+    const int n_tiles = static_cast<int>(row_tiles * ((a.N + tn - 1) / tn));
     const int grid = std::min(n_tiles, sm_count);
     auto go = [&](auto kern) {
         cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
         kern<<<grid, kThreads, kSmemBytes, st>>>(ma, mb, a);
     };
-    if (bf16) {
-        if (a.x2_kmajor) go(matmul_allreduce_kernel<true, true>); else go(matmul_allreduce_kernel<true, false>);
-    } else {
-        if (a.x2_kmajor) go(matmul_allreduce_kernel<false, true>); else go(matmul_allreduce_kernel<false, false>);
-    }
+    auto pick = [&](auto bf) {
+        constexpr bool B = decltype(bf)::value;
+        if (a.x2_kmajor) {
+            if (tn == 128) go(matmul_allreduce_kernel<B, true, 128>);
+            else if (tn == 64) go(matmul_allreduce_kernel<B, true, 64>);
+            else go(matmul_allreduce_kernel<B, true, 32>);
+        } else {
+            if (tn == 128) go(matmul_allreduce_kernel<B, false, 128>);
+            else go(matmul_allreduce_kernel<B, false, 64>);
+        }
+    };
+    if (bf16)
+        pick(std::true_type{});
+    else
+        pick(std::false_type{});
     return nullptr;
 }
 

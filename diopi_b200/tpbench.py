@@ -62,6 +62,7 @@ def main():
     ap.add_argument("--iters", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--check", action="store_true")
+    ap.add_argument("--x2", default="rowmajor", choices=["rowmajor", "kmajor"], help="kmajor: x2 is the transposed view of an [N, K] weight")
     args = ap.parse_args()
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -78,8 +79,10 @@ def main():
     tp_group.create("tp", max_tiles=tiles)
     ctx = Context()
     x1, x2, bias = inputs(rank, M, K, N, dtype, "cuda")
+    if args.x2 == "kmajor":
+        x2 = x2.t().contiguous().t()   # same values, stored as [N, K]
     out = torch.empty(M, N, dtype=dtype, device="cuda")
-    rec = {"op": "matmul_all_reduce", "mode": os.environ.get("DIOPI_B200_MAR_MODE", "auto"), "world": world, "M": M, "N": N, "K_per_rank": K, "dtype": args.dtype}
+    rec = {"op": "matmul_all_reduce", "mode": os.environ.get("DIOPI_B200_MAR_MODE", "auto"), "world": world, "M": M, "N": N, "K_per_rank": K, "dtype": args.dtype, "x2": args.x2}
 
     # handles made once, the entry point called directly: the host side of a call is then a few microseconds, as it is
     # for a C++ consumer, and the figure is the device's

@@ -42,6 +42,21 @@ def test_one_rank_matches_oracle(F, dtype, shape):
     torch.testing.assert_close(got2.cpu().float(), golden.matmul_all_reduce([x1], [x2]).float(), rtol=1e-2, atol=1e-2)
 
 
+@pytest.mark.parametrize("tn", ["128", "64", "32"])
+@pytest.mark.parametrize("kmajor", [False, True])
+def test_tile_widths(F, monkeypatch, tn, kmajor):
+    """Every tile width the launch can pick (DIOPI_B200_MAR_TN forces one; 32 exists only for a K-major x2, where the
+    request is ignored otherwise), on shapes with ragged edges in all three extents."""
+    monkeypatch.setenv("DIOPI_B200_MAR_TN", tn)
+    for (M, K, N) in ((64, 512, 1024), (37, 200, 328), (130, 64, 96)):
+        x1, b = rand((M, K), torch.bfloat16, 20 + M), rand((N,), torch.bfloat16, 21)
+        w = rand((N, K), torch.bfloat16, 22 + N, K ** -0.5)
+        x2 = w.t() if kmajor else w.t().contiguous()
+        want = golden.matmul_all_reduce([x1], [x2], [b])
+        got = F.matmul_all_reduce(x1.cuda(), (w.cuda().t() if kmajor else x2.cuda()), b.cuda(), "solo")
+        torch.testing.assert_close(got.cpu().float(), want.float(), rtol=1e-2, atol=1e-2)
+
+
 def test_transposed_weight_and_stacked_rows(F):
     dtype = torch.bfloat16
     x1 = rand((2, 70, 128), dtype, 4)
