@@ -38,7 +38,7 @@ FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum per token of one decode_split_kernel launch, from the ncu capture
 # of the quarter-size case summarised in profiles/decode_split_kernel_cfg2.md (660.0 MB for 40 019 tokens); the
 # traffic of a launch grows with its token count, so it is scaled by the workload's tokens.
-NCU_TRAFFIC_BYTES_PER_TOKEN = 659.979e6 / 40019
+NCU_TRAFFIC_BYTES_PER_TOKEN = 661.483e6 / 40019
 
 
 def measured_peak():
