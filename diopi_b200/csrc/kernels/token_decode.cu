@@ -66,9 +66,6 @@ struct SplitPlan {
     int ups;           // token groups per ring slot (1, 2 or 4): a tile of TPG groups spans TPG / ups ring slots
     int pdl;           // launch the merge kernel as a programmatic dependent
     int producer_warps;
-    int merge;         // 1: the last CTA to finish a request merges its partials and writes out (no second kernel)
-    int off_ticket;    // shared-memory word that hands the arrival ticket to the consumer warps
-    int* counters;     // [B * n_hg] arrival counters, zeroed before the launch (merge == 1)
 };
 
 // ---------------------------------------------------------------------------
@@ -424,16 +421,6 @@ __global__ void __launch_bounds__(kThreads, 1) decode_split_kernel(const DecodeA
             fetch_logits();
         }
 
-        if (p.merge && kHasV && cta == 0 && real && g == 0) {
-            // requests without a token are nobody's part: their rows of out are zeros
-            for (int i = 0; i < a.B; ++i) {
-                if (pre[i + 1] != pre[i]) continue;
-                T* z = static_cast<T*>(a.out) + static_cast<int64_t>(i) * a.out_s0 + static_cast<int64_t>(h) * a.out_s1 + static_cast<int64_t>(lih * EPC) * a.out_s2;
-#pragma unroll
-                for (int e = 0; e < EPC; ++e) z[e * a.out_s2] = Cvt<T>::from_f(0.f);
-            }
-        }
-
         StageWalk walk;
         walk.init(pre, a.B, t0, t1);
         int req, j0, cnt;
@@ -616,81 +603,12 @@ __global__ void __launch_bounds__(kThreads, 1) decode_split_kernel(const DecodeA
                     if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&bars[2 * p.nstages + 1]), red_phase, give_up) ? 1 : 0)) break;
                     red_phase ^= 1u;
                 }
-                // Which CTAs hold a part of this request: CTA c owns tokens [total * c / n_cta, total * (c + 1) / n_cta).
-                int c_first = cta, c_last = cta, n_parts = 1;
-                if (p.merge) {
-                    auto cta_of = [&](int t) { return static_cast<int>(((static_cast<int64_t>(t) + 1) * p.n_cta + total - 1) / total) - 1; };
-                    c_first = cta_of(pre[req]);
-                    c_last = cta_of(pre[req + 1] - 1);
-                    n_parts = c_last - c_first + 1;
-                    if (total < p.n_cta) {   // some CTAs own no token: they neither write a part nor arrive
-                        n_parts = 0;
-                        for (int cc = c_first; cc <= c_last; ++cc)
-                            n_parts += static_cast<int>(static_cast<int64_t>(total) * cc / p.n_cta) != static_cast<int>(static_cast<int64_t>(total) * (cc + 1) / p.n_cta);
-                    }
-                }
-                T* orow = static_cast<T*>(a.out) + static_cast<int64_t>(req) * a.out_s0 + static_cast<int64_t>(h) * a.out_s1 + static_cast<int64_t>(lih * EPC) * a.out_s2;
-                if (p.merge && n_parts == 1) {
-                    // the whole request ran in this CTA: finish it here, nothing goes through memory
-                    if (real && g == 0) {
-                        const float inv = l > 0.f ? 1.f / l : 0.f;
+                if (real && g == 0) {
+                    const int64_t slot_id = static_cast<int64_t>(cta) + req;
+                    float* dst = ws_acc + (slot_id * a.H + h) * a.D + lih * EPC;
 #pragma unroll
-                        for (int e = 0; e < EPC; ++e) orow[e * a.out_s2] = Cvt<T>::from_f(acc[e] * inv);
-                    }
-                } else {
-                    if (real && g == 0) {
-                        const int64_t slot_id = static_cast<int64_t>(cta) + req;
-                        float* dst = ws_acc + (slot_id * a.H + h) * a.D + lih * EPC;
-#pragma unroll
-                        for (int e = 0; e < EPC; e += 4) *reinterpret_cast<float4*>(dst + e) = make_float4(acc[e], acc[e + 1], acc[e + 2], acc[e + 3]);
-                        if (lih == 0) *reinterpret_cast<float2*>(ws_ml + (slot_id * a.H + h) * 2) = make_float2(m, l);
-                    }
-                    if (p.merge) {
-                        // Arrival ticket: every part is in memory before its CTA counts itself in; the CTA that draws the last
-                        // ticket reads all parts (in CTA order, whatever the order of arrival) and writes the request's rows.
-                        __threadfence();
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive(smem_u32(&bars[2 * p.nstages]));
-                        if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&bars[2 * p.nstages]), red_phase, give_up) ? 1 : 0)) break;
-                        volatile int* ticket = reinterpret_cast<volatile int*>(smem + p.off_ticket);
-                        if (tid == 0) *ticket = atomicAdd(p.counters + static_cast<int64_t>(req) * gridDim.y + blockIdx.y, 1);
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive(smem_u32(&bars[2 * p.nstages + 1]));
-                        if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&bars[2 * p.nstages + 1]), red_phase, give_up) ? 1 : 0)) break;
-                        red_phase ^= 1u;
-                        if (*ticket == n_parts - 1) {
-                            __threadfence();
-                            if (real && g == 0) {
-                                float M = -INFINITY, Lsum = 0.f;
-                                float o[EPC];
-#pragma unroll
-                                for (int e = 0; e < EPC; ++e) o[e] = 0.f;
-                                auto owns = [&](int cc) { return static_cast<int>(static_cast<int64_t>(total) * cc / p.n_cta) != static_cast<int>(static_cast<int64_t>(total) * (cc + 1) / p.n_cta); };
-                                for (int cc = c_first; cc <= c_last; ++cc)
-                                    if (owns(cc)) M = fmaxf(M, __ldcg(ws_ml + ((static_cast<int64_t>(cc) + req) * a.H + h) * 2));
-                                const float Mr = (M == -INFINITY) ? 0.f : M;
-                                for (int cc = c_first; cc <= c_last; ++cc) {
-                                    if (!owns(cc)) continue;
-                                    const int64_t slot_id = static_cast<int64_t>(cc) + req;
-                                    const float2 ml = __ldcg(reinterpret_cast<const float2*>(ws_ml + (slot_id * a.H + h) * 2));
-                                    const float w = exp2f(ml.x - Mr);
-                                    Lsum = fmaf(ml.y, w, Lsum);
-                                    const float* src = ws_acc + (slot_id * a.H + h) * a.D + lih * EPC;
-#pragma unroll
-                                    for (int e = 0; e < EPC; e += 4) {
-                                        const float4 v = __ldcg(reinterpret_cast<const float4*>(src + e));
-                                        o[e] = fmaf(v.x, w, o[e]);
-                                        o[e + 1] = fmaf(v.y, w, o[e + 1]);
-                                        o[e + 2] = fmaf(v.z, w, o[e + 2]);
-                                        o[e + 3] = fmaf(v.w, w, o[e + 3]);
-                                    }
-                                }
-                                const float inv = Lsum > 0.f ? 1.f / Lsum : 0.f;
-#pragma unroll
-                                for (int e = 0; e < EPC; ++e) orow[e * a.out_s2] = Cvt<T>::from_f(o[e] * inv);
-                            }
-                        }
-                    }
+                    for (int e = 0; e < EPC; e += 4) *reinterpret_cast<float4*>(dst + e) = make_float4(acc[e], acc[e + 1], acc[e + 2], acc[e + 3]);
+                    if (lih == 0) *reinterpret_cast<float2*>(ws_ml + (slot_id * a.H + h) * 2) = make_float2(m, l);
                 }
             }
         }
@@ -959,7 +877,6 @@ bool make_split_plan(const DecodeArgs& a, int sm_count, int max_smem, SplitPlan&
         take((a.B + 1) * 4, 4);
         take(red_bytes, 16);
         take(4, 4);
-        take(4, 4);
         fixed = off + 128;
     }
     int nst = (budget - fixed) / p.stage_bytes;
@@ -971,10 +888,7 @@ bool make_split_plan(const DecodeArgs& a, int sm_count, int max_smem, SplitPlan&
     p.off_pre = take((a.B + 1) * 4, 4);
     p.off_red = take(red_bytes, 16);
     p.off_flag = take(4, 4);
-    p.off_ticket = take(4, 4);
     p.smem_bytes = off;
-    p.merge = has_v ? env_int("DIOPI_B200_DECODE_MERGE", 0) : 0;
-    p.counters = nullptr;
 
     // One CTA per SM (times ctas_per_sm) over the head groups, but no more CTAs than there can be work for.
     int n_cta = std::max(1, sm_count * ctas_per_sm / p.n_hg);
@@ -988,7 +902,6 @@ bool make_split_plan(const DecodeArgs& a, int sm_count, int max_smem, SplitPlan&
 template <typename T, int LPH, int MODE>
 void launch_split_t(const DecodeArgs& a, const SplitPlan& p, float* ws_acc, float* ws_ml, cudaStream_t st) {
     dim3 grid(p.n_cta, p.n_hg);
-    if (p.merge && p.counters != nullptr) cudaMemsetAsync(p.counters, 0, static_cast<size_t>(a.B) * p.n_hg * sizeof(int), st);
     constexpr bool fused = MODE == static_cast<int>(DecodeMode::FUSED);
     // fused: 4 token groups per tile (2 with DIOPI_B200_DECODE_TPG=2); one matrix only: 8, so that a tile is 64 KB either way
     if (fused && p.tpg == 2) {
@@ -1000,7 +913,7 @@ void launch_split_t(const DecodeArgs& a, const SplitPlan& p, float* ws_acc, floa
         cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, p.smem_bytes);
         kern<<<grid, kConsumerThreads + 32 * p.producer_warps, p.smem_bytes, st>>>(a, p, ws_acc, ws_ml);
     }
-    if (MODE != static_cast<int>(DecodeMode::QK) && !p.merge) {
+    if (MODE != static_cast<int>(DecodeMode::QK)) {
         // Programmatic dependent launch: the merge kernel's launch latency and set-up overlap the split kernel.
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(a.B, (a.H + 3) / 4);
@@ -1090,7 +1003,7 @@ int64_t decode_workspace_bytes(const DecodeArgs& a, int sm_count, int max_smem) 
     SplitPlan p;
     if (a.mode == DecodeMode::QK) return 0;
     if (!make_split_plan(a, sm_count, max_smem, p)) return 0;
-    return (split_ws_floats_acc(a, p) + split_ws_floats_ml(a, p)) * 4 + static_cast<int64_t>(a.B) * p.n_hg * 4 + 256;
+    return (split_ws_floats_acc(a, p) + split_ws_floats_ml(a, p)) * 4 + 256;
 }
 
 void launch_decode(const DecodeArgs& a, void* ws, int sm_count, int max_smem, cudaStream_t st) {
@@ -1104,7 +1017,6 @@ void launch_decode(const DecodeArgs& a, void* ws, int sm_count, int max_smem, cu
             uintptr_t base = (reinterpret_cast<uintptr_t>(ws) + 255) & ~static_cast<uintptr_t>(255);
             ws_acc = reinterpret_cast<float*>(base);
             ws_ml = ws_acc + split_ws_floats_acc(a, p);
-            p.counters = reinterpret_cast<int*>(ws_ml + split_ws_floats_ml(a, p));
         }
         switch (a.dt) {
             case Dt::F16: launch_split_mode<__half>(a, p, ws_acc, ws_ml, st); break;
