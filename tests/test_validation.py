@@ -154,3 +154,45 @@ def test_zero_size_inputs_succeed_without_a_device(F):
                         torch.zeros(0, dtype=torch.int32), 0, as_device=True)
     a = decode_args(B=0)
     F.token_decode_attention(a["q"], a["k"], a["v"], a["out"], a["b_loc"], a["st"], a["ln"], 4, as_device=True)
+
+
+def test_new_entry_points_validation(F):
+    """RMSNorm backward, the rope + copy call and MatmulAllReduce refuse bad arguments before any CUDA work."""
+    x = torch.zeros(4, 64, dtype=torch.float16)
+    w = torch.zeros(64, dtype=torch.float16)
+    inv = torch.zeros(4, dtype=torch.float32)
+    fails(ERROR_OCCURRED, F.rms_norm_backward, x, x, w, None, inv, (32,), 1e-6, match="normalized_shape")
+    fails(ERROR_OCCURRED, F.rms_norm_backward, x, x, w, None, inv[:3], (64,), 1e-6, match="inv_rms")
+    fails(ERROR_OCCURRED, F.rms_norm_backward, x.float(), x, w, None, inv, (64,), 1e-6, match="share a dtype")
+    fails(DTYPE_NOT_SUPPORTED, F.rms_norm_backward, x, x, w, None, inv.to(torch.int32), (64,), 1e-6, match="inv_rms")
+
+    q, k = torch.zeros(5, 4, 64, dtype=torch.float16), torch.zeros(5, 2, 64, dtype=torch.float16)
+    cs = torch.zeros(5, 1, 32, dtype=torch.float16)
+    pool = torch.zeros(40, 2, 64, dtype=torch.float16)
+    dest = torch.zeros(5, dtype=torch.int32)
+    fails(ERROR_OCCURRED, F.rotary_emb_copy_kv, q, k, k, cs, cs, dest, pool, None, match="given together")
+    fails(ERROR_OCCURRED, F.rotary_emb_copy_kv, q, k, None, cs, cs, dest[:3], pool, None, match="dest_loc")
+    fails(ERROR_OCCURRED, F.rotary_emb_copy_kv, q, k[:, :, :32], None, cs, cs, dest, pool, None, match="kv_heads")
+    fails(DTYPE_NOT_SUPPORTED, F.rotary_emb_copy_kv, q, k, None, cs, cs, dest.float(), pool, None, match="int32 or int64")
+
+    a, b = torch.zeros(8, 64, dtype=torch.float16), torch.zeros(64, 128, dtype=torch.float16)
+    fails(NO_IMPLEMENT, F.matmul_all_reduce, a, b, None, "nobody", reduce_op="max", match="only \"sum\"")
+    fails(DTYPE_NOT_SUPPORTED, F.matmul_all_reduce, a.float(), b.float(), None, "nobody", match="float16, bfloat16")
+    fails(ERROR_OCCURRED, F.matmul_all_reduce, a, b[:32], None, "nobody", match="columns")
+    fails(ERROR_OCCURRED, F.matmul_all_reduce, a, b, torch.zeros(5, dtype=torch.float16), "nobody", match="bias")
+
+
+def test_group_setup_validation(built_libs):
+    """The group set-up calls check their arguments first (no CUDA call is reached here)."""
+    import ctypes
+    from diopi_b200 import _lib
+    impl = _lib.load().impl
+    buf = ctypes.create_string_buffer(64)
+    assert impl.diopiB200GroupCreate(b"g", 0, 9, 4, buf) != 0
+    assert b"1 to 8 ranks" in impl.diopiGetLastErrorString()
+    assert impl.diopiB200GroupCreate(b"g", 3, 2, 4, buf) != 0
+    assert impl.diopiB200GroupCreate(b"", 0, 1, 4, buf) != 0
+    assert impl.diopiB200GroupCreate(b"g", 0, 2, 0, buf) != 0
+    assert impl.diopiB200GroupConnect(b"missing", buf) != 0
+    assert b"no group named" in impl.diopiGetLastErrorString()
+    assert impl.diopiB200GroupDestroy(b"missing") != 0
