@@ -47,10 +47,9 @@ using namespace sm100;  // NOLINT
 
 constexpr int TM = 128, TK = 64;              // rows of an output tile, K step of one ring stage
 constexpr int kTileCap = 128;                 // widest tile; a group's capacity is counted in 128 x 128 tiles
-constexpr int kMaxStages = 6;
+constexpr int kMaxStages = 10;
 constexpr int kThreads = 192;
-constexpr int kABytes = TM * TK * 2;          // 16 KB
-constexpr int kRingBytes = 128 * 1024;        // stages of (x1 tile, x2 tile): 4 x 32 KB, 5 x 24 KB or 6 x 20 KB
+constexpr int kRingBytes = 128 * 1024;        // stages of (x1 tile, x2 tile): 4 x 32 KB ... 10 x 12 KB
 constexpr int kRowPadMax = kTileCap + 4;      // floats per row of the transpose buffer (16-byte stores without bank conflicts)
 constexpr int kOffRing = 0;
 constexpr int kOffT = kOffRing + kRingBytes;  // transpose buffer: 4 warps x 32 rows x (TN + 4) floats
@@ -64,16 +63,20 @@ constexpr uint32_t kTmemCols = 256;           // two accumulators of up to 128 f
 
 // Narrow tiles (TN = 64, 32) exist for outputs of few rows: the product is then bound by streaming the weights, and
 // 128-wide tiles would leave most SMs without work (N = 4096: 32 CTAs at TN = 128, 128 CTAs at TN = 32).
-template <int TN>
+// AM = rows of x1 a stage holds: 128, or 64 when the whole product has at most 64 rows. The MMA still reads 128 rows
+// of shared memory; what it finds behind the 64 loaded ones only reaches accumulator rows that are never read. Halving
+// the x1 tile leaves room for more stages, i.e. more weight bytes in flight per CTA.
+template <int TN, int AM = 128>
 struct Tile {
+    static constexpr int kABytes = AM * TK * 2;
     static constexpr int kBBytes = TN * TK * 2;
     static constexpr int kStageBytes = kABytes + kBBytes;
-    static constexpr int kStages = kRingBytes / kStageBytes;        // 4, 5, 6
+    static constexpr int kStages = kRingBytes / kStageBytes < kMaxStages ? kRingBytes / kStageBytes : kMaxStages;   // 4 ... 10
     static constexpr int kRowPad = TN + 4;
     static constexpr int kLanesPerRow = TN / 4;                     // a lane owns 4 columns
     static constexpr int kRowsPerInstr = 32 / kLanesPerRow;         // rows one warp-wide access covers: 1, 2, 4
-    static constexpr size_t kPartialRowBytes = TN * 8, kPartialTileBytes = TM * kPartialRowBytes;
-    static constexpr size_t kResultRowBytes = TN * 4, kResultTileBytes = TM * kResultRowBytes;
+    static constexpr size_t kPartialRowBytes = TN * 8;   // fp32 payload + mark per value
+    static constexpr size_t kResultRowBytes = TN * 4;    // 16-bit payload pairs + mark
 };
 constexpr size_t kPartialCapBytes = static_cast<size_t>(TM) * kTileCap * 8;   // room of one 128 x 128 tile of partials
 constexpr size_t kResultCapBytes = static_cast<size_t>(TM) * kTileCap * 4;
@@ -109,18 +112,19 @@ __device__ __forceinline__ bool poll_again(unsigned long long& t0, volatile int*
 // any width are packed into regions sized for max_tiles tiles of 128 x 128.
 template <int TN>
 __device__ __forceinline__ size_t partial_slot(int buf, int world, int src, int max_tiles, int tile) {
-    return (static_cast<size_t>(buf) * world + src) * max_tiles * kPartialCapBytes + static_cast<size_t>(tile) * Tile<TN>::kPartialTileBytes;
+    return (static_cast<size_t>(buf) * world + src) * max_tiles * kPartialCapBytes + static_cast<size_t>(tile) * TM * Tile<TN>::kPartialRowBytes;
 }
 template <int TN>
 __device__ __forceinline__ size_t result_slot(int buf, int max_tiles, int tile) {
-    return static_cast<size_t>(buf) * max_tiles * kResultCapBytes + static_cast<size_t>(tile) * Tile<TN>::kResultTileBytes;
+    return static_cast<size_t>(buf) * max_tiles * kResultCapBytes + static_cast<size_t>(tile) * TM * Tile<TN>::kResultRowBytes;
 }
 
-template <bool BF16, bool B_KMAJOR, int TN>
+template <bool BF16, bool B_KMAJOR, int TN, int AM>
 __global__ void __launch_bounds__(kThreads, 1) matmul_allreduce_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                                                                         const MatmulAllReduceArgs a) {
-    using TL = Tile<TN>;
+    using TL = Tile<TN, AM>;
     constexpr int kStages = TL::kStages;
+    constexpr int kABytes = TL::kABytes;
     static_assert(B_KMAJOR || TN >= 64, "an MN-major x2 tile is made of 64-column boxes");
     extern __shared__ __align__(1024) unsigned char smem[];
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kOffBar);
@@ -486,8 +490,9 @@ const char* launch_matmul_allreduce(const MatmulAllReduceArgs& a, int sm_count, 
         const int f = std::atoi(v);
         if (f == 128 || f == 64 || (f == 32 && a.x2_kmajor)) tn = f;
     }
+    const int am = (tn < 128 && a.M <= 64) ? 64 : 128;   // rows of x1 a ring stage holds
     CUtensorMap ma, mb;
-    if (!make_map_2d(&ma, a.x1, a.K, a.M, a.x1_ld, TM, bf16)) return "cuTensorMapEncodeTiled failed for x1";
+    if (!make_map_2d(&ma, a.x1, a.K, a.M, a.x1_ld, am, bf16)) return "cuTensorMapEncodeTiled failed for x1";
     const bool okb = a.x2_kmajor ? make_map_2d(&mb, a.x2, a.K, a.N, a.x2_ld, tn, bf16) : make_map_2d(&mb, a.x2, a.N, a.K, a.x2_ld, TK, bf16);
     if (!okb) return "cuTensorMapEncodeTiled failed for x2";
     const int n_tiles = static_cast<int>(row_tiles * ((a.N + tn - 1) / tn));
@@ -499,12 +504,13 @@ const char* launch_matmul_allreduce(const MatmulAllReduceArgs& a, int sm_count, 
     auto pick = [&](auto bf) {
         constexpr bool B = decltype(bf)::value;
         if (a.x2_kmajor) {
-            if (tn == 128) go(matmul_allreduce_kernel<B, true, 128>);
-            else if (tn == 64) go(matmul_allreduce_kernel<B, true, 64>);
-            else go(matmul_allreduce_kernel<B, true, 32>);
+            if (tn == 128) go(matmul_allreduce_kernel<B, true, 128, 128>);
+            else if (tn == 64) { if (am == 64) go(matmul_allreduce_kernel<B, true, 64, 64>); else go(matmul_allreduce_kernel<B, true, 64, 128>); }
+            else { if (am == 64) go(matmul_allreduce_kernel<B, true, 32, 64>); else go(matmul_allreduce_kernel<B, true, 32, 128>); }
         } else {
-            if (tn == 128) go(matmul_allreduce_kernel<B, false, 128>);
-            else go(matmul_allreduce_kernel<B, false, 64>);
+            if (tn == 128) go(matmul_allreduce_kernel<B, false, 128, 128>);
+            else if (am == 64) go(matmul_allreduce_kernel<B, false, 64, 64>);
+            else go(matmul_allreduce_kernel<B, false, 64, 128>);
         }
     };
     if (bf16)
