@@ -33,33 +33,6 @@ __device__ __forceinline__ float load_inv(const void* inv_rms, Dt inv_dt, int64_
     return Cvt<T>::to_f(static_cast<const T*>(inv_rms)[row]);
 }
 
-// Two fp32 operations per instruction (mul/fma/add.rn.f32x2 on 64-bit register pairs). The rows kernel is close to
-// issue-bound (six fp32 operations per element besides unpacking), so halving their count is what moves it.
-struct F2 {
-    uint64_t v;
-};
-__device__ __forceinline__ F2 f2(float a, float b) {
-    F2 r;
-    asm("mov.b64 %0, {%1, %2};" : "=l"(r.v) : "f"(a), "f"(b));
-    return r;
-}
-__device__ __forceinline__ void unf2(F2 p, float& a, float& b) { asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(p.v)); }
-__device__ __forceinline__ F2 mul2(F2 a, F2 b) {
-    F2 r;
-    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r.v) : "l"(a.v), "l"(b.v));
-    return r;
-}
-__device__ __forceinline__ F2 fma2(F2 a, F2 b, F2 c) {
-    F2 r;
-    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r.v) : "l"(a.v), "l"(b.v), "l"(c.v));
-    return r;
-}
-__device__ __forceinline__ F2 add2(F2 a, F2 b) {
-    F2 r;
-    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r.v) : "l"(a.v), "l"(b.v));
-    return r;
-}
-
 template <typename T, int THREADS, int VPT, bool HAS_DB>
 __global__ void __launch_bounds__(THREADS, (THREADS * VPT * Vec16<T>::N <= 4096 && THREADS == 512) ? 2 : 1) rms_bwd_rows_kernel(RmsNormBwdArgs a, int n_vec) {
     constexpr int N = Vec16<T>::N;
@@ -103,18 +76,16 @@ __global__ void __launch_bounds__(THREADS, (THREADS * VPT * Vec16<T>::N <= 4096 
         }
         if (row + gridDim.x < a.n1) fetch(row + gridDim.x);
         const float inv = load_inv<T>(a.inv_rms, a.inv_dt, row);
-        F2 c2 = f2(0.f, 0.f);
+        float c = 0.f;
 #pragma unroll
         for (int v = 0; v < VPT; ++v) {
             float xf[N], gf[N];
             unpack16<T>(xraw[v], xf);
             unpack16<T>(graw[v], gf);
 #pragma unroll
-            for (int e = 0; e < N; e += 2) c2 = fma2(mul2(f2(gf[e], gf[e + 1]), f2(wf[v][e], wf[v][e + 1])), f2(xf[e], xf[e + 1]), c2);
+            for (int e = 0; e < N; ++e) c = fmaf(gf[e] * wf[v][e], xf[e], c);
         }
-        float c, c_hi;
-        unf2(c2, c, c_hi);
-        c = warp_sum_f(c + c_hi);
+        c = warp_sum_f(c);
         if (lane == 0) s_part[buf][warp] = c;
         __syncthreads();
         float tot = 0.f;
@@ -129,13 +100,11 @@ __global__ void __launch_bounds__(THREADS, (THREADS * VPT * Vec16<T>::N <= 4096 
             float xf[N], gf[N], of[N];
             unpack16<T>(xraw[v], xf);
             unpack16<T>(graw[v], gf);
-            const F2 inv2 = f2(inv, inv), ncoef2 = f2(-coef, -coef);
 #pragma unroll
-            for (int e = 0; e < N; e += 2) {
-                const F2 g2 = f2(gf[e], gf[e + 1]), x2 = f2(xf[e], xf[e + 1]);
-                unf2(fma2(inv2, mul2(g2, f2(wf[v][e], wf[v][e + 1])), mul2(x2, ncoef2)), of[e], of[e + 1]);
-                unf2(fma2(mul2(g2, x2), inv2, f2(dw[v][e], dw[v][e + 1])), dw[v][e], dw[v][e + 1]);
-                if constexpr (HAS_DB) unf2(add2(f2(db[v][e], db[v][e + 1]), g2), db[v][e], db[v][e + 1]);
+            for (int e = 0; e < N; ++e) {
+                of[e] = fmaf(inv, gf[e] * wf[v][e], -xf[e] * coef);
+                dw[v][e] = fmaf(gf[e] * xf[e], inv, dw[v][e]);
+                if constexpr (HAS_DB) db[v][e] += gf[e];
             }
             if (idx < n_vec) __stcs(o4 + idx, pack16<T>(of));
         }
