@@ -999,7 +999,30 @@ cudaError_t static_scratch_address(void** out) {
 
 }  // namespace
 
+// Grouped K/V heads (kv_group query heads read one K/V head) on the split path: the call is run as kv_group passes,
+// pass s taking query head s of every group. Each pass is an ordinary problem with as many query heads as K/V heads
+// (q and out are addressed with the group's stride), so the streaming kernel serves it unchanged. The K/V rows are
+// read once per pass; the plain kernel, which reads them once per query head with one CTA per (request, head),
+// measured 62 GB/s on a 64-over-8-head batch where this form reaches the streaming rate on every pass.
+DecodeArgs group_pass(const DecodeArgs& a, int s) {
+    DecodeArgs b = a;
+    const int64_t e = elem_bytes(a.dt);
+    b.H = a.H / a.kv_group;
+    b.kv_group = 1;
+    b.q = static_cast<const char*>(a.q) + static_cast<int64_t>(s) * a.q_s1 * e;
+    b.out = static_cast<char*>(a.out) + static_cast<int64_t>(s) * a.out_s1 * e;
+    b.q_s1 = a.q_s1 * a.kv_group;
+    b.out_s1 = a.out_s1 * a.kv_group;
+    return b;
+}
+bool grouped_on_split_path(const DecodeArgs& a, int sm_count, int max_smem) {
+    if (a.kv_group <= 1 || a.mode != DecodeMode::FUSED || a.H % a.kv_group != 0) return false;
+    SplitPlan p;
+    return make_split_plan(group_pass(a, 0), sm_count, max_smem, p);
+}
+
 int64_t decode_workspace_bytes(const DecodeArgs& a, int sm_count, int max_smem) {
+    if (grouped_on_split_path(a, sm_count, max_smem)) return decode_workspace_bytes(group_pass(a, 0), sm_count, max_smem);
     SplitPlan p;
     if (a.mode == DecodeMode::QK) return 0;
     if (!make_split_plan(a, sm_count, max_smem, p)) return 0;
@@ -1008,6 +1031,11 @@ int64_t decode_workspace_bytes(const DecodeArgs& a, int sm_count, int max_smem) 
 
 void launch_decode(const DecodeArgs& a, void* ws, int sm_count, int max_smem, cudaStream_t st) {
     if (a.B <= 0 || a.H <= 0 || a.D <= 0) return;
+    if (grouped_on_split_path(a, sm_count, max_smem)) {
+        // the passes share the scratch: they run one after the other on the stream
+        for (int s = 0; s < a.kv_group; ++s) launch_decode(group_pass(a, s), ws, sm_count, max_smem, st);
+        return;
+    }
     SplitPlan p;
     if (make_split_plan(a, sm_count, max_smem, p)) {
         float* ws_acc = nullptr;
