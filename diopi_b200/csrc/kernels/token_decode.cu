@@ -66,6 +66,11 @@ struct SplitPlan {
     int ups;           // token groups per ring slot (1, 2 or 4): a tile of TPG groups spans TPG / ups ring slots
     int pdl;           // launch the merge kernel as a programmatic dependent
     int producer_warps;
+    // Grouped K/V heads: `passes` query heads per K/V head. CTA x of the grid works on token range x / passes for
+    // pass x % passes, so the CTAs that stream the same rows run side by side and all but the first find them in L2.
+    int passes;
+    int64_t q_pass, out_pass;          // element offset of a pass inside q and out
+    int64_t ws_pass_acc, ws_pass_ml;   // float offset of a pass inside the two scratch blocks
 };
 
 // ---------------------------------------------------------------------------
@@ -230,7 +235,10 @@ __global__ void __launch_bounds__(kThreads, 1) decode_split_kernel(const DecodeA
     const int tid = threadIdx.x;
     const int warp = tid >> 5;
     const int lane = tid & 31;
-    const int cta = blockIdx.x;
+    const int pass = p.passes > 1 ? static_cast<int>(blockIdx.x) % p.passes : 0;
+    const int cta = p.passes > 1 ? static_cast<int>(blockIdx.x) / p.passes : static_cast<int>(blockIdx.x);
+    ws_acc += pass * p.ws_pass_acc;
+    ws_ml += pass * p.ws_pass_ml;
     const int hg0 = blockIdx.y * p.hg;               // first head of this CTA
     const int heads_here = min(p.hg, a.H - hg0);
     const int C_eff = heads_here * LPH;               // chunks per row actually copied
@@ -436,7 +444,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_split_kernel(const DecodeA
 #pragma unroll
                 for (int e = 0; e < EPC; ++e) acc[e] = 0.f;
                 if (kHasK) {
-                    const T* qp = static_cast<const T*>(a.q) + static_cast<int64_t>(req) * a.q_s0 + static_cast<int64_t>(h) * a.q_s1 + lih * EPC;
+                    const T* qp = static_cast<const T*>(a.q) + pass * p.q_pass + static_cast<int64_t>(req) * a.q_s0 + static_cast<int64_t>(h) * a.q_s1 + lih * EPC;
                     if (MODE == static_cast<int>(DecodeMode::QK)) {
                         // The reference divides the finished dot product by sqrt(D); do the same at the store.
 #pragma unroll
@@ -626,8 +634,11 @@ __global__ void __launch_bounds__(kThreads, 1) decode_split_kernel(const DecodeA
 // Merges the partials of one (request, head) and writes out[i,h,:]. One warp each.
 template <typename T>
 __global__ void __launch_bounds__(128) decode_combine_kernel(const DecodeArgs a, int n_cta, const float* __restrict__ ws_acc,
-                                                              const float* __restrict__ ws_ml) {
+                                                              const float* __restrict__ ws_ml, int64_t out_pass, int64_t ws_pass_acc,
+                                                              int64_t ws_pass_ml) {
     __shared__ int s_part[4][2];
+    ws_acc += blockIdx.z * ws_pass_acc;   // blockIdx.z: the pass (query head inside its group of K/V sharers)
+    ws_ml += blockIdx.z * ws_pass_ml;
     const int i = blockIdx.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     // start = sum of the lengths before request i, total = sum of all lengths
@@ -700,7 +711,7 @@ __global__ void __launch_bounds__(128) decode_combine_kernel(const DecodeArgs a,
         }
     }
     const float inv = Lsum > 0.f ? 1.f / Lsum : 0.f;
-    T* o = static_cast<T*>(a.out) + static_cast<int64_t>(i) * a.out_s0 + static_cast<int64_t>(h) * a.out_s1;
+    T* o = static_cast<T*>(a.out) + blockIdx.z * out_pass + static_cast<int64_t>(i) * a.out_s0 + static_cast<int64_t>(h) * a.out_s1;
 #pragma unroll
     for (int r = 0; r < R; ++r) {
         const int d = lane + 32 * r;
@@ -889,6 +900,8 @@ bool make_split_plan(const DecodeArgs& a, int sm_count, int max_smem, SplitPlan&
     p.off_red = take(red_bytes, 16);
     p.off_flag = take(4, 4);
     p.smem_bytes = off;
+    p.passes = 1;
+    p.q_pass = p.out_pass = p.ws_pass_acc = p.ws_pass_ml = 0;
 
     // One CTA per SM (times ctas_per_sm) over the head groups, but no more CTAs than there can be work for.
     int n_cta = std::max(1, sm_count * ctas_per_sm / p.n_hg);
@@ -901,7 +914,7 @@ bool make_split_plan(const DecodeArgs& a, int sm_count, int max_smem, SplitPlan&
 
 template <typename T, int LPH, int MODE>
 void launch_split_t(const DecodeArgs& a, const SplitPlan& p, float* ws_acc, float* ws_ml, cudaStream_t st) {
-    dim3 grid(p.n_cta, p.n_hg);
+    dim3 grid(p.n_cta * p.passes, p.n_hg);
     constexpr bool fused = MODE == static_cast<int>(DecodeMode::FUSED);
     // fused: 4 token groups per tile (2 with DIOPI_B200_DECODE_TPG=2); one matrix only: 8, so that a tile is 64 KB either way
     if (fused && p.tpg == 2) {
@@ -916,7 +929,7 @@ void launch_split_t(const DecodeArgs& a, const SplitPlan& p, float* ws_acc, floa
     if (MODE != static_cast<int>(DecodeMode::QK)) {
         // Programmatic dependent launch: the merge kernel's launch latency and set-up overlap the split kernel.
         cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = dim3(a.B, (a.H + 3) / 4);
+        cfg.gridDim = dim3(a.B, (a.H + 3) / 4, p.passes);
         cfg.blockDim = dim3(128);
         cfg.dynamicSmemBytes = 0;
         cfg.stream = st;
@@ -927,7 +940,7 @@ void launch_split_t(const DecodeArgs& a, const SplitPlan& p, float* ws_acc, floa
         cfg.numAttrs = 1;
         const float* acc_c = ws_acc;
         const float* ml_c = ws_ml;
-        cudaLaunchKernelEx(&cfg, decode_combine_kernel<T>, a, p.n_cta, acc_c, ml_c);
+        cudaLaunchKernelEx(&cfg, decode_combine_kernel<T>, a, p.n_cta, acc_c, ml_c, p.out_pass, p.ws_pass_acc, p.ws_pass_ml);
     }
 }
 
@@ -1021,8 +1034,28 @@ bool grouped_on_split_path(const DecodeArgs& a, int sm_count, int max_smem) {
     return make_split_plan(group_pass(a, 0), sm_count, max_smem, p);
 }
 
+// The passes of a grouped call in ONE launch: sm_count / kv_group token ranges, kv_group CTAs (one per pass) on each,
+// neighbours in the grid, so that the K/V rows one of them brings in are L2 hits for the others.
+bool side_by_side_plan(const DecodeArgs& a, int sm_count, int max_smem, SplitPlan& p) {
+    if (env_int("DIOPI_B200_DECODE_GROUP_PASSES_SEQ", 0)) return false;
+    if (sm_count / a.kv_group < 1) return false;
+    const DecodeArgs b = group_pass(a, 0);
+    if (!make_split_plan(b, sm_count / a.kv_group, max_smem, p)) return false;
+    p.passes = a.kv_group;
+    p.q_pass = a.q_s1;
+    p.out_pass = a.out_s1;
+    p.ws_pass_acc = split_ws_floats_acc(b, p);
+    p.ws_pass_ml = split_ws_floats_ml(b, p);
+    return true;
+}
+
 int64_t decode_workspace_bytes(const DecodeArgs& a, int sm_count, int max_smem) {
-    if (grouped_on_split_path(a, sm_count, max_smem)) return decode_workspace_bytes(group_pass(a, 0), sm_count, max_smem);
+    if (grouped_on_split_path(a, sm_count, max_smem)) {
+        int64_t need = decode_workspace_bytes(group_pass(a, 0), sm_count, max_smem);
+        SplitPlan p;
+        if (side_by_side_plan(a, sm_count, max_smem, p)) need = std::max<int64_t>(need, (p.ws_pass_acc + p.ws_pass_ml) * p.passes * 4 + 256);
+        return need;
+    }
     SplitPlan p;
     if (a.mode == DecodeMode::QK) return 0;
     if (!make_split_plan(a, sm_count, max_smem, p)) return 0;
@@ -1032,7 +1065,20 @@ int64_t decode_workspace_bytes(const DecodeArgs& a, int sm_count, int max_smem) 
 void launch_decode(const DecodeArgs& a, void* ws, int sm_count, int max_smem, cudaStream_t st) {
     if (a.B <= 0 || a.H <= 0 || a.D <= 0) return;
     if (grouped_on_split_path(a, sm_count, max_smem)) {
-        // the passes share the scratch: they run one after the other on the stream
+        SplitPlan gp;
+        if (side_by_side_plan(a, sm_count, max_smem, gp)) {
+            const DecodeArgs b = group_pass(a, 0);
+            uintptr_t base = (reinterpret_cast<uintptr_t>(ws) + 255) & ~static_cast<uintptr_t>(255);
+            float* ws_acc = reinterpret_cast<float*>(base);
+            float* ws_ml = ws_acc + gp.ws_pass_acc * gp.passes;
+            switch (b.dt) {
+                case Dt::F16: launch_split_mode<__half>(b, gp, ws_acc, ws_ml, st); break;
+                case Dt::BF16: launch_split_mode<__nv_bfloat16>(b, gp, ws_acc, ws_ml, st); break;
+                default: launch_split_mode<float>(b, gp, ws_acc, ws_ml, st); break;
+            }
+            return;
+        }
+        // else the passes one after the other; they share the scratch
         for (int s = 0; s < a.kv_group; ++s) launch_decode(group_pass(a, s), ws, sm_count, max_smem, st);
         return;
     }

@@ -67,10 +67,11 @@ def time_op(fn, iters, warmup, flush):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--op", required=True, choices=["prefill", "rms_norm", "rms_norm_bwd", "rotary", "rope_copy_kv", "penalty", "copy_kv", "qk", "pv", "pair", "decode"])
+    ap.add_argument("--op", required=True, choices=["prefill", "rms_norm", "rms_norm_bwd", "rotary", "rope_copy_kv", "penalty", "copy_kv", "qk", "pv", "pair", "decode", "paged"])
     ap.add_argument("--size", default="full", choices=["full", "small"])
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--kv-heads", type=int, default=8, help="paged: K/V heads under 64 query heads")
     args = ap.parse_args()
     hbm, tf_burst, tf_sust, kind = peaks()
     ctx = Context()
@@ -156,6 +157,34 @@ def main():
         back = time_rotating(fns, rounds=10, warmup=1)
         rec.update(ms=back, ms_single_launch_with_gap=med, bytes=nbytes, gbs=nbytes / back / 1e6, frac_of_peak=nbytes / back / 1e6 / hbm, unit="GB/s",
                    timing=f"{sets} buffer sets cycled back to back (cold L2), average per launch; ms_single_launch_with_gap brackets one launch alone")
+    elif args.op == "paged":
+        # diopiPagedAttention, 64 query heads x 128 over --kv-heads K/V heads, B 64, lengths U[512, 4096], blocks of 16
+        B, Hq, D, bs, Hkv = 64, 64, 128, 16, args.kv_heads
+        gc = torch.Generator().manual_seed(1006)
+        lens = torch.randint(512, 4097, (B,), generator=gc)
+        nblk = (lens + bs - 1) // bs
+        blocks = int(nblk.sum()) + 8
+        g = torch.Generator(device="cuda").manual_seed(1006)
+        k = torch.randn(blocks * bs, Hkv * D, generator=g, device="cuda", dtype=torch.float32).to(torch.float16)
+        v = torch.randn(blocks * bs, Hkv * D, generator=g, device="cuda", dtype=torch.float32).to(torch.float16)
+        q = torch.randn(B, Hq * D, generator=g, device="cuda", dtype=torch.float32).to(torch.float16)
+        perm = torch.randperm(blocks, generator=gc)
+        table = torch.zeros(B, int(nblk.max()), dtype=torch.int32)
+        o = 0
+        for i in range(B):
+            n = int(nblk[i])
+            table[i, :n] = perm[o:o + n].to(torch.int32)
+            o += n
+        table = table.cuda()
+        lens_l = lens.tolist()
+
+        def run():
+            F.paged_attention(q, k, v, None, lens_l, Hq, Hkv, D, table, bs, ctx=ctx)
+            ctx.release()
+        back = time_rotating([run], rounds=max(20, args.iters), warmup=2)
+        nbytes = 2 * int(lens.sum()) * Hkv * D * 2 + 2 * q.numel() * 2
+        rec.update(ms=back, bytes=nbytes, gbs=nbytes / back / 1e6, frac_of_peak=nbytes / back / 1e6 / hbm, unit="GB/s", kv_heads=Hkv, sum_len=int(lens.sum()),
+                   note="bytes = every K/V row once + q + out: the figure a single pass over the rows would be bound by")
     elif args.op == "penalty":
         p = workloads.penalty()
         med, best = time_op(lambda: F.apply_penalty(p["logits"], p["presence"], p["frequency"], p["ids"], p["counts"], p["cum"], p["max_len"], ctx=ctx),
