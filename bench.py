@@ -51,63 +51,7 @@ def measured_peak():
     return FALLBACK_HBM_GBS, "fallback"
 
 
-class ClockSampler:
-    """Polls SM clock and throttle reasons through NVML while the timed region runs (read-only)."""
-
-    def __init__(self, index: int):
-        self.samples, self.reasons, self.max_mhz = [], set(), None
-        self._stop = threading.Event()
-        self._thread = None
-        try:
-            import pynvml
-            pynvml.nvmlInit()
-            self.nv = pynvml
-            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
-            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
-        except Exception:  # noqa: BLE001
-            self.nv = None
-
-    def _poll_once(self):
-        nv = self.nv
-        self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
-        try:
-            mask = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
-        except Exception:  # noqa: BLE001
-            mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
-        names = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap",
-                 0x80: "hw_power_brake_slowdown", 0x2: "applications_clocks_setting"}
-        for bit, name in names.items():
-            if mask & bit:
-                self.reasons.add(name)
-
-    def _run(self):
-        while not self._stop.is_set():
-            try:
-                self._poll_once()
-            except Exception:  # noqa: BLE001
-                return
-            time.sleep(0.002)
-
-    def start(self):
-        if self.nv:
-            self._thread = threading.Thread(target=self._run, daemon=True)
-            self._thread.start()
-
-    def stop(self):
-        if self.nv:
-            try:
-                self._poll_once()
-            except Exception:  # noqa: BLE001
-                pass
-            self._stop.set()
-            if self._thread:
-                self._thread.join(timeout=1)
-
-    def summary(self):
-        if not self.samples:
-            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": [], "samples": 0}
-        return {"sm_mhz": statistics.median(self.samples), "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
-                "samples": len(self.samples)}
+from diopi_b200.clocks import ClockSampler  # noqa: E402
 
 
 def dist_env():

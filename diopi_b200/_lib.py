@@ -53,6 +53,8 @@ GROUP = {
     "diopiB200GroupCreate": [c_char_p, c_int, c_int, c_int64, c_void_p],
     "diopiB200GroupConnect": [c_char_p, c_void_p],
     "diopiB200GroupDestroy": [c_char_p],
+    "diopiB200GroupSetOption": [c_char_p, c_char_p, c_int64],
+    "diopiB200SetOption": [c_char_p, c_int64],
 }
 
 

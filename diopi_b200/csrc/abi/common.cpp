@@ -39,13 +39,35 @@ void fail(diopiError_t code, const char* fmt, ...) {
     throw OpError(code, buf);
 }
 
-bool log_enabled() {
-    static const bool on = [] {
-        const char* v = std::getenv("DIOPI_B200_LOG");
-        return v && v[0] && v[0] != '0';
+Options& options() {
+    static Options o = [] {
+        auto on = [](const char* name) {
+            const char* v = std::getenv(name);
+            return (v && v[0] && v[0] != '0') ? 1 : 0;
+        };
+        Options x;
+        x.log = on("DIOPI_B200_LOG");
+        x.fuse_token_attention = on("DIOPI_B200_FUSE_TOKEN_ATTENTION");
+        x.decode_plain = on("DIOPI_B200_DECODE_PLAIN");
+        x.prefill_simt = on("DIOPI_B200_PREFILL_SIMT");
+        return x;
     }();
-    return on;
+    return o;
 }
+
+bool set_option(const char* name, int64_t value) {
+    if (name == nullptr) return false;
+    Options& o = options();
+    const int v = value != 0 ? 1 : 0;
+    if (std::strcmp(name, "log") == 0) o.log = v;
+    else if (std::strcmp(name, "fuse_token_attention") == 0) o.fuse_token_attention = v;
+    else if (std::strcmp(name, "decode_plain") == 0) o.decode_plain = v;
+    else if (std::strcmp(name, "prefill_simt") == 0) o.prefill_simt = v;
+    else return false;
+    return true;
+}
+
+bool log_enabled() { return options().log != 0; }
 
 void logf(const char* fmt, ...) {
     if (!log_enabled()) return;
@@ -188,24 +210,44 @@ const DeviceInfo& device_info() {
     return g_dev[dev];
 }
 
-int* async_status_device_ptr() {
-    int* h = g_status_host.load(std::memory_order_acquire);
-    if (h) return h;
-    std::lock_guard<std::mutex> lock(g_status_mu);
-    h = g_status_host.load(std::memory_order_relaxed);
-    if (!h) {
-        // Portable + mapped: under unified addressing every device may store to the same pointer.
-        B200_CUDA(cudaHostAlloc(reinterpret_cast<void**>(&h), 64, cudaHostAllocPortable | cudaHostAllocMapped));
-        std::memset(h, 0, 64);
-        g_status_host.store(h, std::memory_order_release);
-    }
-    return h;
+// One 64-byte line per device, so that a status is attributed to the device whose kernel raised it.
+constexpr int kStatusStrideInts = 16;
+constexpr int kStatusDevices = 64;
+
+int current_device_index() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kStatusDevices) return 0;
+    return dev;
 }
 
-int* async_status_device_ptr_if_ready() { return g_status_host.load(std::memory_order_acquire); }
+int* async_status_device_ptr() {
+    int* h = g_status_host.load(std::memory_order_acquire);
+    if (!h) {
+        std::lock_guard<std::mutex> lock(g_status_mu);
+        h = g_status_host.load(std::memory_order_relaxed);
+        if (!h) {
+            // Portable + mapped: under unified addressing every device may store to the same pointer.
+            const size_t bytes = static_cast<size_t>(kStatusDevices) * kStatusStrideInts * sizeof(int);
+            B200_CUDA(cudaHostAlloc(reinterpret_cast<void**>(&h), bytes, cudaHostAllocPortable | cudaHostAllocMapped));
+            std::memset(h, 0, bytes);
+            g_status_host.store(h, std::memory_order_release);
+        }
+    }
+    return h + current_device_index() * kStatusStrideInts;
+}
+
+int* async_status_device_ptr_if_ready() {
+    int* h = g_status_host.load(std::memory_order_acquire);
+    return h ? h + current_device_index() * kStatusStrideInts : nullptr;
+}
+
+void clear_async_status_if(int code) {
+    int* h = async_status_device_ptr_if_ready();
+    if (h && *reinterpret_cast<volatile int*>(h) == code) *reinterpret_cast<volatile int*>(h) = 0;
+}
 
 void check_async_status() {
-    int* h = g_status_host.load(std::memory_order_acquire);
+    int* h = async_status_device_ptr_if_ready();
     if (!h) return;
     int v = *reinterpret_cast<volatile int*>(h);
     if (v == 0) return;
@@ -214,10 +256,10 @@ void check_async_status() {
     switch (v) {
         case 1: what = "a pool slot index read from b_loc or dest_loc was outside the pool; that row was skipped"; break;
         case 2: what = "a token id passed to diopiApplyPenalty was outside the vocabulary; that entry was skipped"; break;
-        case 3: what = "a kernel gave up waiting for its own memory pipeline"; break;
+        case 3: what = "a kernel gave up a bounded wait (its own memory pipeline, or the rows of a tensor-parallel peer)"; break;
         default: break;
     }
-    fail(diopiErrorOccurred, "an earlier kernel of this library reported status %d: %s", v, what);
+    fail(diopiErrorOccurred, "an earlier kernel of this library reported status %d: %s (this call itself was launched)", v, what);
 }
 
 }  // namespace b200

@@ -29,6 +29,19 @@ struct OpError : public std::exception {
 };
 
 [[noreturn]] void fail(diopiError_t code, const char* fmt, ...) __attribute__((format(printf, 2, 3)));
+
+// Process-wide switches. Each starts from its environment variable, read once when the first op runs, and can be
+// changed afterwards with diopiB200SetOption; no op reads the environment on its call path.
+//   log                   DIOPI_B200_LOG                   one line per call on stderr
+//   fuse_token_attention  DIOPI_B200_FUSE_TOKEN_ATTENTION  run the unfused pair of decode calls as the fused kernel
+//   decode_plain          DIOPI_B200_DECODE_PLAIN          decode ops on the one-CTA-per-(request, head) kernel, no split-KV
+//   prefill_simt          DIOPI_B200_PREFILL_SIMT          prefill on the SIMT kernel, not on the tensor-core one
+struct Options {
+    int log = 0, fuse_token_attention = 0, decode_plain = 0, prefill_simt = 0;
+};
+Options& options();
+// Returns false when `name` is not one of the switches above.
+bool set_option(const char* name, int64_t value);
 void set_last_error(const std::string& msg);
 bool log_enabled();
 void logf(const char* fmt, ...) __attribute__((format(printf, 1, 2)));
@@ -84,13 +97,18 @@ struct DeviceInfo {
 // Properties of the current device, looked up once per device.
 const DeviceInfo& device_info();
 
-// A word in mapped pinned host memory that kernels write when they meet something they
-// must refuse (an index outside the pool, a wait that ran out). Read at the start of every op
-// at no cost; a non-zero value is reported once as an error of the op that sees it.
+// One word per device in mapped pinned host memory that kernels write when they meet something they
+// must refuse (an index outside the pool, a wait that ran out). The word of the current device is read
+// at the end of every op at no cost; a non-zero value is reported once, as the return code of the op that
+// sees it. That op has already made its own launch by then: a status left by an earlier kernel never
+// keeps a later call from running (in a tensor-parallel layer a skipped call on one rank would leave
+// its peers waiting).
 int* async_status_device_ptr();
-// The same word if an earlier call already set it up, else null (kernels accept null). Never allocates.
+// The same word if an earlier call already set the block up, else null (kernels accept null). Never allocates.
 int* async_status_device_ptr_if_ready();
 void check_async_status();
+// Drops the current device's status when it is `code`: for an op that reports the same event through its own error.
+void clear_async_status_if(int code);
 
 // Runs `body`, mapping exceptions to return codes; nothing escapes the C boundary.
 template <typename F>
@@ -99,8 +117,8 @@ diopiError_t guard(const char* op, F&& body) noexcept {
     if (diopiRecordStart) diopiRecordStart(op, &rec);
     diopiError_t rc = diopiSuccess;
     try {
-        check_async_status();
         body();
+        check_async_status();   // after the launch: see the comment at async_status_device_ptr
     } catch (const OpError& e) {
         set_last_error(std::string(op) + ": " + e.msg);
         rc = e.code;

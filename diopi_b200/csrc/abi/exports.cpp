@@ -51,6 +51,7 @@ void run_decode(diopiContextHandle_t ctx, k::DecodeMode mode, const TensorView* 
                 const TensorView* vmat, const TensorView& b_loc, const TensorView& b_start, const TensorView& b_len, int max_input_len, bool launch = true) {
     k::DecodeArgs a{};
     a.mode = mode;
+    a.force_plain = options().decode_plain;
     const TensorView& pool = kmat ? *kmat : *vmat;
     a.dt = float_dt(pool, kmat ? "k" : "v", false);
     B200_REQUIRE(pool.ndim == 3, "the K/V pool must be [slots, head_num, head_dim], got %d dims", pool.ndim);
@@ -130,7 +131,8 @@ void run_decode(diopiContextHandle_t ctx, k::DecodeMode mode, const TensorView* 
 }
 
 // ---- the two-call decode run as one kernel (opt-in) ------------------------------------------------
-// With DIOPI_B200_FUSE_TOKEN_ATTENTION=1 in the environment, diopiTokenAttentionInference checks its arguments and
+// With the option fuse_token_attention on (DIOPI_B200_FUSE_TOKEN_ATTENTION=1 at start-up, or diopiB200SetOption),
+// diopiTokenAttentionInference checks its arguments and
 // records them instead of launching. If the next call of this library on the same context is
 // diopiTokenSoftmaxReduceVInference on the same logits tensor and the same index tensors, the pair runs as the
 // fused kernel and the logits tensor is never written. Any other call of this library on that context first
@@ -144,10 +146,7 @@ struct PendingQK {
 std::mutex g_pending_mu;
 std::unordered_map<diopiContextHandle_t, PendingQK> g_pending;
 
-bool fuse_pair_enabled() {
-    const char* v = std::getenv("DIOPI_B200_FUSE_TOKEN_ATTENTION");
-    return v != nullptr && v[0] != '\0' && v[0] != '0';
-}
+bool fuse_pair_enabled() { return options().fuse_token_attention != 0; }
 
 bool take_pending(diopiContextHandle_t ctx, PendingQK& out) {
     std::lock_guard<std::mutex> lock(g_pending_mu);
@@ -190,6 +189,14 @@ B200_EXPORT const char* diopiGetImplVersion() {
     return buf;
 }
 B200_EXPORT const char* diopiGetLastErrorString() { return last_error_cstr(); }
+
+// Extension: changes one of the process-wide switches of common.hpp (the environment gives only their start values).
+B200_EXPORT diopiError_t diopiB200SetOption(const char* name, int64_t value) {
+    return guard("diopiB200SetOption", [&] {
+        if (!set_option(name, value))
+            fail(diopiErrorOccurred, "unknown option '%s'; known: log, fuse_token_attention, decode_plain, prefill_simt", name ? name : "(null)");
+    });
+}
 
 // ---------------------------------------------------------------------------------------------
 B200_EXPORT diopiError_t diopiDestIndexCopyKV(diopiContextHandle_t ctx, diopiTensorHandle_t out, diopiConstTensorHandle_t kh, diopiConstTensorHandle_t dest_loc) {
@@ -284,6 +291,7 @@ B200_EXPORT diopiError_t diopiContextAttentionInference(diopiContextHandle_t ctx
         TensorView o = view_of(context_attention_out, "context_attention_out"), qv = view_of(q, "q"), kv = view_of(kh, "k"), vv = view_of(v, "v");
         TensorView bs = view_of(b_start_loc, "b_start_loc"), bn = view_of(b_seq_len, "b_seq_len");
         k::PrefillArgs a{};
+        a.force_simt = options().prefill_simt != 0;
         a.dt = float_dt(qv, "q", false);
         same_dtype(kv, "k", qv, "q");
         same_dtype(vv, "v", qv, "q");
@@ -670,6 +678,7 @@ B200_EXPORT diopiError_t diopiTokenDecodeAttentionInferenceNoAlloc(diopiContextH
         TensorView bl = view_of(b_loc, "b_loc"), bs = view_of(b_start_loc, "b_start_loc"), bn = view_of(b_seq_len, "b_seq_len");
         k::DecodeArgs a{};
         a.mode = k::DecodeMode::FUSED;
+        a.force_plain = options().decode_plain;
         a.dt = float_dt(kv, "k", false);
         B200_REQUIRE(kv.ndim == 3 && vv.ndim == 3 && qv.ndim == 3 && o.ndim == 3, "q, k, v and out must have 3 dims");
         a.H = static_cast<int>(kv.shape[1]);
@@ -824,6 +833,7 @@ B200_EXPORT diopiError_t diopiPromptFlashAttention(diopiContextHandle_t ctx, dio
         flush_pending(ctx);
         TensorView o = view_of(out, "out"), qv = view_of(query, "query"), kv = view_of(key, "key"), vv = view_of(value, "value");
         k::PrefillArgs a{};
+        a.force_simt = options().prefill_simt != 0;
         a.dt = float_dt(qv, "query", false);
         same_dtype(kv, "key", qv, "query");
         same_dtype(vv, "value", qv, "query");
@@ -887,6 +897,7 @@ B200_EXPORT diopiError_t diopiPagedAttention(diopiContextHandle_t ctx, diopiTens
         TensorView o = view_of(out, "out"), qv = view_of(q, "q"), kv = view_of(kh, "k"), vv = view_of(v, "v"), bt = view_of(block_table, "block_table");
         k::DecodeArgs a{};
         a.mode = k::DecodeMode::FUSED;
+        a.force_plain = options().decode_plain;
         a.dt = float_dt(qv, "q", false);
         same_dtype(kv, "k", qv, "q");
         same_dtype(vv, "v", qv, "q");

@@ -7,9 +7,14 @@
 //   diopiB200GroupCreate(name, rank, world, max_tiles, handle_out)   on every rank: allocates and exports the local area
 //   (exchange the 64-byte handles by any means: torch.distributed, MPI, a file)
 //   diopiB200GroupConnect(name, all_handles)                         on every rank: maps the peers' areas
-// and then calls diopiMatmulAllReduce(..., group = name, ...) like the reference's backend does. These three set-up
-// entry points have no counterpart in the reference.
-#include <cstdlib>
+// and then calls diopiMatmulAllReduce(..., group = name, ...) like the reference's backend does. The set-up entry
+// points have no counterpart in the reference.
+//
+// Recovery rule. Every wait of the kernel on a peer is bounded (diopiB200GroupSetWaitLimit, 2 s by default). When one
+// runs out on any rank (a peer that never made the call, or died), that rank reports status 3 and marks the group
+// unusable on every rank; from then on diopiMatmulAllReduce on that group returns an error without launching on the
+// rank that gave up, and on the others as soon as one of their kernels has seen the mark. The consumer then calls
+// diopiB200GroupDestroy on every rank and sets the group up again.
 #include <cstring>
 #include <map>
 #include <mutex>
@@ -29,7 +34,11 @@ struct Group {
     void* mapped[k::kMaxGroupRanks] = {nullptr}; // peers' areas as opened here (null for the own rank)
     unsigned char* stage[k::kMaxGroupRanks] = {nullptr};
     unsigned char* result[k::kMaxGroupRanks] = {nullptr};
-    uint32_t* ctrl = nullptr;
+    uint32_t* ctrl[k::kMaxGroupRanks] = {nullptr};
+    int* poison = nullptr;                       // mapped pinned host word: a kernel of this rank found or made the group unusable
+    unsigned long long wait_limit_ns = 2000000000ull;
+    int form = 0;         // 0: chosen per call; 1: one-shot; 2: two-shot
+    int tile_width = 0;   // 0: chosen per call; 128, 64, 32
 };
 
 std::mutex g_mu;
@@ -40,13 +49,14 @@ void set_pointers(Group& g, int r, void* base) {
     char* b = static_cast<char*>(base);
     g.stage[r] = reinterpret_cast<unsigned char*>(b + l.stage_off);
     g.result[r] = reinterpret_cast<unsigned char*>(b + l.result_off);
-    if (r == g.rank) g.ctrl = reinterpret_cast<uint32_t*>(b + l.ctrl_off);
+    g.ctrl[r] = reinterpret_cast<uint32_t*>(b + l.ctrl_off);
 }
 
 void release(Group& g) {
     for (int r = 0; r < g.world; ++r)
         if (g.mapped[r]) cudaIpcCloseMemHandle(g.mapped[r]);
     if (g.local) cudaFree(g.local);
+    if (g.poison) cudaFreeHost(g.poison);
     g = Group{};
 }
 
@@ -88,6 +98,10 @@ B200_EXPORT diopiError_t diopiB200GroupCreate(const char* group, int rank, int w
             e = cudaIpcGetMemHandle(&h, g.local);
             if (e == cudaSuccess) std::memcpy(local_handle, &h, sizeof(h));
         }
+        if (e == cudaSuccess) {
+            e = cudaHostAlloc(reinterpret_cast<void**>(&g.poison), 64, cudaHostAllocMapped);
+            if (e == cudaSuccess) std::memset(g.poison, 0, 64);
+        }
         if (e != cudaSuccess) {
             cudaFree(g.local);
             fail(diopiErrorOccurred, "cuda error while creating group '%s': %s", group, cudaGetErrorString(e));
@@ -118,6 +132,28 @@ B200_EXPORT diopiError_t diopiB200GroupConnect(const char* group, const void* ha
             set_pointers(g, r, p);
         }
         g.connected = true;
+    });
+}
+
+B200_EXPORT diopiError_t diopiB200GroupSetOption(const char* group, const char* option, int64_t value) {
+    return guard("diopiB200GroupSetOption", [&] {
+        B200_REQUIRE(group != nullptr && option != nullptr, "group and option must not be null");
+        std::lock_guard<std::mutex> lock(g_mu);
+        auto it = g_groups.find(group);
+        B200_REQUIRE(it != g_groups.end(), "no group named '%s'", group);
+        Group& g = it->second;
+        if (std::strcmp(option, "wait_limit_ms") == 0) {
+            B200_REQUIRE(value >= 1 && value <= 600000, "wait_limit_ms must be between 1 and 600000 (10 min), got %ld", (long)value);
+            g.wait_limit_ns = static_cast<unsigned long long>(value) * 1000000ull;
+        } else if (std::strcmp(option, "form") == 0) {
+            B200_REQUIRE(value >= 0 && value <= 2, "form must be 0 (chosen per call), 1 (one-shot) or 2 (two-shot), got %ld", (long)value);
+            g.form = static_cast<int>(value);
+        } else if (std::strcmp(option, "tile_width") == 0) {
+            B200_REQUIRE(value == 0 || value == 128 || value == 64 || value == 32, "tile_width must be 0 (chosen per call), 128, 64 or 32, got %ld", (long)value);
+            g.tile_width = static_cast<int>(value);
+        } else {
+            fail(diopiErrorOccurred, "unknown group option '%s'; known: wait_limit_ms, form, tile_width", option);
+        }
     });
 }
 
@@ -189,24 +225,33 @@ B200_EXPORT diopiError_t diopiMatmulAllReduce(diopiContextHandle_t ctx, diopiTen
             Group& g = it->second;
             B200_REQUIRE(g.connected, "group '%s' is not connected yet", group);
             B200_REQUIRE(g.device == di.device, "group '%s' lives on device %d, the current device is %d", group, g.device, di.device);
+            if (*reinterpret_cast<volatile int*>(g.poison) != 0) {
+                clear_async_status_if(3);   // the same event; this error names it better
+                fail(diopiErrorOccurred,
+                     "group '%s' is unusable: a kernel of this group gave up waiting for a peer's rows (or a peer did), so the ranks' call "
+                     "numbers may no longer agree; destroy the group on every rank and create it again",
+                     group);
+            }
             if (M == 0 || N == 0) return;
             const int tiles = k::matmul_allreduce_tiles(M, N);
             B200_REQUIRE(tiles <= g.max_tiles, "the output has %d tiles of 128 x 128; group '%s' was created for at most %d", tiles, group, g.max_tiles);
             a.rank = g.rank;
             a.world = g.world;
             a.max_tiles = g.max_tiles;
-            a.ctrl = g.ctrl;
+            a.ctrl = g.ctrl[g.rank];
+            a.poison_host = g.poison;
+            a.wait_limit_ns = g.wait_limit_ns;
             // One-shot (every rank receives every partial) for groups of two or three and for outputs of fewer tiles than
             // ranks; else two-shot (partials to a tile's owner, finished tiles handed round): the second hop costs a
-            // microsecond or two, the one-shot bytes grow with the group. DIOPI_B200_MAR_MODE=1|2 forces a form.
+            // microsecond or two, the one-shot bytes grow with the group. The group option "form" forces one.
             a.two_shot = g.world >= 4 && tiles >= g.world;
-            if (const char* v = std::getenv("DIOPI_B200_MAR_MODE")) {
-                if (v[0] == '1') a.two_shot = false;
-                if (v[0] == '2') a.two_shot = g.world > 1;
-            }
+            if (g.form == 1) a.two_shot = false;
+            if (g.form == 2) a.two_shot = g.world > 1;
+            a.force_tile_width = g.tile_width;
             for (int r = 0; r < g.world; ++r) {
                 a.peer_stage[r] = g.stage[r];
                 a.peer_result[r] = g.result[r];
+                a.peer_ctrl[r] = g.ctrl[r];
             }
         }
         a.x1 = av.data;

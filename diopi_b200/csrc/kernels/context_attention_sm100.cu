@@ -474,11 +474,7 @@ bool make_map(CUtensorMap* map, const void* base, int64_t rows, int H, int64_t s
 
 void launch_prefill_tc(const PrefillArgs& a, int /*sm_count*/, int max_smem, cudaStream_t st, bool* taken) {
     *taken = false;
-    static const bool disabled = [] {
-        const char* v = std::getenv("DIOPI_B200_PREFILL_SIMT");
-        return v && v[0] && v[0] != '0';
-    }();
-    if (disabled) return;
+    if (a.force_simt) return;
     if (a.dt != Dt::F16 && a.dt != Dt::BF16) return;
     if (a.D != HD || a.H > 65535 || kSmemBytes > max_smem) return;
     if (a.total_rows >= (1ll << 31) - BM) return;
@@ -507,8 +503,7 @@ void launch_prefill_tc(const PrefillArgs& a, int /*sm_count*/, int max_smem, cud
     p.uniform_len = a.uniform_len;
     p.kv_group = a.kv_group;
     dim3 grid(p.n_tiles_max, a.H, 1);
-    int poly = kDefaultPolyEvery;
-    if (const char* v = std::getenv("DIOPI_B200_PREFILL_POLY_EVERY")) poly = std::atoi(v);
+    const int poly = kDefaultPolyEvery;
     auto go = [&](auto kern) {
         cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
         kern<<<grid, kThreads, kSmemBytes, st>>>(mq, mk, mv, p);

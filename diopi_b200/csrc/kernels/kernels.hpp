@@ -50,7 +50,8 @@ struct DecodeArgs {
     int* status;
     int block_size;      // 0: b_loc names one slot per token, right-aligned in its first max_input_len columns;
                          // > 0: b_loc is a block table, token j of request i sits in row b_loc[i, j / block_size] * block_size + j % block_size
-    int kv_group;        // query heads per K/V head (plain path only; 0 or 1 = one to one)
+    int kv_group;        // query heads per K/V head (0 or 1 = one to one)
+    int force_plain;     // non-zero: the one-CTA-per-(request, head) kernel whatever the shape (no split-KV, no scratch)
 };
 
 // Size in bytes of the scratch the split-KV path needs for these arguments, 0 if the
@@ -172,6 +173,7 @@ struct PrefillArgs {
     int max_input_len;
     int64_t uniform_len = 0;     // > 0: padded batch, request i owns rows [i * uniform_len, (i + 1) * uniform_len)
     int kv_group = 1;            // query heads per K/V head (grouped-query attention); k/v have H / kv_group heads
+    bool force_simt = false;     // the SIMT kernel whatever the shape
 };
 void launch_prefill(const PrefillArgs& a, int sm_count, int max_smem, cudaStream_t st);
 
@@ -187,10 +189,14 @@ struct MatmulAllReduceArgs {
     bool x2_kmajor;
     int M, N, K;
     int rank, world, max_tiles;
-    uint32_t* ctrl;           // this rank's two control words: calls finished so far, CTAs of the running call that left
+    uint32_t* ctrl;           // this rank's control words: [0] calls finished so far, [1] CTAs of the running call that left, [2] poisoned
+    uint32_t* peer_ctrl[kMaxGroupRanks];         // the control words of every rank (own included), as mapped into this process
+    int* poison_host;         // mapped host word of this group: set when a kernel of this rank found or made the group unusable
+    unsigned long long wait_limit_ns;            // how long a wait for a peer's rows (or for this kernel's own pipeline) may last
     unsigned char* peer_stage[kMaxGroupRanks];   // partial-tile area of every rank (own included), as mapped into this process
     unsigned char* peer_result[kMaxGroupRanks];  // finished-tile area of every rank (two-shot form)
     bool two_shot;            // partials to the tile's owner only, finished tiles handed round
+    int force_tile_width;     // 0: the launch picks; 128, 64 or (K-major x2 only) 32: this width
     int* status;
 };
 int matmul_allreduce_tiles(int64_t M, int64_t N);

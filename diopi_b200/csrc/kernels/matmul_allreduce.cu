@@ -27,8 +27,11 @@
 // Waiting on another rank's kernel: the marks are the call's sequence number (kept in device memory, no reset between
 // calls, nothing per call from the host: a captured launch can be replayed) and the staging
 // area is double-buffered; a rank cannot run two calls ahead of a peer, because it needs that peer's rows of the
-// call in between. A wait that runs out (a peer that never calls) raises the status word (code 3) and the kernel
-// returns with TMEM freed.
+// call in between. A wait that runs out (a peer that never calls; the limit is a property of the group, 2 s unless
+// set otherwise) raises the status word (code 3), the kernel returns with TMEM freed, and the group is poisoned on
+// every rank (word 2 of each rank's control words): the ranks' call numbers may no longer agree, so no later call
+// may trust a mark. Kernels launched on a poisoned group leave at once; the host refuses them until the group is
+// destroyed and created again.
 #include <cuda.h>
 
 #include <cstdlib>
@@ -97,10 +100,10 @@ __device__ __forceinline__ bool ld_pair(const unsigned char* p, uint32_t epoch, 
     return static_cast<uint32_t>(x >> 32) == epoch && static_cast<uint32_t>(y >> 32) == epoch;
 }
 // Between two polls: starts the clock at the first miss, gives up after the time limit or when another role did.
-__device__ __forceinline__ bool poll_again(unsigned long long& t0, volatile int* give_up) {
+__device__ __forceinline__ bool poll_again(unsigned long long& t0, volatile int* give_up, unsigned long long limit_ns) {
     const unsigned long long now = global_ns();
     if (t0 == 0) t0 = now;
-    if (*give_up || now - t0 > kWaitLimitNs) {
+    if (*give_up || now - t0 > limit_ns) {
         *give_up = 1;
         return false;
     }
@@ -140,6 +143,19 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_allreduce_kernel(const __g
     // can be replayed. Every CTA reads it here, before any CTA of this launch can have left.
     const uint32_t epoch = *reinterpret_cast<volatile const uint32_t*>(a.ctrl) + 1u;
     const int buf = static_cast<int>(epoch & 1u);   // which half of the staging area this call uses
+    // A group in which any rank ever gave up a wait is poisoned for good: the ranks' call numbers may no longer agree,
+    // and a stale partial row of the abandoned call would pass for a fresh one. Every CTA reads the word here, before
+    // anything is allocated or sent, and leaves; the host refuses further calls until the group is made anew.
+    if (__syncthreads_or(*reinterpret_cast<volatile const uint32_t*>(a.ctrl + 2) != 0u ? 1 : 0)) {   // one answer per CTA
+        if (tid == 0 && blockIdx.x == 0) {
+            report_status(a.status, 3);
+            if (a.poison_host) *reinterpret_cast<volatile int*>(a.poison_host) = 1;
+        }
+        return;
+    }
+    // The waits inside the CTA (ring, accumulators) last as long as the epilogue warps wait for a peer: give them
+    // twice the peer limit, so that the peer wait is the one that runs out first and names the cause.
+    const unsigned long long pipe_limit = 2ull * a.wait_limit_ns;
 
     if (tid == 0) {
         for (int s = 0; s < kStages; ++s) {
@@ -171,7 +187,7 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_allreduce_kernel(const __g
                 for (int kb = 0; kb < kblocks; ++kb, ++it) {
                     const int s = it % kStages;
                     const uint32_t ph = static_cast<uint32_t>((it / kStages) & 1);
-                    if (!mbar_wait(bar(EMPTY + s), ph ^ 1u, give_up)) goto producer_done;
+                    if (!mbar_wait(bar(EMPTY + s), ph ^ 1u, give_up, pipe_limit)) goto producer_done;
                     mbar_expect_tx(bar(FULL + s), TL::kStageBytes);
                     const uint32_t a_dst = smem_u32(smem + kOffRing + s * TL::kStageBytes), b_dst = a_dst + kABytes;
                     tma_load_2d(a_dst, &map_a, kb * TK, m0, bar(FULL + s));
@@ -193,12 +209,12 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_allreduce_kernel(const __g
             int it = 0, nt = 0;
             for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++nt) {
                 const int acc = nt & 1;
-                if (!mbar_wait(bar(ACC_EMPTY + acc), static_cast<uint32_t>(((nt >> 1) & 1) ^ 1), give_up)) break;
+                if (!mbar_wait(bar(ACC_EMPTY + acc), static_cast<uint32_t>(((nt >> 1) & 1) ^ 1), give_up, pipe_limit)) break;
                 tc_fence_after();
                 bool ok = true;
                 for (int kb = 0; kb < kblocks; ++kb, ++it) {
                     const int s = it % kStages;
-                    if (!mbar_wait(bar(FULL + s), static_cast<uint32_t>((it / kStages) & 1), give_up)) {
+                    if (!mbar_wait(bar(FULL + s), static_cast<uint32_t>((it / kStages) & 1), give_up, pipe_limit)) {
                         ok = false;
                         break;
                     }
@@ -230,7 +246,7 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_allreduce_kernel(const __g
         for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x, ++nt) {
             const int acc = nt & 1;
             const int m0 = (tile / tiles_n) * TM, n0 = (tile % tiles_n) * TN;
-            if (!warp_wait(bar(ACC_FULL + acc), static_cast<uint32_t>((nt >> 1) & 1), give_up)) {
+            if (!warp_wait(bar(ACC_FULL + acc), static_cast<uint32_t>((nt >> 1) & 1), give_up, pipe_limit)) {
                 ok = false;
                 break;
             }
@@ -318,7 +334,7 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_allreduce_kernel(const __g
                             }
                         }
                         if (__all_sync(0xffffffffu, here ? 1 : 0)) break;
-                        if (!__all_sync(0xffffffffu, poll_again(t0, give_up) ? 1 : 0)) {   // the warp stops as one
+                        if (!__all_sync(0xffffffffu, poll_again(t0, give_up, a.wait_limit_ns) ? 1 : 0)) {   // the warp stops as one
                             ok = false;
                             break;
                         }
@@ -382,7 +398,7 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_allreduce_kernel(const __g
                             }
                         }
                         if (__all_sync(0xffffffffu, here ? 1 : 0)) break;
-                        if (!__all_sync(0xffffffffu, poll_again(t0, give_up) ? 1 : 0)) {
+                        if (!__all_sync(0xffffffffu, poll_again(t0, give_up, a.wait_limit_ns) ? 1 : 0)) {
                             ok = false;
                             break;
                         }
@@ -410,7 +426,13 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_allreduce_kernel(const __g
         }
     }
     if (*give_up) {
-        if (tid == 0) report_status(a.status, 3);
+        if (tid == 0) {
+            report_status(a.status, 3);
+            // Make the give-up sticky on every rank: a plain store into each peer's control words (and the own ones).
+            for (int p = 0; p < a.world; ++p) *reinterpret_cast<volatile uint32_t*>(a.peer_ctrl[p] + 2) = 1u;
+            if (a.poison_host) *reinterpret_cast<volatile int*>(a.poison_host) = 1;
+            __threadfence_system();
+        }
         const unsigned long long t_begin = global_ns();
         while (global_ns() - t_begin < 2000000ull) __nanosleep(1000);  // let copies/MMAs still in flight finish
         __syncthreads();
@@ -456,8 +478,8 @@ bool make_map_2d(CUtensorMap* map, const void* base, int64_t inner, int64_t oute
 int matmul_allreduce_tiles(int64_t M, int64_t N) { return static_cast<int>(((M + TM - 1) / TM) * ((N + kTileCap - 1) / kTileCap)); }
 
 // One rank's area: partial tiles [2 halves][world sources][max_tiles] (fp32 with arrival marks, 128 KB each), finished
-// tiles [2][max_tiles] (16-bit with arrival marks, 64 KB each, two-shot form) and two control words (calls finished,
-// CTAs of the running call that have left).
+// tiles [2][max_tiles] (16-bit with arrival marks, 64 KB each, two-shot form) and four control words (calls finished,
+// CTAs of the running call that have left, poisoned, spare).
 MarLayout matmul_allreduce_layout(int world, int max_tiles) {
     MarLayout l;
     size_t off = 0;
@@ -466,7 +488,7 @@ MarLayout matmul_allreduce_layout(int world, int max_tiles) {
     l.result_off = off;
     off += static_cast<size_t>(2) * max_tiles * kResultCapBytes;
     l.ctrl_off = off;
-    off += 2 * sizeof(uint32_t);
+    off += 4 * sizeof(uint32_t);
     l.bytes = (off + 255) / 256 * 256;
     return l;
 }
@@ -482,12 +504,12 @@ const char* launch_matmul_allreduce(const MatmulAllReduceArgs& a, int sm_count, 
         return "x1, x2 and out need 16-byte aligned bases and row pitches that are multiples of 16 bytes";
     const bool bf16 = a.dt == Dt::BF16;
     // Tile width: 128 when there are enough 128-wide tiles to occupy the SMs; else narrower, so that more CTAs stream
-    // the weights (32 needs x2 K-major: an MN-major tile is made of 64-column boxes). DIOPI_B200_MAR_TN forces a width.
+    // the weights (32 needs x2 K-major: an MN-major tile is made of 64-column boxes). force_tile_width overrides the choice.
     const int64_t row_tiles = (a.M + TM - 1) / TM;
     int tn = 128;
     if (row_tiles * ((a.N + 127) / 128) * 2 <= sm_count) tn = (a.x2_kmajor && row_tiles * ((a.N + 63) / 64) * 2 <= sm_count * 2) ? 32 : 64;
-    if (const char* v = std::getenv("DIOPI_B200_MAR_TN")) {
-        const int f = std::atoi(v);
+    {
+        const int f = a.force_tile_width;
         if (f == 128 || f == 64 || (f == 32 && a.x2_kmajor)) tn = f;
     }
     const int am = (tn < 128 && a.M <= 64) ? 64 : 128;   // rows of x1 a ring stage holds

@@ -43,14 +43,14 @@ __device__ __forceinline__ unsigned long long global_ns() {
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
     return t;
 }
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* give_up) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* give_up, unsigned long long limit_ns = kWaitLimitNs) {
     if (mbar_try_wait(bar, parity)) return true;
     const unsigned long long t0 = global_ns();
     uint32_t spins = 0;
     while (!mbar_try_wait(bar, parity)) {
         if ((++spins & 0x3fu) == 0) {
             if (*give_up) return false;
-            if (global_ns() - t0 > kWaitLimitNs) {
+            if (global_ns() - t0 > limit_ns) {
                 *give_up = 1;
                 return false;
             }
@@ -60,8 +60,8 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
 }
 
 // Warp-uniform form for code that goes on to warp-collective tcgen05.ld/st: all lanes agree on the outcome.
-__device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, volatile int* give_up) {
-    return __all_sync(0xffffffffu, mbar_wait(bar, parity, give_up) ? 1 : 0) != 0;
+__device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, volatile int* give_up, unsigned long long limit_ns = kWaitLimitNs) {
+    return __all_sync(0xffffffffu, mbar_wait(bar, parity, give_up, limit_ns) ? 1 : 0) != 0;
 }
 
 __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, uint32_t bar) {

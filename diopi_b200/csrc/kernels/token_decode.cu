@@ -28,7 +28,6 @@
 // Plain path: one CTA per (request, head), any strides, any D up to 512. Used when the
 // rows are not 16-byte aligned/dense or D*e/16 is not 8, 16 or 32.
 #include <cfloat>
-#include <cstdlib>
 #include <type_traits>
 #include <mutex>
 
@@ -825,17 +824,11 @@ __global__ void __launch_bounds__(128) decode_plain_kernel(const DecodeArgs a) {
 // ---------------------------------------------------------------------------
 int elem_bytes(Dt dt) { return dt == Dt::F32 ? 4 : 2; }
 
-int env_int(const char* name, int dflt) {
-    const char* v = std::getenv(name);
-    if (!v || !*v) return dflt;
-    return std::atoi(v);
-}
-
 // Fills `p` when the arguments qualify for the split path.
 bool make_split_plan(const DecodeArgs& a, int sm_count, int max_smem, SplitPlan& p) {
     if (a.dt == Dt::F64) return false;
     if (a.kv_group > 1) return false;  // a K/V row shared by several query heads: plain path
-    if (env_int("DIOPI_B200_DECODE_PLAIN", 0)) return false;
+    if (a.force_plain) return false;
     const int e = elem_bytes(a.dt);
     const bool has_k = a.mode != DecodeMode::PV, has_v = a.mode != DecodeMode::QK;
     if ((a.D * e) % 16 != 0) return false;
@@ -855,21 +848,16 @@ bool make_split_plan(const DecodeArgs& a, int sm_count, int max_smem, SplitPlan&
     p.n_hg = (a.H + p.hg - 1) / p.hg;
     p.C = p.hg * lph;
     p.G = std::min(kConsumerThreads / p.C, kMaxG);
-    if (a.mode == DecodeMode::FUSED) {
-        p.tpg = env_int("DIOPI_B200_DECODE_TPG", 4);
-        if (p.tpg != 2 && p.tpg != 4) p.tpg = 4;
-    } else {
-        p.tpg = 8;
-    }
+    p.tpg = a.mode == DecodeMode::FUSED ? 4 : 8;   // a tile is 64 KB either way (two matrices or one)
     p.TT = p.G * p.tpg;
     p.nmat = (has_k && has_v) ? 2 : 1;
-    p.pdl = env_int("DIOPI_B200_DECODE_PDL", 1);
-    p.producer_warps = std::max(1, std::min(kMaxProducerWarps, env_int("DIOPI_B200_DECODE_PRODUCERS", 4)));
-    p.ups = env_int("DIOPI_B200_DECODE_UPS", p.tpg);
-    if (p.ups != 1 && p.ups != 2 && p.ups != 4 && p.ups != 8) p.ups = p.tpg;
-    if (p.ups > p.tpg) p.ups = p.tpg;
+    // Settled by sweeps: dependent launch of the merge kernel, four producer warps, one ring slot per tile, one CTA per SM,
+    // as many ring slots as fit.
+    p.pdl = 1;
+    p.producer_warps = kMaxProducerWarps;
+    p.ups = p.tpg;
     p.stage_bytes = p.ups * p.G * p.C * 16 * p.nmat;
-    const int ctas_per_sm = std::max(1, std::min(2, env_int("DIOPI_B200_DECODE_CTAS_PER_SM", 1)));
+    const int ctas_per_sm = 1;
 
     const int red_bytes = (p.G > 1 && has_v) ? kConsumerThreads * (16 / e + 2) * 4 : 0;
     int off = 0;
@@ -891,7 +879,7 @@ bool make_split_plan(const DecodeArgs& a, int sm_count, int max_smem, SplitPlan&
         fixed = off + 128;
     }
     int nst = (budget - fixed) / p.stage_bytes;
-    nst = std::min(nst, std::min(kMaxStages, std::max(2, env_int("DIOPI_B200_DECODE_STAGES", kMaxStages))));
+    nst = std::min(nst, kMaxStages);
     if (nst < p.tpg / p.ups + 1) return false;  // a tile holds tpg/ups ring slots at once; one more must be in flight
     p.nstages = nst;
     off = nst * p.stage_bytes;
@@ -916,12 +904,8 @@ template <typename T, int LPH, int MODE>
 void launch_split_t(const DecodeArgs& a, const SplitPlan& p, float* ws_acc, float* ws_ml, cudaStream_t st) {
     dim3 grid(p.n_cta * p.passes, p.n_hg);
     constexpr bool fused = MODE == static_cast<int>(DecodeMode::FUSED);
-    // fused: 4 token groups per tile (2 with DIOPI_B200_DECODE_TPG=2); one matrix only: 8, so that a tile is 64 KB either way
-    if (fused && p.tpg == 2) {
-        auto kern = decode_split_kernel<T, LPH, MODE, (fused ? 2 : 8)>;
-        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, p.smem_bytes);
-        kern<<<grid, kConsumerThreads + 32 * p.producer_warps, p.smem_bytes, st>>>(a, p, ws_acc, ws_ml);
-    } else {
+    // fused: 4 token groups per tile; one matrix only: 8, so that a tile is 64 KB either way
+    {
         auto kern = decode_split_kernel<T, LPH, MODE, (fused ? 4 : 8)>;
         cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, p.smem_bytes);
         kern<<<grid, kConsumerThreads + 32 * p.producer_warps, p.smem_bytes, st>>>(a, p, ws_acc, ws_ml);
@@ -1037,7 +1021,6 @@ bool grouped_on_split_path(const DecodeArgs& a, int sm_count, int max_smem) {
 // The passes of a grouped call in ONE launch: sm_count / kv_group token ranges, kv_group CTAs (one per pass) on each,
 // neighbours in the grid, so that the K/V rows one of them brings in are L2 hits for the others.
 bool side_by_side_plan(const DecodeArgs& a, int sm_count, int max_smem, SplitPlan& p) {
-    if (env_int("DIOPI_B200_DECODE_GROUP_PASSES_SEQ", 0)) return false;
     if (sm_count / a.kv_group < 1) return false;
     const DecodeArgs b = group_pass(a, 0);
     if (!make_split_plan(b, sm_count / a.kv_group, max_smem, p)) return false;

@@ -44,6 +44,11 @@ def last_error() -> str:
     return _impl().diopiGetLastErrorString().decode(errors="replace")
 
 
+def set_option(name: str, value: int) -> None:
+    """A process-wide switch of the library: log, fuse_token_attention, decode_plain, prefill_simt."""
+    check_returncode("diopiB200SetOption", _impl().diopiB200SetOption(name.encode(), int(value)))
+
+
 def destindex_copy_kv(k, dest_loc, out, *, ctx=None, as_device=None):
     """out[dest_loc] = k; returns out."""
     tk, td, to = _t(k, as_device), _t(dest_loc, as_device), _t(out, as_device)

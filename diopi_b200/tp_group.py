@@ -31,9 +31,10 @@ def exchange(local: bytes, pg=None) -> bytes:
     return b"".join(bytes(h) for h in gathered)
 
 
-def create(name: str, pg=None, max_tiles: int = 256, rank: int | None = None, world: int | None = None) -> None:
+def create(name: str, pg=None, max_tiles: int = 256, rank: int | None = None, world: int | None = None, wait_limit_ms: int | None = None) -> None:
     """Creates and connects the group `name` over the ranks of process group `pg` (default: the world group).
-    Without torch.distributed (rank and world left None, or world == 1) a group of one rank is made."""
+    Without torch.distributed (rank and world left None, or world == 1) a group of one rank is made.
+    `wait_limit_ms` bounds every wait of a kernel of the group on a peer (2 s when left None)."""
     impl = _lib.load().impl
     if world is None:
         import torch.distributed as dist
@@ -43,11 +44,20 @@ def create(name: str, pg=None, max_tiles: int = 256, rank: int | None = None, wo
             rank, world = 0, 1
     buf = ctypes.create_string_buffer(HANDLE_BYTES)
     check_returncode("diopiB200GroupCreate", impl.diopiB200GroupCreate(name.encode(), int(rank), int(world), int(max_tiles), buf))
+    if wait_limit_ms is not None:
+        set_option(name, "wait_limit_ms", wait_limit_ms)
     if world > 1:
         handles = exchange(buf.raw, pg)
         check_returncode("diopiB200GroupConnect", impl.diopiB200GroupConnect(name.encode(), ctypes.c_char_p(handles)))
         import torch.distributed as dist
         dist.barrier(group=pg)   # nobody launches before every rank has mapped every area
+
+
+def set_option(name: str, option: str, value: int) -> None:
+    """wait_limit_ms, form (0 auto, 1 one-shot, 2 two-shot) or tile_width (0 auto, 128, 64, 32) of group `name`;
+    form and tile_width must be set alike on every rank."""
+    impl = _lib.load().impl
+    check_returncode("diopiB200GroupSetOption", impl.diopiB200GroupSetOption(name.encode(), option.encode(), int(value)))
 
 
 def destroy(name: str) -> None:

@@ -2,12 +2,12 @@
 group of one):
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \\
-        -m diopi_b200.tpbench [--rows 64 --k-total 4096 --cols 4096] [--check] [--iters 50]
+        -m diopi_b200.tpbench [--rows 64 --k-total 4096 --cols 4096] [--iters 50]
 
 Every rank holds x1 [M, K_total / N] and x2 [K_total / N, n] of a row-parallel linear layer. Rank 0 prints one JSON line:
 the time per call of the fused kernel (CUDA events, max over ranks) beside the same product done as torch.matmul
-followed by an NCCL all-reduce, and with --check the comparison of every rank's result with the sum the CPU oracle
-forms from all ranks' inputs (inputs are seeded per rank, so every rank can rebuild all of them).
+followed by an NCCL all-reduce, with the SM clocks sampled meanwhile. Inputs are seeded per rank, so every rank can
+rebuild all of them (the parity check against the CPU oracle lives with the tests: tests/mar_ranks.py).
 """
 from __future__ import annotations
 
@@ -15,12 +15,9 @@ import argparse
 import json
 import os
 import sys
-from pathlib import Path
 
 import torch
 import torch.distributed as dist
-
-ROOT = Path(__file__).resolve().parent.parent
 
 
 def inputs(rank, M, K, N, dtype, device):
@@ -61,7 +58,7 @@ def main():
     ap.add_argument("--dtype", default="bf16", choices=["bf16", "f16"])
     ap.add_argument("--iters", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--check", action="store_true")
+    ap.add_argument("--form", type=int, default=0, choices=[0, 1, 2], help="0 chosen per call, 1 one-shot, 2 two-shot")
     ap.add_argument("--x2", default="rowmajor", choices=["rowmajor", "kmajor"], help="kmajor: x2 is the transposed view of an [N, K] weight")
     args = ap.parse_args()
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -77,12 +74,13 @@ def main():
     M, N, K = args.rows, args.cols, args.k_total // world
     tiles = ((M + 127) // 128) * ((N + 127) // 128)
     tp_group.create("tp", max_tiles=tiles)
+    tp_group.set_option("tp", "form", args.form)
     ctx = Context()
     x1, x2, bias = inputs(rank, M, K, N, dtype, "cuda")
     if args.x2 == "kmajor":
         x2 = x2.t().contiguous().t()   # same values, stored as [N, K]
     out = torch.empty(M, N, dtype=dtype, device="cuda")
-    rec = {"op": "matmul_all_reduce", "mode": os.environ.get("DIOPI_B200_MAR_MODE", "auto"), "world": world, "M": M, "N": N, "K_per_rank": K, "dtype": args.dtype, "x2": args.x2}
+    rec = {"op": "matmul_all_reduce", "form": {0: "auto", 1: "one-shot", 2: "two-shot"}[args.form], "world": world, "M": M, "N": N, "K_per_rank": K, "dtype": args.dtype, "x2": args.x2}
 
     # handles made once, the entry point called directly: the host side of a call is then a few microseconds, as it is
     # for a C++ consumer, and the figure is the device's
@@ -97,26 +95,12 @@ def main():
         if rc != 0:
             check_returncode("diopiMatmulAllReduce", rc)
 
-    if args.check:
-        sys.path.insert(0, str(ROOT))
-        from oracle import golden
-        fused()
-        torch.cuda.synchronize()
-        cpu = [inputs(r, M, K, N, dtype, "cpu") for r in range(world)]
-        want = golden.matmul_all_reduce([c[0] for c in cpu], [c[1] for c in cpu], [c[2] for c in cpu])
-        err = float((out.cpu().float() - want.float()).abs().max())
-        ok = torch.allclose(out.cpu().float(), want.float(), rtol=1e-2, atol=1e-2)
-        same = True
-        if world > 1:
-            gathered = [torch.empty_like(out) for _ in range(world)]
-            dist.all_gather(gathered, out)
-            same = all(torch.equal(g, gathered[0]) for g in gathered)
-            flag = torch.tensor([int(ok and same)], device="cuda")
-            dist.all_reduce(flag, op=dist.ReduceOp.MIN)
-            ok = bool(flag.item())
-        rec.update(parity="ok" if (ok and same) else "MISMATCH", max_abs_err=err, ranks_identical=bool(same))
-
+    from .clocks import ClockSampler
+    sampler = ClockSampler(torch.cuda.current_device())
+    sampler.start()
     rec["fused_ms"], rec["fused_host_ms"] = timed(fused, args.iters, args.warmup)
+    sampler.stop()
+    rec["clocks"] = sampler.summary()
 
     def unfused():
         torch.matmul(x1, x2, out=out)
@@ -133,7 +117,7 @@ def main():
     tp_group.destroy("tp")
     if world > 1:
         dist.destroy_process_group()
-    return 0 if rec.get("parity", "ok") == "ok" else 1
+    return 0
 
 
 if __name__ == "__main__":

@@ -253,6 +253,20 @@ diopiError_t diopiMatmulAllReduce(diopiContextHandle_t ctx, diopiTensorHandle_t 
 diopiError_t diopiB200GroupCreate(const char* group, int rank, int world, int64_t max_tiles, void* local_handle);
 diopiError_t diopiB200GroupConnect(const char* group, const void* handles);
 diopiError_t diopiB200GroupDestroy(const char* group);
+/* Options of one group; no counterpart in the reference.
+ *   "wait_limit_ms"  how long a kernel of the group waits for a peer's rows before it gives up (1 .. 600000; 2000 when
+ *                    never set). A wait that runs out makes the call that sees it next fail with status 3 and marks the
+ *                    group unusable on every rank: later calls on it are refused until every rank has destroyed the
+ *                    group and created it again (the ranks' call numbers may no longer agree).
+ *   "form"           0 the exchange is chosen per call, 1 one-shot (every rank receives every partial), 2 two-shot
+ *                    (partials to a tile's owner, finished tiles handed round). Must be the same on every rank.
+ *   "tile_width"     0 chosen per call, or 128 / 64 / 32 output columns per tile. Must be the same on every rank. */
+diopiError_t diopiB200GroupSetOption(const char* group, const char* option, int64_t value);
+
+/* Process-wide switches; no counterpart in the reference. Each starts from an environment variable read once
+ * (DIOPI_B200_LOG, DIOPI_B200_FUSE_TOKEN_ATTENTION, DIOPI_B200_DECODE_PLAIN, DIOPI_B200_PREFILL_SIMT) and is changed
+ * here by name: "log", "fuse_token_attention", "decode_plain", "prefill_simt"; value 0 switches off, non-zero on. */
+diopiError_t diopiB200SetOption(const char* name, int64_t value);
 
 /* Extension with no counterpart in the reference: the same fused decode step for callers that
  * cannot provide scratch memory (an engine whose HBM all went to the KV pool and whose context has

@@ -44,10 +44,11 @@ def test_one_rank_matches_oracle(F, dtype, shape):
 
 @pytest.mark.parametrize("tn", ["128", "64", "32"])
 @pytest.mark.parametrize("kmajor", [False, True])
-def test_tile_widths(F, monkeypatch, tn, kmajor):
-    """Every tile width the launch can pick (DIOPI_B200_MAR_TN forces one; 32 exists only for a K-major x2, where the
-    request is ignored otherwise), on shapes with ragged edges in all three extents."""
-    monkeypatch.setenv("DIOPI_B200_MAR_TN", tn)
+def test_tile_widths(F, tn, kmajor):
+    """Every tile width the launch can pick (the group option tile_width forces one; 32 exists only for a K-major x2,
+    where the request is ignored otherwise), on shapes with ragged edges in all three extents."""
+    from diopi_b200 import tp_group
+    tp_group.set_option("solo", "tile_width", int(tn))
     for (M, K, N) in ((64, 512, 1024), (37, 200, 328), (130, 64, 96)):
         x1, b = rand((M, K), torch.bfloat16, 20 + M), rand((N,), torch.bfloat16, 21)
         w = rand((N, K), torch.bfloat16, 22 + N, K ** -0.5)
@@ -55,6 +56,7 @@ def test_tile_widths(F, monkeypatch, tn, kmajor):
         want = golden.matmul_all_reduce([x1], [x2], [b])
         got = F.matmul_all_reduce(x1.cuda(), (w.cuda().t() if kmajor else x2.cuda()), b.cuda(), "solo")
         torch.testing.assert_close(got.cpu().float(), want.float(), rtol=1e-2, atol=1e-2)
+    tp_group.set_option("solo", "tile_width", 0)
 
 
 def test_transposed_weight_and_stacked_rows(F):
@@ -96,19 +98,35 @@ def test_refusals(F):
     assert F.matmul_all_reduce(a[:0], b, None, "solo").shape == (0, 64)
 
 
-@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-@pytest.mark.parametrize("mode", ["1", "2"])
-def test_two_ranks_match_oracle(mode):
-    """One process per GPU under torchrun: every rank's result equals the oracle's sum over both ranks, and the two
-    ranks hold identical bits; in the one-shot form (1) and in the two-shot form (2)."""
-    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1", "--master-port", "29617",
-           "-m", "diopi_b200.tpbench", "--check", "--iters", "3", "--rows", "200", "--cols", "1032"]
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0", DIOPI_B200_MAR_MODE=mode)
-    res = subprocess.run(cmd, cwd=ROOT, env=env, capture_output=True, text=True, timeout=600)
+def run_ranks(world, what, extra=(), port=29617):
+    """Runs tests/mar_ranks.py as one process per GPU; NVLS is switched off in NCCL, the kernels use plain peer stores."""
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1", "--master-port", str(port),
+           str(ROOT / "tests" / "mar_ranks.py"), what, *extra]
+    res = subprocess.run(cmd, cwd=ROOT, env=dict(os.environ, NCCL_NVLS_ENABLE="0"), capture_output=True, text=True, timeout=600)
     assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-2000:]
-    line = [l for l in res.stdout.splitlines() if l.startswith("{")][-1]
-    rec = json.loads(line)
-    assert rec["parity"] == "ok" and rec["world"] == 2
+    return json.loads([l for l in res.stdout.splitlines() if l.startswith("{")][-1])
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+@pytest.mark.parametrize("mode", ["1", "2"])
+def test_ranks_match_oracle(world, mode):
+    """One process per GPU under torchrun: every rank's result equals the oracle's sum over all ranks, and all ranks
+    hold identical bits; in the one-shot form (1) and in the two-shot form (2)."""
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    rec = run_ranks(world, "check", extra=["--form", mode])
+    assert rec["parity"] == "ok" and rec["world"] == world and rec["ranks_identical"]
+
+
+def test_a_missing_rank_runs_the_wait_out_and_the_group_recovers():
+    """The bounded wait on a peer, made to run out from the host: rank 1 leaves one call out, the other rank's kernel
+    gives up after the group's 50 ms limit and returns (the GPU still answers), later calls are refused with status 3 /
+    'unusable', and after Destroy + Create on both ranks the group gives the right result again."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    rec = run_ranks(2, "timeout", extra=["--limit-ms", "50"], port=29618)
+    assert rec["result"] == "ok" and rec["gpu_alive"] and rec["refused_afterwards"] and rec["recovered_after_recreate"]
+    assert rec["gave_up_after_ms"] < 2500
 
 
 def test_replay_from_a_cuda_graph(F):

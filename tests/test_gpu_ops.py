@@ -318,6 +318,46 @@ def test_decode_cfg2_full_size(F, cfg2):
     assert torch.equal(moved, fused)
 
 
+def test_decode_cfg5_shard_full_size(F):
+    """One GPU's share of the 64-head decode config (8 heads, 128 requests, lengths up to 8192): 2 KB rows, i.e. the
+    kernel form with several tokens side by side and four copy-issuing warps, at the size the benchmark runs it.
+    Same size-independent properties as the 32-head config."""
+    from diopi_b200 import workloads
+    w = workloads.decode("cfg5", device="cuda", head_range=workloads.shard_heads(64, 8, 0))
+    assert tuple(w.q.shape) == (128, 8, 128)
+    F.destindex_copy_kv(w.k_new, w.dest_loc, w.k_pool)
+    F.destindex_copy_kv(w.v_new, w.dest_loc, w.v_pool)
+    assert torch.equal(w.k_pool[w.dest_loc.long()], w.k_new) and torch.equal(w.v_pool[w.dest_loc.long()], w.v_new)
+    args = (w.b_loc, w.b_start_loc, w.b_seq_len, w.max_input_len)
+    fused = torch.empty_like(w.q)
+    F.token_decode_attention(w.q, w.k_pool, w.v_pool, fused, *args)
+    # (1) stand-alone pair through fp16 logits
+    att = torch.zeros(w.q.shape[1], w.sum_len, dtype=w.q.dtype, device="cuda")
+    F.token_attention(w.q, w.k_pool, att, *args)
+    two = torch.empty_like(w.q)
+    F.token_softmax_reducev(att, w.v_pool, two, *args, 0)
+    close(two, fused)
+    # (2) five requests against the oracle with fp32 accumulation
+    reqs = [0, 41, 127, int(w.b_seq_len.argmax()), int(w.b_seq_len.argmin())]
+    close(fused[reqs], compact_oracle(w, reqs, w.k_pool, w.v_pool), torch.float16)
+    # (3) linear in V
+    w.v_pool.mul_(2)
+    twice = torch.empty_like(w.q)
+    F.token_decode_attention(w.q, w.k_pool, w.v_pool, twice, *args)
+    w.v_pool.mul_(0.5)
+    assert float((twice.float() - 2 * fused.float()).abs().max()) <= 2.0 ** -23
+    # (4) re-paging the pool changes nothing
+    slots = w.k_pool.shape[0]
+    perm = torch.randperm(slots, device="cuda")
+    inv = torch.empty_like(perm)
+    inv[perm] = torch.arange(slots, device="cuda")
+    k2, v2 = w.k_pool[perm], w.v_pool[perm]
+    b2 = inv[w.b_loc.long()].to(torch.int32)
+    moved = torch.empty_like(w.q)
+    F.token_decode_attention(w.q, k2, v2, moved, b2, w.b_start_loc, w.b_seq_len, w.max_input_len)
+    assert torch.equal(moved, fused)
+
+
 # ------------------------------------------------------------------ the pair of decode calls run as one kernel (opt-in)
 def test_token_attention_pair_runs_fused_when_asked(F, monkeypatch):
     """With DIOPI_B200_FUSE_TOKEN_ATTENTION=1 the logits call is recorded and the softmax-reduce call that follows on
@@ -334,7 +374,7 @@ def test_token_attention_pair_runs_fused_when_asked(F, monkeypatch):
     plain_out = torch.empty_like(d["q"])
     F.token_softmax_reducev(plain_att, d["v"], plain_out, *idx, 0)
 
-    monkeypatch.setenv("DIOPI_B200_FUSE_TOKEN_ATTENTION", "1")
+    F.set_option("fuse_token_attention", 1)
     att = torch.full((8, total), 7.0, dtype=torch.float16, device="cuda")
     out = torch.empty_like(d["q"])
     F.token_attention(d["q"], d["k"], att, *idx)
@@ -363,7 +403,7 @@ def test_token_attention_pair_runs_fused_when_asked(F, monkeypatch):
     from diopi_b200.runtime import DiopiError
     with pytest.raises(DiopiError):
         F.token_attention(d["q"][:, :4], d["k"], att, *idx)
-    monkeypatch.delenv("DIOPI_B200_FUSE_TOKEN_ATTENTION")
+    F.set_option("fuse_token_attention", 0)
     F.token_attention(d["q"], d["k"], att2.zero_(), *idx)
     torch.cuda.synchronize()
     assert torch.equal(att2, plain_att)
@@ -715,6 +755,42 @@ def test_context_attention_ragged(F, dtype, H, D, lens):
     out2 = torch.zeros_like(out)
     F.context_attention(q.cuda(), k.cuda(), v.cuda(), out2, st.long().cuda(), lens_t.long().cuda(), 1)
     assert torch.equal(out2, out)
+
+
+def test_context_attention_cfg4_full_size(F):
+    """The tensor-core prefill config at the size the benchmark runs it (8 requests of 1024..8192 rows, 32 heads,
+    D 128, fp16). Whole (request, head) pairs are compared with the row-blocked oracle evaluated with fp32
+    accumulation: the longest request (64 query tiles, several thousand keys per row: lazily raised maximum,
+    polynomial exponentials, multi-wave tile order), the shortest, and two neighbours in the packed batch (last rows
+    of one request next to the first rows of the other). Then two size-independent properties."""
+    from diopi_b200 import workloads
+    p = workloads.prefill(device="cuda")
+    q, k, v, st, ln, mx = p["q"], p["k"], p["v"], p["b_start_loc"], p["b_seq_len"], p["max_input_len"]
+    lens = [int(x) for x in p["lens"]]
+    assert max(lens) > 8000 and q.shape[1:] == (32, 128)
+    out = torch.zeros_like(q)
+    F.context_attention(q, k, v, out, st, ln, mx)
+    longest, shortest = lens.index(max(lens)), lens.index(min(lens))
+    starts = [int(x) for x in st.cpu()]
+    for req, head in [(longest, 0), (longest, 31), (shortest, 5), (0, 17), (1, 17)]:
+        s0, L = starts[req], lens[req]
+        sl = slice(s0, s0 + L)
+        one = lambda t: t[sl, head:head + 1].cpu()
+        want = golden.context_attention(one(q), one(k), one(v), torch.zeros(L, 1, 128), torch.zeros(1, dtype=torch.int32),
+                                        torch.tensor([L], dtype=torch.int32), L, upcast=True, row_block=1024)
+        close(out[sl, head:head + 1], want, torch.float16)
+    # (1) run to run identical
+    again = torch.zeros_like(q)
+    F.context_attention(q, k, v, again, st, ln, mx)
+    assert torch.equal(again, out)
+    # (2) packing the requests in the reverse order moves their rows and nothing else
+    order = list(range(len(lens)))[::-1]
+    rows = torch.cat([torch.arange(starts[i], starts[i] + lens[i]) for i in order]).cuda()
+    ln2 = torch.tensor([lens[i] for i in order], dtype=torch.int32)
+    st2 = torch.cat([torch.zeros(1, dtype=torch.int32), ln2.cumsum(0)[:-1].to(torch.int32)])
+    out2 = torch.zeros_like(q)
+    F.context_attention(q[rows], k[rows], v[rows], out2, st2.cuda(), ln2.cuda(), mx)
+    assert torch.equal(out2, out[rows])
 
 
 # ------------------------------------------------------------------ padded-batch prefill (BSH) with grouped-query heads

@@ -10,6 +10,8 @@ failure has then already run every other test."""
 import pytest
 import torch
 
+from oracle import golden
+
 pytestmark = pytest.mark.gpu
 
 
@@ -54,6 +56,10 @@ def test_no_alloc_entry_matches_the_ordinary_one(built_libs):
             tol = dict(rtol=1e-3, atol=1e-3) if c["q"].dtype == torch.float32 else dict(rtol=1e-2, atol=1e-2)
             torch.testing.assert_close(got.float(), want.float(), **tol)
             assert torch.equal(got, want)  # same kernels, same partition: identical bits
+        # and against the CPU oracle evaluated with fp32 accumulation, not only against the sibling entry point
+        ref = golden.token_decode_attention(c["q"].cpu(), c["k"].cpu(), c["v"].cpu(), torch.zeros(c["q"].shape), c["b_loc"].cpu(),
+                                            c["start"].cpu(), c["lens"].cpu(), c["mx"], upcast=True)
+        torch.testing.assert_close(got.cpu().float(), ref.float(), **tol)
         assert ctx.stats()["require_calls"] == before, "the no-alloc entry point asked the context for memory"
 
     # a problem whose partials exceed the built-in array is refused with both numbers in the message
