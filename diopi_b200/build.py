@@ -37,6 +37,7 @@ IMPL_SOURCES = [
     "abi/tp_group.cpp",
     "kernels/dest_index_copy.cu",
     "kernels/token_decode.cu",
+    "kernels/token_decode_gqa.cu",
     "kernels/rms_norm.cu",
     "kernels/rms_norm_backward.cu",
     "kernels/rotary.cu",

@@ -24,6 +24,8 @@ DECODE_CONFIGS = {
     "cfg2": dict(B=64, H=32, D=128, dtype=torch.float16, lo=512, hi=4096, pool="B*hi", std=0.5, seed=1002),
     # a quarter of cfg2 (same rows, 16 requests): small enough for a multi-pass profiler capture, still >> L2
     "cfg2s": dict(B=16, H=32, D=128, dtype=torch.float16, lo=512, hi=4096, pool="B*hi", std=0.5, seed=1012),
+    # small enough for its K/V rows (67 MB) to stay in the 126 MB L2 between steps: the L2-warm variant of the step
+    "cfg2w": dict(B=8, H=32, D=128, dtype=torch.float16, lo=512, hi=512, pool="sum+64", std=0.5, seed=1022),
     "cfg5": dict(B=128, H=64, D=128, dtype=torch.float16, lo=1024, hi=8192, pool="sum+128", std=0.5, seed=1005),
 }
 
