@@ -170,20 +170,27 @@ __global__ void __launch_bounds__(128) decode_combine_kernel(const DecodeArgs a,
     int c_first = 0, c_last = -1;
     auto first_token = [&](int c) { return static_cast<int>(static_cast<int64_t>(all) * c / n_cta); };
     if (L > 0) {
-        auto cta_of = [&](int t) {  // largest c with first_token(c) <= t
-            int lo = 0, hi = n_cta - 1;
-            while (lo < hi) {
-                const int mid = (lo + hi + 1) >> 1;
-                if (first_token(mid) <= t)
-                    lo = mid;
-                else
-                    hi = mid - 1;
-            }
-            return lo;
+        // largest c with first_token(c) <= t: all * c / n_cta < t + 1, i.e. c <= ((t + 1) * n_cta - 1) / all. One division
+        // each (a binary search over first_token cost eight 64-bit divisions per bound, microseconds of serial integer work).
+        auto cta_of = [&](int t) {
+            const int64_t c = ((static_cast<int64_t>(t) + 1) * n_cta - 1) / all;
+            return static_cast<int>(c < n_cta - 1 ? c : n_cta - 1);
         };
         c_first = cta_of(before);
         c_last = cta_of(before + L - 1);
     }
+
+    // Bit c - c_first of `live` = CTA c's range is not empty (an empty range wrote nothing); a request spans few CTAs.
+    uint64_t live = 0;
+    {
+        int lo = first_token(c_first);
+        for (int c = c_first; c <= c_last; ++c) {
+            const int hi = first_token(c + 1);
+            if (hi != lo && c - c_first < 64) live |= 1ull << (c - c_first);
+            lo = hi;
+        }
+    }
+    auto is_live = [&](int c) { return c - c_first < 64 ? ((live >> (c - c_first)) & 1ull) != 0 : first_token(c) != first_token(c + 1); };
 
     // Everything above read only the caller's inputs. The partials are written by the split kernel, which may
     // still be running when this kernel was launched early: wait for it to finish (no-op for a plain launch).
@@ -196,12 +203,12 @@ __global__ void __launch_bounds__(128) decode_combine_kernel(const DecodeArgs a,
     // Two passes with independent loads (one memory latency each): the maximum over the parts, then the weighted sum.
     float M = -INFINITY, Lsum = 0.f;
     for (int c = c_first; c <= c_last; ++c) {
-        if (first_token(c) == first_token(c + 1)) continue;  // an empty range wrote nothing
+        if (!is_live(c)) continue;
         M = fmaxf(M, ws_ml[((static_cast<int64_t>(c) + i) * a.H + h) * 2]);
     }
     const float Mr = (M == -INFINITY) ? 0.f : M;
     for (int c = c_first; c <= c_last; ++c) {
-        if (first_token(c) == first_token(c + 1)) continue;
+        if (!is_live(c)) continue;
         const int64_t slot_id = static_cast<int64_t>(c) + i;
         const float2 ml = *reinterpret_cast<const float2*>(ws_ml + (slot_id * a.H + h) * 2);
         const float w = exp2f(ml.x - Mr);

@@ -9,7 +9,10 @@
 //     S [16 heads x 16 tokens] = Q_g [16 x D] K^T      (rows beyond kv_group are zero padding)
 //     O [16 heads x D]        += P [16 x 16] V
 // with the online softmax on the accumulator fragment in between, exactly the layout trick of blocked attention: the
-// accumulator fragment of S is the A fragment of the second product.
+// accumulator fragment of S is the A fragment of the second product. Tried and dropped: blocks of 8 tokens (m16n8k8 for the
+// second product, six 33 KB stages instead of three 66 KB ones): 107 us where this form takes 97 us on 64 query heads
+// over 8 K/V heads, the per-stage hand-over costs more than the shorter chain wins; a 128-register cap, so that the
+// merge kernel's CTAs become resident beside this kernel's: 101 us.
 //
 // Work split: the flattened (request, token) pairs are cut into equal ranges, one per CTA (as in token_decode.cu).
 // Per CTA four producer warps look up slots and issue one bulk copy per row part (the K/V heads of this CTA:
@@ -138,53 +141,77 @@ __global__ void __launch_bounds__(kGqaThreads, 1) decode_gqa_kernel(const Decode
 
     if (warp >= kGqaConsumerWarps) {
         // =========================== producer warps ==============================
-        // Warp pw, lane l owns token pw + 4 l of every stage: one slot lookup and two bulk copies (K part, V part).
-        // Warp 0 also announces the bytes of the stage; a copy of another warp may land before the announcement: the
-        // phase cannot complete before the announcing arrive, so the early bytes are only booked ahead.
+        // A stage's tokens are dealt out to the four warps (token pw + 4 i to warp pw), so a stage occupies only
+        // TT / 4 lanes of each; the other lanes work on the stages after it: a warp looks up the slots of a batch of
+        // 32 / (TT / 4) stages with one load per lane, and the batch after that is requested before the copies of this
+        // one are issued. (With one stage of lookahead the slot load's latency, a microsecond under load, set the
+        // time per stage.) Warp 0 also announces the bytes of each stage; a copy of another warp may land before the
+        // announcement: the phase cannot complete before the announcing arrive, so the early bytes are only booked ahead.
         const int pw = warp - kGqaConsumerWarps;
-        const int my_tok = pw + kGqaProducerWarps * lane;
+        const int LPS = TT / kGqaProducerWarps;   // lanes per stage: 2, 4, 8 or 16
+        const int NB = 32 / LPS;                  // stages per batch
+        const int sb = lane / LPS;                // this lane's stage inside a batch
+        const int my_tok = pw + kGqaProducerWarps * (lane % LPS);
         const char* kbase = static_cast<const char*>(a.kmat) + static_cast<int64_t>(hg0) * a.k_s1 * 2;
         const char* vbase = static_cast<const char*>(a.vmat) + static_cast<int64_t>(hg0) * a.v_s1 * 2;
         const int64_t k_row = a.k_s0 * 2, v_row = a.v_s0 * 2;
         StageWalk walk;
         walk.init(pre, a.B, t0, t1);
-        int req, j0, cnt;
-        bool last;
-        bool have = walk.next(TT, req, j0, cnt, last);
-        auto fetch_slot = [&](int r, int j, int n) -> int64_t {
-            if (my_tok >= n) return 0;
-            const int L = pre[r + 1] - pre[r];
-            int64_t sl = token_slot(a, r, L, static_cast<int64_t>(j) + my_tok);
-            if (sl < 0 || sl >= a.slots) {
-                report_status(a.status, 1);
-                sl = 0;  // keep the byte count of the stage intact
+        // Walks the next batch: returns its number of stages; this lane keeps the token count of its stage and the slot of its token.
+        auto load_batch = [&](int& my_cnt, int64_t& my_slot) -> int {
+            int n = 0, req = 0, j0 = 0, cnt = 0, my_req = 0, my_j = 0;
+            bool last;
+            my_cnt = 0;
+            my_slot = 0;
+            for (; n < NB; ++n) {
+                if (!walk.next(TT, req, j0, cnt, last)) break;
+                if (n == sb) {
+                    my_req = req;
+                    my_j = j0;
+                    my_cnt = cnt;
+                }
             }
-            return sl;
+            if (my_tok < my_cnt) {
+                const int L = pre[my_req + 1] - pre[my_req];
+                int64_t sl = token_slot(a, my_req, L, static_cast<int64_t>(my_j) + my_tok);
+                if (sl < 0 || sl >= a.slots) {
+                    report_status(a.status, 1);
+                    sl = 0;  // keep the byte count of the stage intact
+                }
+                my_slot = sl;
+            }
+            return n;
         };
-        int64_t slot = have ? fetch_slot(req, j0, cnt) : 0;
+        int cur_cnt, nxt_cnt;
+        int64_t cur_slot, nxt_slot;
+        int n_cur = load_batch(cur_cnt, cur_slot);
         int ring = 0;
         uint32_t ring_phase = 0;
-        while (have) {
-            const int cur_cnt = cnt;
-            const int64_t cur_slot = slot;
-            have = walk.next(TT, req, j0, cnt, last);   // the next stage's slot is looked up before blocking
-            if (have) slot = fetch_slot(req, j0, cnt);
-            bool ok = true;
-            if (lane == 0) {
-                ok = mbar_wait(smem_u32(&bars[p.nstages + ring]), ring_phase ^ 1u, give_up);
-                if (ok && pw == 0) mbar_arrive_expect_tx(smem_u32(&bars[ring]), static_cast<uint32_t>(cur_cnt) * row_bytes * 2u);
+        bool ok = true;
+        while (ok && n_cur > 0) {
+            const int n_nxt = load_batch(nxt_cnt, nxt_slot);   // in flight while this batch's copies are issued
+            for (int s = 0; s < n_cur; ++s) {
+                const int cnt_s = __shfl_sync(0xffffffffu, cur_cnt, s * LPS);
+                if (lane == 0) {
+                    ok = mbar_wait(smem_u32(&bars[p.nstages + ring]), ring_phase ^ 1u, give_up);
+                    if (ok && pw == 0) mbar_arrive_expect_tx(smem_u32(&bars[ring]), static_cast<uint32_t>(cnt_s) * row_bytes * 2u);
+                }
+                ok = __all_sync(0xffffffffu, ok ? 1 : 0) != 0;
+                if (!ok) break;
+                if (sb == s && my_tok < cur_cnt) {
+                    const uint32_t full = smem_u32(&bars[ring]);
+                    const uint32_t dst = smem_u32(smem + static_cast<size_t>(ring) * p.stage_bytes) + static_cast<uint32_t>(my_tok) * static_cast<uint32_t>(p.pitch);
+                    bulk_g2s(dst, kbase + cur_slot * k_row, row_bytes, full);
+                    bulk_g2s(dst + v_off, vbase + cur_slot * v_row, row_bytes, full);
+                }
+                if (++ring == p.nstages) {
+                    ring = 0;
+                    ring_phase ^= 1u;
+                }
             }
-            if (!__all_sync(0xffffffffu, ok ? 1 : 0)) break;
-            if (my_tok < cur_cnt) {
-                const uint32_t full = smem_u32(&bars[ring]);
-                const uint32_t dst = smem_u32(smem + static_cast<size_t>(ring) * p.stage_bytes) + static_cast<uint32_t>(my_tok) * static_cast<uint32_t>(p.pitch);
-                bulk_g2s(dst, kbase + cur_slot * k_row, row_bytes, full);
-                bulk_g2s(dst + v_off, vbase + cur_slot * v_row, row_bytes, full);
-            }
-            if (++ring == p.nstages) {
-                ring = 0;
-                ring_phase ^= 1u;
-            }
+            n_cur = n_nxt;
+            cur_cnt = nxt_cnt;
+            cur_slot = nxt_slot;
         }
     } else {
         // =========================== consumer warps ==============================

@@ -852,3 +852,82 @@ def test_paged_attention_batches(F, dtype, heads, kv_heads, dim, block):
     assert torch.count_nonzero(out[2]) == 0   # the empty request
     out64 = F.paged_attention(q.cuda(), k.cuda(), v.cuda(), None, lens, heads, kv_heads, dim, table.long().cuda(), block)
     assert torch.equal(out64, out)
+
+
+# ------------------------------------------------------------------ grouped K/V heads: the single-pass kernel
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("heads,kv_heads,dim,block", [(16, 8, 128, 16), (32, 8, 128, 16), (64, 8, 128, 16), (16, 1, 128, 16), (12, 3, 128, 8), (40, 5, 64, 32),
+                                                      (32, 2, 64, 16), (24, 12, 128, 16), (7, 1, 64, 4), (48, 16, 128, 128)])
+def test_paged_attention_grouped_heads(F, dtype, heads, kv_heads, dim, block):
+    """Query-head groups of 2 to 16 over 1 to 16 K/V heads (powers of two and not), head dims 64 and 128: every
+    shape of the tensor-core kernel (K/V heads per CTA 1, 2, 4, 8; 8 to 1 token blocks per stage; a second CTA row
+    for the heads beyond eight), with request lengths that leave ragged last blocks, an empty and a one-token request."""
+    g = torch.Generator().manual_seed(heads * 131 + kv_heads * 7 + dim)
+    lens = [1, 700, 0, 129, 16, 17, 333, 15, 1024, 31]
+    B = len(lens)
+    nblocks = sum((L + block - 1) // block for L in lens) + 3
+    rows = nblocks * block
+    k = (torch.randn(rows, kv_heads * dim, generator=g) * 0.5).to(dtype)
+    v = torch.randn(rows, kv_heads * dim, generator=g).to(dtype)
+    q = torch.randn(B, heads * dim, generator=g).to(dtype)
+    perm = torch.randperm(nblocks, generator=g)
+    width = max((L + block - 1) // block for L in lens)
+    table = torch.zeros(B, width, dtype=torch.int32)
+    used = 0
+    for i, L in enumerate(lens):
+        nb = (L + block - 1) // block
+        table[i, :nb] = perm[used:used + nb].to(torch.int32)
+        used += nb
+    want = golden.paged_attention(q, k, v, None, lens, heads, kv_heads, dim, table, block, upcast=True)
+    out = F.paged_attention(q.cuda(), k.cuda(), v.cuda(), None, lens, heads, kv_heads, dim, table.cuda(), block)
+    close(out, want, dtype)
+    assert torch.count_nonzero(out[2]) == 0   # the empty request
+    # same answer from the one-CTA-per-(request, head) kernel, which shares no code with the tensor-core one
+    F.set_option("decode_plain", 1)
+    try:
+        plain = F.paged_attention(q.cuda(), k.cuda(), v.cuda(), None, lens, heads, kv_heads, dim, table.cuda(), block)
+    finally:
+        F.set_option("decode_plain", 0)
+    close(out, plain.float().cpu(), dtype)
+    # rows the block table never names may hold anything, infinities and NaNs included: they are never weighted in
+    kk, vv = k.clone(), v.clone()
+    named = torch.zeros(rows, dtype=torch.bool)
+    for i, L in enumerate(lens):
+        j = torch.arange(L)
+        named[table[i].long()[j // block] * block + j % block] = True
+    kk[~named] = float("nan")
+    vv[~named] = float("inf")
+    out2 = F.paged_attention(q.cuda(), kk.cuda(), vv.cuda(), None, lens, heads, kv_heads, dim, table.cuda(), block)
+    assert torch.equal(out2, out)
+
+
+def test_paged_attention_grouped_full_size(F):
+    """64 query heads over 8 K/V heads at the size the benchmark runs (64 requests of 512..4096 tokens): sampled
+    requests against the oracle with fp32 accumulation, run-to-run identical bits, and the same result from a cache
+    whose blocks were moved to other places."""
+    from diopi_b200 import opbench
+    c = opbench.paged_case(8)
+    args = (c["lens"], c["q_heads"], c["kv_heads"], c["D"])
+    out = F.paged_attention(c["q"], c["k"], c["v"], None, *args, c["table"], c["block"])
+    again = F.paged_attention(c["q"], c["k"], c["v"], None, *args, c["table"], c["block"])
+    assert torch.equal(out, again)
+    lens = c["lens"]
+    reqs = [0, 31, 63, lens.index(max(lens)), lens.index(min(lens))]
+    bs, tab = c["block"], c["table"].cpu()
+    for i in reqs:
+        nb = (lens[i] + bs - 1) // bs
+        blocks = tab[i, :nb].long()
+        rows = (blocks[:, None] * bs + torch.arange(bs)[None, :]).reshape(-1).cuda()
+        k1, v1 = c["k"][rows].cpu(), c["v"][rows].cpu()
+        t1 = torch.arange(nb, dtype=torch.int32).view(1, nb)
+        want = golden.paged_attention(c["q"][i:i + 1].cpu(), k1, v1, None, [lens[i]], c["q_heads"], c["kv_heads"], c["D"], t1, bs, upcast=True)
+        close(out[i:i + 1], want, torch.float16)
+    nblocks = c["k"].shape[0] // bs
+    perm = torch.randperm(nblocks, device="cuda")        # new block b holds old block perm[b]
+    inv = torch.empty_like(perm)
+    inv[perm] = torch.arange(nblocks, device="cuda")
+    k2 = c["k"].view(nblocks, bs, -1)[perm].reshape(c["k"].shape)
+    v2 = c["v"].view(nblocks, bs, -1)[perm].reshape(c["v"].shape)
+    t2 = inv[c["table"].long()].to(torch.int32)
+    moved = F.paged_attention(c["q"], k2, v2, None, *args, t2, c["block"])
+    assert torch.equal(moved, out)
