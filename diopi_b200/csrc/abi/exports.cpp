@@ -327,7 +327,8 @@ B200_EXPORT diopiError_t diopiContextAttentionInference(diopiContextHandle_t ctx
         if (qv.numel == 0 || a.B == 0) return;
         cudaStream_t st = stream_of(ctx);
         const DeviceInfo& di = device_info();
-        k::launch_prefill(a, di.sm_count, di.max_smem_optin, st);
+        const char* path = k::launch_prefill(a, di.sm_count, di.max_smem_optin, st);
+        logf("prefill B=%d H=%d D=%d rows=%ld kv_group=%d: %s kernel", a.B, a.H, a.D, (long)a.total_rows, a.kv_group, path);
         B200_CUDA(cudaGetLastError());
     });
 }
@@ -877,7 +878,8 @@ B200_EXPORT diopiError_t diopiPromptFlashAttention(diopiContextHandle_t ctx, dio
         if (rows == 0) return;
         cudaStream_t st = stream_of(ctx);
         const DeviceInfo& di = device_info();
-        k::launch_prefill(a, di.sm_count, di.max_smem_optin, st);
+        const char* path = k::launch_prefill(a, di.sm_count, di.max_smem_optin, st);
+        logf("prefill B=%d H=%d D=%d rows=%ld kv_group=%d: %s kernel", a.B, a.H, a.D, (long)a.total_rows, a.kv_group, path);
         B200_CUDA(cudaGetLastError());
     });
 }

@@ -9,7 +9,7 @@
 //
 // This file holds the blockwise SIMT kernel: any dtype (fp16/bf16/fp32), any D up to 256, never
 // more than two K/V tiles of 32 keys in shared memory, fp32 arithmetic with an online softmax. It
-// is the path for shapes the tensor-core kernel does not take.
+// is the path for shapes the tensor-core kernel does not take (fp32, head dims other than 64, 128, 256, unaligned rows).
 #include "dev_util.cuh"
 
 namespace b200 {
@@ -140,17 +140,18 @@ void launch_simt(const PrefillArgs& a, cudaStream_t st) {
 
 }  // namespace
 
-void launch_prefill(const PrefillArgs& a, int sm_count, int max_smem, cudaStream_t st) {
-    if (a.B <= 0 || a.H <= 0 || a.D <= 0 || a.total_rows <= 0) return;
+const char* launch_prefill(const PrefillArgs& a, int sm_count, int max_smem, cudaStream_t st) {
+    if (a.B <= 0 || a.H <= 0 || a.D <= 0 || a.total_rows <= 0) return "none";
     bool taken = false;
     launch_prefill_tc(a, sm_count, max_smem, st, &taken);
-    if (taken) return;
+    if (taken) return "tensor-core";
     switch (a.dt) {
         case Dt::F16: launch_simt<__half>(a, st); break;
         case Dt::BF16: launch_simt<__nv_bfloat16>(a, st); break;
         case Dt::F32: launch_simt<float>(a, st); break;
         default: break;
     }
+    return "simt";
 }
 
 }  // namespace k

@@ -1,20 +1,29 @@
 // Tensor-core causal prefill for sm_100a: tcgen05.mma with accumulators in TMEM, operands staged by TMA.
-// Path of diopiContextAttentionInference for fp16/bf16, head_dim 128, dense 16-byte aligned rows; every
-// other shape runs on the blockwise SIMT kernel. Replaces the per-request matmul/mask/softmax/matmul
-// chain of impl/torch/functions/functions_lightllm.cpp:109-147.
+// Path of diopiContextAttentionInference (and of diopiPromptFlashAttention) for fp16/bf16, head_dim 64, 128 or 256,
+// dense 16-byte aligned rows; every other shape runs on the blockwise SIMT kernel. Replaces the per-request
+// matmul/mask/softmax/matmul chain of impl/torch/functions/functions_lightllm.cpp:109-147.
 //
-// One CTA = one tile of 128 query rows of one (request, head); two CTAs share an SM so that one CTA's
-// soft-max overlaps the other's MMAs. Per CTA, for key blocks of 64 up to the causal limit:
-//   warp 0 (one lane)  TMA: Q once (two 64-wide boxes, 128-byte swizzle), then K_j and V_j into a 2-stage ring
-//   warp 1 (one lane)  issues both products, each as soon as its inputs are ready (probing the barriers, never
-//                      blocking on one while the other could go):
-//                        S_j = Q K_j^T  tcgen05.mma M128 N64 K16 x 8, both operands K-major from shared memory,
-//                                       into TMEM buffer S[j%2] once P V of block j - 2 has released it
-//                        O  += P_j V_j  tcgen05.mma M128 N128 K16 x 4, A = P_j read from TMEM, B = V_j MN-major
-//   warps 2-5          thread = query row: tcgen05.ld of its S row, causal/length mask, online soft-max in base 2
-//                      (scale and maximum folded into one fma + ex2.approx per score; the reference maximum is
-//                      only raised when the row maximum grew by more than 2^8, and only then is O in TMEM
-//                      rescaled), P_j packed to 16 bit and written over the S cells just read
+// One CTA per SM works on NT tiles of 128 query rows of one (request, head) that share every K/V block they read
+// (key blocks of 64; head_dim 64 and 128: two tiles, head_dim 256: one), with two score buffers per tile:
+//   warp 0 (one lane)  TMA: the Q tiles once (64-wide boxes, 128-byte swizzle), then K_j and V_j into a ring of 4 (2) stages
+//   warp 1 (warp 2)    one lane issues every product of tile 0 (tile 1) as soon as its inputs are ready (probing the
+//                      barriers, never blocking on one while another could go):
+//                        S_t = Q_t K_j^T  tcgen05.mma M128 N64 K16, both operands K-major from shared memory
+//                        O_t += P_t V_j   tcgen05.mma M128 N<HD> K16, A = P_t read from TMEM, B = V_j MN-major
+//   warps 4-7 (8-11)   soft-max of tile 0 (tile 1), thread = query row: tcgen05.ld of its S row, causal/length mask,
+//                      online soft-max in base 2 (scale and maximum folded into one fma + ex2 per score; the reference
+//                      maximum is only raised when the row maximum grew by more than 2^8, and only then is O in TMEM
+//                      rescaled), P packed to 16 bit and written over the S cells just read
+// While the soft-max of block j reads one score buffer of a tile, Q_t K_{j+1}^T fills the other. A K/V block is fetched
+// and held in shared memory once for both tiles. TMEM columns (512 allocated): score buffers at 64 * (2 t + j % 2),
+// O_t at 256 + t * HD.
+// What the measurements taught (benchmark config: 8 requests of 1024..8192 rows, 32 heads, D 128, fp16):
+//   one tile per CTA, two CTAs per SM, own K/V copies: 873 TFLOP/s; this form: 979 TFLOP/s. On the way: one thread
+//   issuing for both tiles was the limit (1.30 of the time of one issuing warp per tile with descriptors made once); key
+//   blocks of 128 with a single score buffer per tile (no room in TMEM for two) serialise Q K^T, soft-max and P V of a
+//   tile and reached 680 TFLOP/s; holding a row of 128 scores in registers spills; with the exponentials removed
+//   altogether the time does not change, so the special-function unit is not the limit: the soft-max warps
+//   (two per scheduler) are bound by instruction issue and dependent latencies, about 7 instructions per score.
 // The L x L score and mask tensors of the reference never exist; FLOPs counted = 4*D*L*(L+1)/2 per head.
 //
 // All waits are bounded (2 s); a wait that runs out sets a flag, every role leaves its loop, TMEM is
@@ -35,32 +44,38 @@ namespace {
 
 using namespace sm100;  // NOLINT
 
-constexpr int BM = 128;      // query rows per CTA
-constexpr int BN = 64;       // keys per block
-constexpr int HD = 128;      // head dim
-constexpr int kStages = 2;   // K/V ring
-constexpr int kDefaultPolyEvery = 8;  // share of the exponentials computed on the fma pipe (see prefill_tc_kernel)
-constexpr int kThreads = 192;
+constexpr int BM = 128;      // query rows per tile
 constexpr float kLog2e = 1.4426950408889634f;
+constexpr uint32_t kTmemCols = 512;
+constexpr uint32_t kColO = 256;
 
-// shared memory map (bytes); every operand tile starts on a 1024-byte boundary (128-byte swizzle atoms)
-constexpr int kQBytes = BM * HD * 2;            // 32 KB: two [128 x 64] blocks
-constexpr int kKStage = BN * HD * 2;            // 16 KB: two [64 x 64] blocks
-constexpr int kVStage = BN * HD * 2;            // 16 KB
-constexpr int kOffQ = 0;
-constexpr int kOffK = kOffQ + kQBytes;
-constexpr int kOffV = kOffK + kStages * kKStage;
-constexpr int kOffBar = kOffV + kStages * kVStage;   // 96 KB
-constexpr int kNumBars = 15;
-constexpr int kOffTmemSlot = kOffBar + kNumBars * 8;
-constexpr int kOffFlag = kOffTmemSlot + 8;
-constexpr int kSmemBytes = kOffFlag + 8;          // two CTAs per SM: 2 * (96.2 KB + 1 KB reserved) of the SM's 228 KB
+enum Bar { Q_FULL = 0, K_FULL = 1, V_FULL = 5, K_EMPTY = 9, V_EMPTY = 13, O_FULL = 17, S_FULL = 19, S_EMPTY = 23, P_FULL = 27, kNumBars = 31 };   // up to four ring stages and four score buffers
 
-// TMEM columns (fp32 cells): S[0] 0..63, S[1] 64..127 (P_j overwrites the first 32 cells of S[j%2]), O 128..255
-constexpr uint32_t kTmemCols = 256;
-constexpr uint32_t kColS0 = 0, kColO = 128;
-
-enum Bar { Q_FULL = 0, K_FULL = 1, V_FULL = 3, K_EMPTY = 5, V_EMPTY = 7, S_FULL = 9, S_EMPTY = 11, P_FULL = 13, O_FULL = 14 };
+// Shared-memory map and sizes of one configuration; every operand tile starts on a 1024-byte boundary (swizzle atoms).
+template <int HD, int BN, int NT>
+struct Cfg {
+    static_assert(HD % 64 == 0 && HD <= 256 && BN == 64 && (NT == 1 || NT == 2), "unsupported tile shape");
+    static_assert(NT * HD <= 256, "the O tiles take TMEM columns 256..511");
+    // score buffers per tile: as many as fit TMEM columns 0..255, two at most (a second one lets Q K^T of block j + 1 run
+    // while the soft-max of block j reads the first)
+    static constexpr int kSlotsPerTile = 256 / (NT * BN) >= 2 ? 2 : 1;
+    static_assert(NT * BN * kSlotsPerTile <= 256, "score buffers take TMEM columns 0..255");
+    static constexpr int kThreads = 128 + 128 * NT;   // warp group 0: TMA warp, MMA warp, two idle warps; then one soft-max warp group per tile
+    static constexpr int kDBlocks = HD / 64;          // 64-wide column blocks of a row
+    static constexpr int kQTile = BM * HD * 2;
+    static constexpr int kKStage = BN * HD * 2;
+    // K/V ring: four stages where they fit beside the Q tiles (64-key blocks at head_dim <= 128), else two
+    static constexpr int kStages = (NT * BM * HD * 2 + 8 * BN * HD * 2 <= 200 * 1024) ? 4 : 2;
+    static constexpr int kOffQ = 0;
+    static constexpr int kOffK = kOffQ + NT * kQTile;
+    static constexpr int kOffV = kOffK + kStages * kKStage;
+    static constexpr int kOffBar = kOffV + kStages * kKStage;
+    static constexpr int kOffTmemSlot = kOffBar + kNumBars * 8;
+    static constexpr int kOffFlag = kOffTmemSlot + 8;
+    static constexpr int kUsedBytes = kOffFlag + 8;
+    // at least 120 KB, so that never two CTAs share an SM: each allocates all 512 TMEM columns
+    static constexpr int kSmemBytes = kUsedBytes > 120 * 1024 ? kUsedBytes : 120 * 1024;
+};
 
 struct TcParams {
     IndexArg b_start, b_len;
@@ -68,7 +83,7 @@ struct TcParams {
     int64_t total_rows;
     void* out;
     int64_t o_s0, o_s1;
-    int n_tiles_max;
+    int n_groups_max;      // upper bound of the number of groups of NT tiles over all requests
     float scale_log2;
     int* status;
     int64_t uniform_len;   // > 0: request i owns rows [i * uniform_len, (i + 1) * uniform_len)
@@ -143,45 +158,59 @@ __device__ __forceinline__ uint32_t pack2(float a, float b) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
+// Share of the exponentials computed on the fma pipe, per head dim (see prefill_tc_kernel).
+constexpr int kPolyEvery64 = 2, kPolyEvery128 = 8, kPolyEvery256 = 8;
+
 // kPolyEvery: of every kPolyEvery groups of four scores, one computes two of its exponentials on the fma pipe
 // (1: half of all exponentials, 2: a quarter, 4: an eighth, 8: a sixteenth, 0: none).
-template <bool BF16, int kPolyEvery>
-__global__ void __launch_bounds__(kThreads, 2) prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-                                                                   const __grid_constant__ CUtensorMap map_v, const TcParams p) {
+template <bool BF16, int HD, int BN, int NT, int kPolyEvery>
+__global__ void __launch_bounds__(Cfg<HD, BN, NT>::kThreads, 1)
+    prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                      const TcParams p) {
+    using C = Cfg<HD, BN, NT>;
+    constexpr int kStages = C::kStages;
     extern __shared__ __align__(1024) unsigned char smem[];
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kOffBar);
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + kOffTmemSlot);
-    volatile int* give_up = reinterpret_cast<volatile int*>(smem + kOffFlag);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::kOffBar);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + C::kOffTmemSlot);
+    volatile int* give_up = reinterpret_cast<volatile int*>(smem + C::kOffFlag);
     auto bar = [&](int i) { return smem_u32(&bars[i]); };
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int h = blockIdx.y;
     const int hkv = h / p.kv_group;   // grouped-query attention: several query heads share one K/V head
 
-    // ---- which (request, row tile) is this CTA? Heaviest tiles (late rows) are handed out first. ----
+    // ---- which (request, group of NT row tiles) is this CTA? Heaviest groups (late rows) are handed out first. ----
     int req = -1;
     int64_t L = 0, start = 0, r0 = 0;
     {
-        const int64_t flat = static_cast<int64_t>(p.n_tiles_max) - 1 - blockIdx.x;
+        const int64_t flat = static_cast<int64_t>(p.n_groups_max) - 1 - blockIdx.x;
         int64_t before = 0;
         for (int i = 0; i < p.B; ++i) {
             int64_t Li = p.uniform_len > 0 ? p.uniform_len : load_index(p.b_len, i);
             const int64_t si = p.uniform_len > 0 ? i * p.uniform_len : load_index(p.b_start, i);
             if (Li <= 0 || si < 0 || si >= p.total_rows) continue;
             Li = imin64(Li, p.total_rows - si);
-            const int64_t nt = (Li + BM - 1) / BM;
-            if (flat < before + nt) {
+            const int64_t ng = (Li + BM * NT - 1) / (BM * NT);
+            if (flat < before + ng) {
                 req = i;
                 L = Li;
                 start = si;
-                r0 = (flat - before) * BM;
+                r0 = (flat - before) * (BM * NT);
                 break;
             }
-            before += nt;
+            before += ng;
         }
     }
     if (req < 0) return;  // the whole CTA leaves together, before any barrier or TMEM use
-    const int nblk = static_cast<int>((imin64(L, r0 + BM) + BN - 1) / BN);
+    // key blocks tile t reads: up to its last row's diagonal; a tile that starts beyond the request has none
+    int nblk[NT];
+    int nblk_max = 0;
+#pragma unroll
+    for (int t = 0; t < NT; ++t) {
+        const int64_t rt = r0 + static_cast<int64_t>(t) * BM;
+        nblk[t] = rt < L ? static_cast<int>((imin64(L, rt + BM) + BN - 1) / BN) : 0;
+        nblk_max = nblk[t] > nblk_max ? nblk[t] : nblk_max;
+    }
 
     if ((smem_u32(smem) & 1023u) != 0) {  // the swizzled tiles need a 1024-byte aligned base; refuse rather than compute garbage
         if (tid == 0) report_status(p.status, 3);
@@ -192,13 +221,16 @@ __global__ void __launch_bounds__(kThreads, 2) prefill_tc_kernel(const __grid_co
         for (int s = 0; s < kStages; ++s) {
             mbar_init(bar(K_FULL + s), 1);
             mbar_init(bar(V_FULL + s), 1);
-            mbar_init(bar(K_EMPTY + s), 1);
-            mbar_init(bar(V_EMPTY + s), 1);
-            mbar_init(bar(S_FULL + s), 1);
-            mbar_init(bar(S_EMPTY + s), 1);   // freed by the commit that follows P V of the block that used the buffer
+            mbar_init(bar(K_EMPTY + s), NT);   // one arrival per tile: the commit after its product, or a plain arrive for a tile that skips the block
+            mbar_init(bar(V_EMPTY + s), NT);
         }
-        mbar_init(bar(P_FULL), 4);
         mbar_init(bar(O_FULL), 1);
+        mbar_init(bar(O_FULL + 1), 1);
+        for (int s = 0; s < 4; ++s) {
+            mbar_init(bar(S_FULL + s), 1);
+            mbar_init(bar(S_EMPTY + s), 1);    // freed by the commit that follows the P V that read the buffer
+            mbar_init(bar(P_FULL + s), 4);     // the four warps of a soft-max group
+        }
         *give_up = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -211,75 +243,103 @@ __global__ void __launch_bounds__(kThreads, 2) prefill_tc_kernel(const __grid_co
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
+    // Score buffer of (tile t, block j) and how many times it was used before: a tile's buffers take turns.
+    constexpr int SPT = C::kSlotsPerTile;
+    auto slot_of = [](int t, int j) { return t * SPT + (j % SPT); };
+    auto use_of = [](int j) { return j / SPT; };
+
     if (warp == 0) {
         // ================================ TMA producer =================================
         if (lane == 0) {
             const int row0 = static_cast<int>(start + r0);
-            mbar_expect_tx(bar(Q_FULL), kQBytes);
-            tma_load_3d(smem_u32(smem + kOffQ), &map_q, 0, h, row0, bar(Q_FULL));
-            tma_load_3d(smem_u32(smem + kOffQ + BM * 128), &map_q, 64, h, row0, bar(Q_FULL));
-            for (int j = 0; j < nblk; ++j) {
+            mbar_expect_tx(bar(Q_FULL), NT * C::kQTile);
+#pragma unroll
+            for (int t = 0; t < NT; ++t)
+#pragma unroll
+                for (int d = 0; d < C::kDBlocks; ++d)
+                    tma_load_3d(smem_u32(smem + C::kOffQ + t * C::kQTile + d * (BM * 128)), &map_q, d * 64, h, row0 + t * BM, bar(Q_FULL));
+            for (int j = 0; j < nblk_max; ++j) {
                 const int s = j % kStages;
                 const uint32_t ph = static_cast<uint32_t>((j / kStages) & 1);
                 const int krow = static_cast<int>(start + static_cast<int64_t>(j) * BN);
                 if (!mbar_wait(bar(K_EMPTY + s), ph ^ 1u, give_up)) break;
-                mbar_expect_tx(bar(K_FULL + s), kKStage);
-                tma_load_3d(smem_u32(smem + kOffK + s * kKStage), &map_k, 0, hkv, krow, bar(K_FULL + s));
-                tma_load_3d(smem_u32(smem + kOffK + s * kKStage + BN * 128), &map_k, 64, hkv, krow, bar(K_FULL + s));
+                mbar_expect_tx(bar(K_FULL + s), C::kKStage);
+#pragma unroll
+                for (int d = 0; d < C::kDBlocks; ++d)
+                    tma_load_3d(smem_u32(smem + C::kOffK + s * C::kKStage + d * (BN * 128)), &map_k, d * 64, hkv, krow, bar(K_FULL + s));
                 if (!mbar_wait(bar(V_EMPTY + s), ph ^ 1u, give_up)) break;
-                mbar_expect_tx(bar(V_FULL + s), kVStage);
-                tma_load_3d(smem_u32(smem + kOffV + s * kVStage), &map_v, 0, hkv, krow, bar(V_FULL + s));
-                tma_load_3d(smem_u32(smem + kOffV + s * kVStage + BN * 128), &map_v, 64, hkv, krow, bar(V_FULL + s));
+                mbar_expect_tx(bar(V_FULL + s), C::kKStage);
+#pragma unroll
+                for (int d = 0; d < C::kDBlocks; ++d)
+                    tma_load_3d(smem_u32(smem + C::kOffV + s * C::kKStage + d * (BN * 128)), &map_v, d * 64, hkv, krow, bar(V_FULL + s));
             }
         }
-    } else if (warp == 1) {
-        // ================================ MMA issuer ===================================
-        if (lane == 0) {
+    } else if (warp == 1 || (NT == 2 && warp == 2)) {
+        // ================================ MMA issuers: one warp (one lane) per tile ===================================
+        const int t = warp - 1;
+        if (lane == 0 && nblk[t] == 0) {
+            // A tile beyond the request's end reads no block: its share of the K/V hand-backs is given as soon as each
+            // block has landed (an arrival must not fall into an earlier phase of the barrier).
+            bool ok = true;
+            for (int j = 0; ok && j < nblk_max; ++j) {
+                const int s = j % kStages;
+                const uint32_t ph = static_cast<uint32_t>((j / kStages) & 1);
+                ok = mbar_wait(bar(K_FULL + s), ph, give_up) && mbar_wait(bar(V_FULL + s), ph, give_up);
+                if (ok) {
+                    mbar_arrive(bar(K_EMPTY + s));
+                    mbar_arrive(bar(V_EMPTY + s));
+                }
+            }
+        } else if (lane == 0) {
             const uint32_t idesc_qk = make_idesc(BM, BN, BF16 ? 1 : 0, 0);
             const uint32_t idesc_pv = make_idesc(BM, HD, BF16 ? 1 : 0, 1);
-            const uint32_t q_addr = smem_u32(smem + kOffQ);
+            // Descriptors are made once; a product adds the (compile-time) offset of its 16-wide k step to the address field.
+            const uint64_t q_desc = make_desc(smem_u32(smem + C::kOffQ + t * C::kQTile), 0, 1024);
+            const uint64_t k_desc0 = make_desc(smem_u32(smem + C::kOffK), 0, 1024);          // stage s: + s * stage bytes in the address field
+            const uint64_t v_desc0 = make_desc(smem_u32(smem + C::kOffV), BN * 128, 1024);
+            const int my_blocks = nblk[t];
             bool ok = mbar_wait(bar(Q_FULL), 0, give_up);
-            // Event driven: Q K^T of the next block and P V of the oldest finished soft-max are issued in whatever
-            // order their inputs become ready, so a ready P never queues behind a Q K^T that still waits for its
-            // S buffer, and the other way round.
+            // Event driven: the next Q K^T and the P V of the oldest finished soft-max are issued in whatever order their
+            // inputs become ready; P V first, because it is what frees a score buffer.
             int nqk = 0, npv = 0;
             unsigned long long idle_since = 0;
-            while (ok && npv < nblk) {
+            while (ok && npv < my_blocks) {
                 bool progressed = false;
                 if (npv < nqk) {
-                    const int i = npv;
-                    const int s = i % kStages;
-                    if (mbar_test(bar(P_FULL), static_cast<uint32_t>(i & 1)) && mbar_test(bar(V_FULL + s), static_cast<uint32_t>((i / kStages) & 1))) {
+                    const int j = npv;
+                    const int s = j % kStages, sl = slot_of(t, j);
+                    if (mbar_test(bar(P_FULL + sl), static_cast<uint32_t>(use_of(j) & 1)) && mbar_test(bar(V_FULL + s), static_cast<uint32_t>((j / kStages) & 1))) {
                         tc_fence_after();
-                        const uint32_t v_addr = smem_u32(smem + kOffV + s * kVStage);
+                        const uint64_t vd = v_desc0 + static_cast<uint64_t>(s) * (C::kKStage >> 4);
 #pragma unroll
-                        for (int t = 0; t < BN / 16; ++t) {
-                            // B = V [64 keys x 128 d], MN-major: 16 keys = 16 rows of 128 bytes; the second 64-wide d block is 8 KB further
-                            const uint64_t bd = make_desc(v_addr + t * 16 * 128, BN * 128, 1024);
-                            // A = P in TMEM: 16 keys = 8 cells of the S buffer the soft-max threads overwrote
-                            umma_ts(tmem_base + kColO, tmem_base + kColS0 + s * BN + t * 8, bd, idesc_pv, (i > 0 || t > 0) ? 1u : 0u);
+                        for (int kk = 0; kk < BN / 16; ++kk) {
+                            // B = V [BN keys x HD], MN-major: 16 keys = 16 rows of 128 bytes; the next 64-wide column block is BN * 128 bytes further.
+                            // A = P in TMEM: 16 keys = 8 cells of the score buffer the soft-max threads overwrote.
+                            umma_ts(tmem_base + kColO + t * HD, tmem_base + sl * BN + kk * 8, vd + static_cast<uint64_t>((kk * 16 * 128) >> 4), idesc_pv,
+                                    (j > 0 || kk > 0) ? 1u : 0u);
                         }
-                        umma_commit(bar(S_EMPTY + s));   // the S/P buffer may be overwritten by Q K^T of block i + 2
+                        umma_commit(bar(S_EMPTY + sl));
                         umma_commit(bar(V_EMPTY + s));
-                        umma_commit(bar(O_FULL));
+                        umma_commit(bar(O_FULL + t));
                         ++npv;
                         progressed = true;
                     }
                 }
-                if (nqk < nblk) {
-                    const int s = nqk % kStages;
-                    const uint32_t ph = static_cast<uint32_t>((nqk / kStages) & 1);
-                    if (mbar_test(bar(K_FULL + s), ph) && mbar_test(bar(S_EMPTY + s), ph ^ 1u)) {
+                if (nqk < my_blocks) {
+                    const int j = nqk;
+                    const int s = j % kStages, sl = slot_of(t, j);
+                    if (mbar_test(bar(K_FULL + s), static_cast<uint32_t>((j / kStages) & 1)) &&
+                        mbar_test(bar(S_EMPTY + sl), static_cast<uint32_t>((use_of(j) & 1) ^ 1))) {
                         tc_fence_after();
-                        const uint32_t k_addr = smem_u32(smem + kOffK + s * kKStage);
+                        const uint64_t kd = k_desc0 + static_cast<uint64_t>(s) * (C::kKStage >> 4);
 #pragma unroll
-                        for (int t = 0; t < HD / 16; ++t) {
-                            // both operands K-major; d block t/4 (64 wide), 16 d = 32 bytes inside the swizzled row
-                            const uint64_t ad = make_desc(q_addr + (t / 4) * (BM * 128) + (t % 4) * 32, 0, 1024);
-                            const uint64_t bd = make_desc(k_addr + (t / 4) * (BN * 128) + (t % 4) * 32, 0, 1024);
-                            umma(tmem_base + kColS0 + s * BN, ad, bd, idesc_qk, t > 0 ? 1u : 0u);
+                        for (int kk = 0; kk < HD / 16; ++kk) {
+                            // both operands K-major; column block kk / 4 (64 wide), 16 columns = 32 bytes inside the swizzled row
+                            const uint64_t ad = q_desc + static_cast<uint64_t>(((kk / 4) * (BM * 128) + (kk % 4) * 32) >> 4);
+                            const uint64_t bd = kd + static_cast<uint64_t>(((kk / 4) * (BN * 128) + (kk % 4) * 32) >> 4);
+                            umma(tmem_base + sl * BN, ad, bd, idesc_qk, kk > 0 ? 1u : 0u);
                         }
-                        umma_commit(bar(S_FULL + s));
+                        umma_commit(bar(S_FULL + sl));
                         umma_commit(bar(K_EMPTY + s));
                         ++nqk;
                         progressed = true;
@@ -293,115 +353,151 @@ __global__ void __launch_bounds__(kThreads, 2) prefill_tc_kernel(const __grid_co
                     if (idle_since == 0) idle_since = now;
                     if (now - idle_since > kWaitLimitNs) {
                         *give_up = 1;
-                        break;
+                        ok = false;
                     }
                 }
             }
+            // blocks beyond this tile's diagonal that the other tile still reads: hand them back as they land
+            for (int j = my_blocks; ok && j < nblk_max; ++j) {
+                const int s = j % kStages;
+                const uint32_t ph = static_cast<uint32_t>((j / kStages) & 1);
+                ok = mbar_wait(bar(K_FULL + s), ph, give_up) && mbar_wait(bar(V_FULL + s), ph, give_up);
+                if (ok) {
+                    mbar_arrive(bar(K_EMPTY + s));
+                    mbar_arrive(bar(V_EMPTY + s));
+                }
+            }
         }
-    } else {
+    } else if (warp >= 4) {
         // ================================ soft-max warps: thread = query row ==========================
-        const int quarter = warp & 3;                 // the TMEM lane quarter this warp may touch
-        const int row = quarter * 32 + lane;          // row inside the tile
-        const int64_t rr = r0 + row;                  // row inside the request
+        const int t = NT == 2 ? ((warp - 4) >> 2) : 0;   // the tile of this warp group
+        const int quarter = warp & 3;                    // the TMEM lane quarter this warp may touch
+        const int row = quarter * 32 + lane;             // row inside the tile
+        const int64_t rt0 = r0 + static_cast<int64_t>(t) * BM;   // first row of the tile inside the request
+        const int64_t rr = rt0 + row;                    // this thread's row inside the request
+        const int my_blocks = nblk[t];
         const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+        const uint32_t o_col = kColO + t * HD;
         float m_used = -INFINITY, l = 0.f;
         bool ok = true;
-        for (int j = 0; j < nblk; ++j) {
-            const int s = j % kStages;
-            const uint32_t ph = static_cast<uint32_t>((j / kStages) & 1);
-            if (!warp_wait(bar(S_FULL + s), ph, give_up)) {
+        for (int j = 0; j < my_blocks; ++j) {
+            const int sl = slot_of(t, j);
+            const uint32_t ph = static_cast<uint32_t>(use_of(j) & 1);
+            if (!warp_wait(bar(S_FULL + sl), ph, give_up)) {
                 ok = false;
                 break;
             }
             tc_fence_after();
-            uint32_t u0[32], u1[32];
-            tmem_ld32(lane_base + kColS0 + s * BN, u0);
-            tmem_ld32(lane_base + kColS0 + s * BN + 32, u1);
-            tmem_wait_ld();
-
-            // Raw scores stay in the registers the TMEM load filled; scale and maximum are folded into the
-            // exponent: p = 2^(s * scale - m) is one fma and one ex2 per element.
-            float sc[BN];
-#pragma unroll
-            for (int c = 0; c < 32; ++c) {
-                sc[c] = __uint_as_float(u0[c]);
-                sc[c + 32] = __uint_as_float(u1[c]);
-            }
             const int64_t key0 = static_cast<int64_t>(j) * BN;
-            if ((key0 + BN - 1 > r0) || (key0 + BN > L)) {  // block touches the diagonal or the request's end
-                const int64_t lim = imin64(rr, L - 1) - key0;  // last allowed column of this row inside the block
+            const bool edge = (key0 + BN - 1 > rt0) || (key0 + BN > L);   // block touches the tile's diagonal or the request's end
+            const int lim = edge ? static_cast<int>(imin64(imin64(rr, L - 1) - key0, BN)) : BN;   // last allowed column of this row inside the block
+            {
+                // 64 scores fit in registers: one trip to TMEM, the row maximum and the exponentials on the same registers.
+                // Two copies of the code, with and without the mask, so that a block away from the diagonal executes no
+                // masking instruction at all (merged, the compiler turns the mask into 64 predicated selects every block).
+                auto block64 = [&](auto edge_c) -> bool {
+                    constexpr bool kEdge = decltype(edge_c)::value;
+                    uint32_t ua[32], ub[32];
+                    tmem_ld32(lane_base + sl * BN, ua);
+                    tmem_ld32(lane_base + sl * BN + 32, ub);
+                    tmem_wait_ld();
+                    float sc[64];
 #pragma unroll
-                for (int c = 0; c < BN; ++c)
-                    if (c > lim) sc[c] = -INFINITY;
-            }
-            // three-input maximum: 32 instructions for 64 values, in four independent chains
-            float mx0 = fmaxf(sc[0], sc[1]), mx1 = fmaxf(sc[2], sc[3]), mx2 = fmaxf(sc[4], sc[5]), mx3 = fmaxf(sc[6], sc[7]);
-#pragma unroll
-            for (int c = 8; c < BN; c += 8) {
-                mx0 = fmax3(mx0, sc[c], sc[c + 1]);
-                mx1 = fmax3(mx1, sc[c + 2], sc[c + 3]);
-                mx2 = fmax3(mx2, sc[c + 4], sc[c + 5]);
-                mx3 = fmax3(mx3, sc[c + 6], sc[c + 7]);
-            }
-            const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * p.scale_log2;  // scale > 0: max commutes with it
-            // Lazy maximum: keep the old reference while the new maximum is within 2^8 of it.
-            const float m_new = fmaxf(m_used, mx);
-            const bool need = (m_new > m_used + 8.0f) || (m_used == -INFINITY && m_new != -INFINITY);
-            if (__any_sync(0xffffffffu, need)) {
-                const float m_next = need ? m_new : m_used;
-                const float alpha = (m_used == -INFINITY) ? 0.f : fast_exp2(m_used - m_next);
-                if (j > 0) {
-                    if (!warp_wait(bar(O_FULL), static_cast<uint32_t>((j - 1) & 1), give_up)) {
-                        ok = false;
-                        break;
+                    for (int c = 0; c < 32; ++c) {
+                        sc[c] = __uint_as_float(ua[c]);
+                        sc[c + 32] = __uint_as_float(ub[c]);
                     }
-                    tc_fence_after();
+                    if constexpr (kEdge) {
 #pragma unroll
-                    for (int c4 = 0; c4 < HD / 32; ++c4) {
-                        uint32_t o[32];
-                        tmem_ld32(lane_base + kColO + c4 * 32, o);
-                        tmem_wait_ld();
-#pragma unroll
-                        for (int c = 0; c < 32; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * alpha);
-                        tmem_st32(lane_base + kColO + c4 * 32, o);
+                        for (int c = 0; c < 64; ++c)
+                            if (c > lim) sc[c] = -INFINITY;
                     }
-                    tmem_wait_st();
-                }
-                l *= alpha;
-                m_used = m_next;
-            }
-            const float neg_m = (m_used == -INFINITY) ? 0.f : -m_used;
-            float rs0 = 0.f, rs1 = 0.f, rs2 = 0.f, rs3 = 0.f;
+                    float mx0 = fmaxf(sc[0], sc[1]), mx1 = fmaxf(sc[2], sc[3]), mx2 = fmaxf(sc[4], sc[5]), mx3 = fmaxf(sc[6], sc[7]);
 #pragma unroll
-            for (int c = 0; c < BN; c += 4) {
-                ffma2(sc[c], sc[c + 1], sc[c], sc[c + 1], p.scale_log2, neg_m);
-                ffma2(sc[c + 2], sc[c + 3], sc[c + 2], sc[c + 3], p.scale_log2, neg_m);
-                sc[c] = fast_exp2(sc[c]);
-                sc[c + 1] = fast_exp2(sc[c + 1]);
-                if (kPolyEvery > 0 && (c / 4) % (kPolyEvery > 0 ? kPolyEvery : 1) == 0) {
-                    poly_exp2_pair(sc[c + 2], sc[c + 3]);
-                } else {
-                    sc[c + 2] = fast_exp2(sc[c + 2]);
-                    sc[c + 3] = fast_exp2(sc[c + 3]);
-                }
-                fadd2(rs0, rs1, sc[c], sc[c + 1]);
-                fadd2(rs2, rs3, sc[c + 2], sc[c + 3]);
-            }
-            l += (rs0 + rs1) + (rs2 + rs3);
-            // P_j over the S cells this thread just consumed: cell c holds keys 2c (low half) and 2c + 1
-            uint32_t pk[32];
+                    for (int c = 8; c < 64; c += 8) {
+                        mx0 = fmax3(mx0, sc[c], sc[c + 1]);
+                        mx1 = fmax3(mx1, sc[c + 2], sc[c + 3]);
+                        mx2 = fmax3(mx2, sc[c + 4], sc[c + 5]);
+                        mx3 = fmax3(mx3, sc[c + 6], sc[c + 7]);
+                    }
+                    const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * p.scale_log2;  // scale > 0: max commutes with it
+                    // Lazy maximum: keep the old reference while the new maximum is within 2^8 of it.
+                    const float m_new = fmaxf(m_used, mx);
+                    const bool need = (m_new > m_used + 8.0f) || (m_used == -INFINITY && m_new != -INFINITY);
+                    if (__any_sync(0xffffffffu, need)) {
+                        const float m_next = need ? m_new : m_used;
+                        const float alpha = (m_used == -INFINITY) ? 0.f : fast_exp2(m_used - m_next);
+                        if (j > 0) {
+                            if (!warp_wait(bar(O_FULL + t), static_cast<uint32_t>((j - 1) & 1), give_up)) return false;
+                            tc_fence_after();
 #pragma unroll
-            for (int c = 0; c < 32; ++c) pk[c] = pack2<BF16>(sc[2 * c], sc[2 * c + 1]);
-            tmem_st32(lane_base + kColS0 + s * BN, pk);
+                            for (int c4 = 0; c4 < HD / 32; ++c4) {
+                                uint32_t o[32];
+                                tmem_ld32(lane_base + o_col + c4 * 32, o);
+                                tmem_wait_ld();
+#pragma unroll
+                                for (int c = 0; c < 32; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * alpha);
+                                tmem_st32(lane_base + o_col + c4 * 32, o);
+                            }
+                            tmem_wait_st();
+                        }
+                        l *= alpha;
+                        m_used = m_next;
+                    }
+                    const float neg_m = (m_used == -INFINITY) ? 0.f : -m_used;
+                    float rs0 = 0.f, rs1 = 0.f, rs2 = 0.f, rs3 = 0.f;
+                    if constexpr (kPolyEvery == 0) {
+                        // plain scalar form: one fma, one ex2, one add per score
+#pragma unroll
+                        for (int c = 0; c < 64; c += 4) {
+                            sc[c] = fast_exp2(fmaf(sc[c], p.scale_log2, neg_m));
+                            sc[c + 1] = fast_exp2(fmaf(sc[c + 1], p.scale_log2, neg_m));
+                            sc[c + 2] = fast_exp2(fmaf(sc[c + 2], p.scale_log2, neg_m));
+                            sc[c + 3] = fast_exp2(fmaf(sc[c + 3], p.scale_log2, neg_m));
+                            rs0 += sc[c];
+                            rs1 += sc[c + 1];
+                            rs2 += sc[c + 2];
+                            rs3 += sc[c + 3];
+                        }
+                    } else {
+#pragma unroll
+                        for (int c = 0; c < 64; c += 4) {
+                            ffma2(sc[c], sc[c + 1], sc[c], sc[c + 1], p.scale_log2, neg_m);
+                            ffma2(sc[c + 2], sc[c + 3], sc[c + 2], sc[c + 3], p.scale_log2, neg_m);
+                            sc[c] = fast_exp2(sc[c]);
+                            sc[c + 1] = fast_exp2(sc[c + 1]);
+                            if ((c / 4) % (kPolyEvery > 0 ? kPolyEvery : 1) == 0) {
+                                poly_exp2_pair(sc[c + 2], sc[c + 3]);
+                            } else {
+                                sc[c + 2] = fast_exp2(sc[c + 2]);
+                                sc[c + 3] = fast_exp2(sc[c + 3]);
+                            }
+                            fadd2(rs0, rs1, sc[c], sc[c + 1]);
+                            fadd2(rs2, rs3, sc[c + 2], sc[c + 3]);
+                        }
+                    }
+                    l += (rs0 + rs1) + (rs2 + rs3);
+                    uint32_t pk[32];
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) pk[c] = pack2<BF16>(sc[2 * c], sc[2 * c + 1]);   // cell c: keys 2c (low half) and 2c + 1
+                    tmem_st32(lane_base + sl * BN, pk);
+                    return true;
+                };
+                const bool fine = edge ? block64(std::true_type{}) : block64(std::false_type{});
+                if (!fine) {
+                    ok = false;
+                    break;
+                }
+            }
             tmem_wait_st();
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(bar(P_FULL));
+            if (lane == 0) mbar_arrive(bar(P_FULL + sl));
         }
-        // The last two P V products may both still be in flight here (a finished S_j only proves that P V of block
-        // j - 2 is done), and a parity wait can only tell neighbouring phases apart: wait for them one by one.
-        if (ok && nblk >= 2) ok = warp_wait(bar(O_FULL), static_cast<uint32_t>((nblk - 2) & 1), give_up);
-        if (ok && warp_wait(bar(O_FULL), static_cast<uint32_t>((nblk - 1) & 1), give_up)) {
+        // With two score buffers per tile the last two P V products may both still be in flight here (a finished S_j only
+        // proves that P V of block j - 2 is done), and a parity wait can only tell neighbouring phases apart: wait for them one by one.
+        if (ok && my_blocks >= 2) ok = warp_wait(bar(O_FULL + t), static_cast<uint32_t>((my_blocks - 2) & 1), give_up);
+        if (ok && my_blocks >= 1 && warp_wait(bar(O_FULL + t), static_cast<uint32_t>((my_blocks - 1) & 1), give_up)) {
             tc_fence_after();
             const float inv = l > 0.f ? 1.f / l : 0.f;
             const bool store = rr < L;
@@ -409,7 +505,7 @@ __global__ void __launch_bounds__(kThreads, 2) prefill_tc_kernel(const __grid_co
 #pragma unroll
             for (int c4 = 0; c4 < HD / 32; ++c4) {
                 uint32_t o[32];
-                tmem_ld32(lane_base + kColO + c4 * 32, o);
+                tmem_ld32(lane_base + o_col + c4 * 32, o);
                 tmem_wait_ld();
                 if (store) {
 #pragma unroll
@@ -458,10 +554,10 @@ EncodeFn encode_fn() {
 }
 
 // 3-D view [D, H, rows] of a packed [rows, H, D] tensor; box = 64 elements x 1 head x `box_rows` rows, 128-byte swizzle.
-bool make_map(CUtensorMap* map, const void* base, int64_t rows, int H, int64_t s0, int64_t s1, int box_rows, bool bf16) {
+bool make_map(CUtensorMap* map, const void* base, int D, int64_t rows, int H, int64_t s0, int64_t s1, int box_rows, bool bf16) {
     EncodeFn fn = encode_fn();
     if (!fn) return false;
-    const cuuint64_t dims[3] = {static_cast<cuuint64_t>(HD), static_cast<cuuint64_t>(H), static_cast<cuuint64_t>(rows)};
+    const cuuint64_t dims[3] = {static_cast<cuuint64_t>(D), static_cast<cuuint64_t>(H), static_cast<cuuint64_t>(rows)};
     const cuuint64_t strides[2] = {static_cast<cuuint64_t>(s1) * 2, static_cast<cuuint64_t>(s0) * 2};
     const cuuint32_t box[3] = {64, 1, static_cast<cuuint32_t>(box_rows)};
     const cuuint32_t estr[3] = {1, 1, 1};
@@ -470,24 +566,15 @@ bool make_map(CUtensorMap* map, const void* base, int64_t rows, int H, int64_t s
     return r == CUDA_SUCCESS;
 }
 
-}  // namespace
-
-void launch_prefill_tc(const PrefillArgs& a, int /*sm_count*/, int max_smem, cudaStream_t st, bool* taken) {
-    *taken = false;
-    if (a.force_simt) return;
-    if (a.dt != Dt::F16 && a.dt != Dt::BF16) return;
-    if (a.D != HD || a.H > 65535 || kSmemBytes > max_smem) return;
-    if (a.total_rows >= (1ll << 31) - BM) return;
-    auto ok = [](const void* p, int64_t s0, int64_t s1) {
-        return reinterpret_cast<uintptr_t>(p) % 16 == 0 && (s0 * 2) % 16 == 0 && (s1 * 2) % 16 == 0 && s0 > 0 && s1 > 0;
-    };
-    if (!ok(a.q, a.q_s0, a.q_s1) || !ok(a.kmat, a.k_s0, a.k_s1) || !ok(a.vmat, a.v_s0, a.v_s1) || !ok(a.out, a.o_s0, a.o_s1)) return;
+template <int HD, int BN, int NT, int kPolyEvery>
+bool launch_cfg(const PrefillArgs& a, int max_smem, cudaStream_t st) {
+    using C = Cfg<HD, BN, NT>;
+    if (C::kSmemBytes > max_smem) return false;
     const bool bf16 = a.dt == Dt::BF16;
     CUtensorMap mq, mk, mv;
-    if (!make_map(&mq, a.q, a.total_rows, a.H, a.q_s0, a.q_s1, BM, bf16)) return;
-    if (!make_map(&mk, a.kmat, a.total_rows, a.H / a.kv_group, a.k_s0, a.k_s1, BN, bf16)) return;
-    if (!make_map(&mv, a.vmat, a.total_rows, a.H / a.kv_group, a.v_s0, a.v_s1, BN, bf16)) return;
-
+    if (!make_map(&mq, a.q, HD, a.total_rows, a.H, a.q_s0, a.q_s1, BM, bf16)) return false;
+    if (!make_map(&mk, a.kmat, HD, a.total_rows, a.H / a.kv_group, a.k_s0, a.k_s1, BN, bf16)) return false;
+    if (!make_map(&mv, a.vmat, HD, a.total_rows, a.H / a.kv_group, a.v_s0, a.v_s1, BN, bf16)) return false;
     TcParams p;
     p.b_start = a.b_start;
     p.b_len = a.b_len;
@@ -497,32 +584,40 @@ void launch_prefill_tc(const PrefillArgs& a, int /*sm_count*/, int max_smem, cud
     p.out = a.out;
     p.o_s0 = a.o_s0;
     p.o_s1 = a.o_s1;
-    p.n_tiles_max = static_cast<int>(a.total_rows / BM + a.B);
+    p.n_groups_max = static_cast<int>(a.total_rows / (BM * NT) + a.B);
     p.scale_log2 = kLog2e / sqrtf(static_cast<float>(HD));
     p.status = nullptr;
     p.uniform_len = a.uniform_len;
     p.kv_group = a.kv_group;
-    dim3 grid(p.n_tiles_max, a.H, 1);
-    const int poly = kDefaultPolyEvery;
+    dim3 grid(p.n_groups_max, a.H, 1);
     auto go = [&](auto kern) {
-        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
-        kern<<<grid, kThreads, kSmemBytes, st>>>(mq, mk, mv, p);
-    };
-    auto pick = [&](auto bf) {
-        constexpr bool B = decltype(bf)::value;
-        switch (poly) {
-            case 1: go(prefill_tc_kernel<B, 1>); break;
-            case 2: go(prefill_tc_kernel<B, 2>); break;
-            case 4: go(prefill_tc_kernel<B, 4>); break;
-            case 8: go(prefill_tc_kernel<B, 8>); break;
-            default: go(prefill_tc_kernel<B, 0>); break;
-        }
+        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+        kern<<<grid, C::kThreads, C::kSmemBytes, st>>>(mq, mk, mv, p);
     };
     if (bf16)
-        pick(std::true_type{});
+        go(prefill_tc_kernel<true, HD, BN, NT, kPolyEvery>);
     else
-        pick(std::false_type{});
-    *taken = true;
+        go(prefill_tc_kernel<false, HD, BN, NT, kPolyEvery>);
+    return true;
+}
+
+}  // namespace
+
+void launch_prefill_tc(const PrefillArgs& a, int /*sm_count*/, int max_smem, cudaStream_t st, bool* taken) {
+    *taken = false;
+    if (a.force_simt) return;
+    if (a.dt != Dt::F16 && a.dt != Dt::BF16) return;
+    if ((a.D != 64 && a.D != 128 && a.D != 256) || a.H > 65535) return;
+    if (a.total_rows >= (1ll << 31) - 2 * BM) return;
+    auto ok = [](const void* p, int64_t s0, int64_t s1) {
+        return reinterpret_cast<uintptr_t>(p) % 16 == 0 && (s0 * 2) % 16 == 0 && (s1 * 2) % 16 == 0 && s0 > 0 && s1 > 0;
+    };
+    if (!ok(a.q, a.q_s0, a.q_s1) || !ok(a.kmat, a.k_s0, a.k_s1) || !ok(a.vmat, a.v_s0, a.v_s1) || !ok(a.out, a.o_s0, a.o_s1)) return;
+    switch (a.D) {
+        case 64: *taken = launch_cfg<64, 64, 2, kPolyEvery64>(a, max_smem, st); break;
+        case 128: *taken = launch_cfg<128, 64, 2, kPolyEvery128>(a, max_smem, st); break;
+        default: *taken = launch_cfg<256, 64, 1, kPolyEvery256>(a, max_smem, st); break;
+    }
 }
 
 }  // namespace k

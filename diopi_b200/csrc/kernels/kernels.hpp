@@ -175,7 +175,8 @@ struct PrefillArgs {
     int kv_group = 1;            // query heads per K/V head (grouped-query attention); k/v have H / kv_group heads
     bool force_simt = false;     // the SIMT kernel whatever the shape
 };
-void launch_prefill(const PrefillArgs& a, int sm_count, int max_smem, cudaStream_t st);
+// Returns the name of the kernel family that took the call ("tensor-core", "simt") or "none" for an empty problem.
+const char* launch_prefill(const PrefillArgs& a, int sm_count, int max_smem, cudaStream_t st);
 
 // ---- matmul + all-reduce over a tensor-parallel group --------------------------------------
 constexpr int kMaxGroupRanks = 8;

@@ -98,6 +98,22 @@ def test_refusals(F):
     assert F.matmul_all_reduce(a[:0], b, None, "solo").shape == (0, 64)
 
 
+def test_group_options(F):
+    from diopi_b200 import tp_group
+    from diopi_b200.runtime import DiopiError
+    tp_group.set_option("solo", "wait_limit_ms", 100)
+    tp_group.set_option("solo", "form", 2)          # a group of one has nobody to hand tiles to: runs as one-shot
+    x1, x2 = rand((64, 128), torch.float16, 31).cuda(), rand((128, 256), torch.float16, 32, 0.1).cuda()
+    got = F.matmul_all_reduce(x1, x2, None, "solo")
+    torch.testing.assert_close(got.cpu().float(), golden.matmul_all_reduce([x1.cpu()], [x2.cpu()]).float(), rtol=1e-2, atol=1e-2)
+    tp_group.set_option("solo", "form", 0)
+    tp_group.set_option("solo", "wait_limit_ms", 2000)
+    for option, value, msg in (("wait_limit_ms", 0, "between 1 and 600000"), ("form", 3, "form must be"), ("tile_width", 48, "tile_width must be"),
+                               ("colour", 1, "unknown group option")):
+        with pytest.raises(DiopiError, match=msg):
+            tp_group.set_option("solo", option, value)
+
+
 def run_ranks(world, what, extra=(), port=29617):
     """Runs tests/mar_ranks.py as one process per GPU; NVLS is switched off in NCCL, the kernels use plain peer stores."""
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1", "--master-port", str(port),

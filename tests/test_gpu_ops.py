@@ -757,6 +757,38 @@ def test_context_attention_ragged(F, dtype, H, D, lens):
     assert torch.equal(out2, out)
 
 
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("H,D", [(3, 64), (2, 128), (2, 256)])
+def test_context_attention_tensor_core_head_dims(F, capfd, dtype, H, D):
+    """Head dims 64, 128 and 256 (the reference's own config runs 64 and 256, diopi_configs.py:9339-9381) on the
+    tensor-core kernel: the log line proves which kernel took the call; requests that end inside a key block, inside
+    a row tile, inside the second tile of a pair, one of a single row and one of several hundred key blocks' worth."""
+    g = torch.Generator().manual_seed(D * 3 + H)
+    lens = [1, 130, 700, 257, 1029, 128, 256, 383]
+    total = sum(lens)
+    q, k, v = ((torch.randn(total, H, D, generator=g) / D ** 0.5 * 3).to(dtype) for _ in range(3))
+    lens_t = torch.tensor(lens, dtype=torch.int32)
+    st = torch.cat([torch.zeros(1, dtype=torch.int32), lens_t.cumsum(0)[:-1].to(torch.int32)])
+    want = golden.context_attention(q, k, v, torch.zeros(total, H, D), st, lens_t, max(lens), upcast=True)
+    out = torch.zeros(total, H, D, dtype=dtype, device="cuda")
+    F.set_option("log", 1)
+    try:
+        F.context_attention(q.cuda(), k.cuda(), v.cuda(), out, st.cuda(), lens_t.cuda(), max(lens))
+        torch.cuda.synchronize()
+    finally:
+        F.set_option("log", 0)
+    assert "tensor-core kernel" in capfd.readouterr().err
+    close(out, want, dtype)
+    # the SIMT kernel, which shares no code with it, agrees
+    F.set_option("prefill_simt", 1)
+    try:
+        simt = torch.zeros_like(out)
+        F.context_attention(q.cuda(), k.cuda(), v.cuda(), simt, st.cuda(), lens_t.cuda(), max(lens))
+    finally:
+        F.set_option("prefill_simt", 0)
+    close(out, simt.float().cpu(), dtype)
+
+
 def test_context_attention_cfg4_full_size(F):
     """The tensor-core prefill config at the size the benchmark runs it (8 requests of 1024..8192 rows, 32 heads,
     D 128, fp16). Whole (request, head) pairs are compared with the row-blocked oracle evaluated with fp32

@@ -196,3 +196,18 @@ def test_group_setup_validation(built_libs):
     assert impl.diopiB200GroupConnect(b"missing", buf) != 0
     assert b"no group named" in impl.diopiGetLastErrorString()
     assert impl.diopiB200GroupDestroy(b"missing") != 0
+
+
+def test_option_entry_points(F, built_libs):
+    """The switches are changed by name; unknown names and values out of range come back as errors with the known names."""
+    from diopi_b200 import tp_group
+    for name in ("log", "fuse_token_attention", "decode_plain", "prefill_simt"):
+        F.set_option(name, 1)
+        F.set_option(name, 0)
+    with pytest.raises(DiopiError, match="unknown option 'warp_speed'.*known: log"):
+        F.set_option("warp_speed", 1)
+    rc = built_libs.impl.diopiB200SetOption(None, 1)
+    assert rc == ERROR_OCCURRED
+    # group options: refused for a group that does not exist (creating one needs a device)
+    with pytest.raises(DiopiError, match="no group named 'ghost'"):
+        tp_group.set_option("ghost", "wait_limit_ms", 50)
