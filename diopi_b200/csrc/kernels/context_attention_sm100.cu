@@ -491,12 +491,18 @@ __global__ void __launch_bounds__(Cfg<HD, BN, NT>::kThreads, 1)
             }
             tmem_wait_st();
             tc_fence_before();
+            // A parity wait tells n finished products from n + 1, not from n + 2. Inside the loop that is enough: at the
+            // start of block j between j - 1 and j products of this tile are finished (Q K_j^T needed the buffer P V_{j-2}
+            // read; P V_j is not issued yet). After the last hand-over it would not be (n - 2, n - 1 or n): so the last
+            // block sees P V_{n-2} finished before it hands P over, which leaves n - 1 or n for the wait after the loop.
+            if (j > 0 && j == my_blocks - 1 && !warp_wait(bar(O_FULL + t), static_cast<uint32_t>((j - 1) & 1), give_up)) {
+                ok = false;
+                break;
+            }
             __syncwarp();
             if (lane == 0) mbar_arrive(bar(P_FULL + sl));
         }
-        // With two score buffers per tile the last two P V products may both still be in flight here (a finished S_j only
-        // proves that P V of block j - 2 is done), and a parity wait can only tell neighbouring phases apart: wait for them one by one.
-        if (ok && my_blocks >= 2) ok = warp_wait(bar(O_FULL + t), static_cast<uint32_t>((my_blocks - 2) & 1), give_up);
+        // All products but the last are known to be finished (see the loop): one wait for the last one.
         if (ok && my_blocks >= 1 && warp_wait(bar(O_FULL + t), static_cast<uint32_t>((my_blocks - 1) & 1), give_up)) {
             tc_fence_after();
             const float inv = l > 0.f ? 1.f / l : 0.f;
