@@ -198,6 +198,7 @@ struct MatmulAllReduceArgs {
     unsigned char* peer_result[kMaxGroupRanks];  // finished-tile area of every rank (two-shot form)
     bool two_shot;            // partials to the tile's owner only, finished tiles handed round
     int force_tile_width;     // 0: the launch picks; 128, 64 or (K-major x2 only) 32: this width
+    int k_splits;             // set by the launch: CTAs that share one output tile, each with a slice of K (groups of one only)
     int* status;
 };
 int matmul_allreduce_tiles(int64_t M, int64_t N);

@@ -138,6 +138,12 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_allreduce_kernel(const __g
     const int tiles_n = (a.N + TN - 1) / TN;
     const int n_tiles = ((a.M + TM - 1) / TM) * tiles_n;
     const int kblocks = (a.K + TK - 1) / TK;
+    // Split-K (groups of one rank only): S CTAs share an output tile, each with a slice of the k blocks; the slices meet in
+    // the staging area like the partials of S ranks would. Virtual tile vt = tile * S + slice; S = 1 is the plain form.
+    const int S = a.k_splits > 1 ? a.k_splits : 1;
+    const int n_vt = n_tiles * S;
+    const int W = a.world * S;            // sources of partial rows per tile
+    const int mt = a.max_tiles / S;       // tiles the staging area holds when every rank brings S sources
     // The call's sequence number lives in device memory (the number of calls this group has finished, plus one) and is
     // advanced by the last CTA to leave: the host passes nothing that changes from call to call, so a captured launch
     // can be replayed. Every CTA reads it here, before any CTA of this launch can have left.
@@ -182,9 +188,11 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_allreduce_kernel(const __g
         // ================================ TMA producer =================================
         if (lane == 0) {
             int it = 0;  // ring position, counted over all tiles of this CTA
-            for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+            for (int vt = blockIdx.x; vt < n_vt; vt += gridDim.x) {
+                const int tile = vt / S, slice = vt - tile * S;
                 const int m0 = (tile / tiles_n) * TM, n0 = (tile % tiles_n) * TN;
-                for (int kb = 0; kb < kblocks; ++kb, ++it) {
+                const int kb0 = slice * kblocks / S, kb1 = (slice + 1) * kblocks / S;
+                for (int kb = kb0; kb < kb1; ++kb, ++it) {
                     const int s = it % kStages;
                     const uint32_t ph = static_cast<uint32_t>((it / kStages) & 1);
                     if (!mbar_wait(bar(EMPTY + s), ph ^ 1u, give_up, pipe_limit)) goto producer_done;
@@ -207,12 +215,14 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_allreduce_kernel(const __g
         if (lane == 0) {
             const uint32_t idesc = make_idesc(TM, TN, BF16 ? 1 : 0, B_KMAJOR ? 0 : 1);
             int it = 0, nt = 0;
-            for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++nt) {
+            for (int vt = blockIdx.x; vt < n_vt; vt += gridDim.x, ++nt) {
+                const int slice = vt % S;
+                const int kb0 = slice * kblocks / S, kb1 = (slice + 1) * kblocks / S;
                 const int acc = nt & 1;
                 if (!mbar_wait(bar(ACC_EMPTY + acc), static_cast<uint32_t>(((nt >> 1) & 1) ^ 1), give_up, pipe_limit)) break;
                 tc_fence_after();
                 bool ok = true;
-                for (int kb = 0; kb < kblocks; ++kb, ++it) {
+                for (int kb = kb0; kb < kb1; ++kb, ++it) {
                     const int s = it % kStages;
                     if (!mbar_wait(bar(FULL + s), static_cast<uint32_t>((it / kStages) & 1), give_up, pipe_limit)) {
                         ok = false;
@@ -225,7 +235,7 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_allreduce_kernel(const __g
                         const uint64_t ad = make_desc(a_addr + t * 32, 0, 1024);   // K-major: 16 k = 32 bytes inside the swizzled row
                         const uint64_t bd = B_KMAJOR ? make_desc(b_addr + t * 32, 0, 1024)
                                                      : make_desc(b_addr + t * 16 * 128, TK * 128, 1024);  // MN-major: 16 k = 16 rows; next 64 columns 8 KB on
-                        umma(tmem_base + acc * kTileCap, ad, bd, idesc, (kb > 0 || t > 0) ? 1u : 0u);
+                        umma(tmem_base + acc * kTileCap, ad, bd, idesc, (kb > kb0 || t > 0) ? 1u : 0u);
                     }
                     umma_commit(bar(EMPTY + s));
                 }
@@ -243,7 +253,8 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_allreduce_kernel(const __g
         bool ok = true;
         int nt = 0;
         // ---- first pass: every tile of this CTA, product -> partial rows into the staging areas -----------------------
-        for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x, ++nt) {
+        for (int vt = blockIdx.x; ok && vt < n_vt; vt += gridDim.x, ++nt) {
+            const int tile = vt / S, slice = vt - tile * S;
             const int acc = nt & 1;
             const int m0 = (tile / tiles_n) * TM, n0 = (tile % tiles_n) * TN;
             if (!warp_wait(bar(ACC_FULL + acc), static_cast<uint32_t>((nt >> 1) & 1), give_up, pipe_limit)) {
@@ -268,7 +279,7 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_allreduce_kernel(const __g
             // whole rows now: a lane owns columns 4 cl .. 4 cl + 3 of the rows sub, sub + RPI, ... of this warp's slab
             const int col = n0 + 4 * cl;
             float4 bias4 = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (a.bias != nullptr && col < a.N) {
+            if (a.bias != nullptr && col < a.N && slice == 0) {   // the bias once per rank: with the first slice of K
                 if (BF16) {
                     const __nv_bfloat16* b = static_cast<const __nv_bfloat16*>(a.bias) + col;
                     bias4 = make_float4(__bfloat162float(b[0]), __bfloat162float(b[1]), __bfloat162float(b[2]), __bfloat162float(b[3]));
@@ -278,7 +289,7 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_allreduce_kernel(const __g
                 }
             }
             const int rows_here = min(32, a.M - (m0 + quarter * 32));   // rows of this warp's slab that exist
-            const size_t slot = partial_slot<TN>(buf, a.world, a.rank, a.max_tiles, tile);
+            const size_t slot = partial_slot<TN>(buf, W, a.rank * S + slice, mt, tile);
             const int owner = tile % a.world;
             if (col < a.N) {
                 for (int rr = sub; rr < rows_here; rr += RPI) {
@@ -307,7 +318,9 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_allreduce_kernel(const __g
         // list is row q + 4 e, and one warp-wide access covers RPI consecutive entries.
         const unsigned char* my_stage = a.peer_stage[a.rank];
         constexpr int RB = 8;   // accesses in flight per warp
-        for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x) {
+        for (int vt = blockIdx.x; ok && vt < n_vt; vt += gridDim.x) {
+            const int tile = vt / S;
+            if (vt - tile * S != 0) continue;   // the CTA with the first slice of a tile adds the sources up
             if (a.two_shot && tile % a.world != a.rank) continue;
             const int m0 = (tile / tiles_n) * TM, n0 = (tile % tiles_n) * TN;
             const int col = n0 + 4 * cl;
@@ -316,8 +329,8 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_allreduce_kernel(const __g
                 float4 sum[RB];
 #pragma unroll
                 for (int i = 0; i < RB; ++i) sum[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-                for (int r = 0; ok && r < a.world; ++r) {
-                    const unsigned char* src = my_stage + partial_slot<TN>(buf, a.world, r, a.max_tiles, tile) + 16 * cl;
+                for (int r = 0; ok && r < W; ++r) {
+                    const unsigned char* src = my_stage + partial_slot<TN>(buf, W, r, mt, tile) + 16 * cl;
                     uint32_t w[RB][4];
                     unsigned long long t0 = 0;
                     for (;;) {   // until every word of the batch carries this call's number
@@ -512,25 +525,40 @@ const char* launch_matmul_allreduce(const MatmulAllReduceArgs& a, int sm_count, 
         const int f = a.force_tile_width;
         if (f == 128 || f == 64 || (f == 32 && a.x2_kmajor)) tn = f;
     }
-    const int am = (tn < 128 && a.M <= 64) ? 64 : 128;   // rows of x1 a ring stage holds
+    // Split-K, for a group of one rank (a plain product) whose output has too few 128-wide tiles for the SMs: instead of
+    // narrower tiles (every CTA then re-reads all of x1 from L2: 128 CTAs x 512 KB at M 64, K 4096) several CTAs share a
+    // 128-wide tile and a slice of K each; the slices are added in the staging area like the partials of ranks.
+    int splits = 1;
+    if (a.world == 1 && a.force_tile_width == 0) {
+        const int64_t tiles128 = row_tiles * ((a.N + 127) / 128);
+        const int64_t kblocks = (a.K + TK - 1) / TK;
+        int64_t sp = std::min<int64_t>(std::min<int64_t>(sm_count / std::max<int64_t>(tiles128, 1), kblocks / 4), std::min<int64_t>(a.max_tiles / std::max<int64_t>(tiles128, 1), 8));
+        if (tiles128 * 2 <= sm_count && sp >= 2) {
+            splits = static_cast<int>(sp);
+            tn = 128;
+        }
+    }
+    const int am = ((tn < 128 || splits > 1) && a.M <= 64) ? 64 : 128;   // rows of x1 a ring stage holds
     CUtensorMap ma, mb;
     if (!make_map_2d(&ma, a.x1, a.K, a.M, a.x1_ld, am, bf16)) return "cuTensorMapEncodeTiled failed for x1";
     const bool okb = a.x2_kmajor ? make_map_2d(&mb, a.x2, a.K, a.N, a.x2_ld, tn, bf16) : make_map_2d(&mb, a.x2, a.N, a.K, a.x2_ld, TK, bf16);
     if (!okb) return "cuTensorMapEncodeTiled failed for x2";
     const int n_tiles = static_cast<int>(row_tiles * ((a.N + tn - 1) / tn));
-    const int grid = std::min(n_tiles, sm_count);
+    const int grid = std::min(n_tiles * splits, sm_count);
+    MatmulAllReduceArgs b = a;
+    b.k_splits = splits;
     auto go = [&](auto kern) {
         cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
-        kern<<<grid, kThreads, kSmemBytes, st>>>(ma, mb, a);
+        kern<<<grid, kThreads, kSmemBytes, st>>>(ma, mb, b);
     };
     auto pick = [&](auto bf) {
         constexpr bool B = decltype(bf)::value;
         if (a.x2_kmajor) {
-            if (tn == 128) go(matmul_allreduce_kernel<B, true, 128, 128>);
+            if (tn == 128) { if (am == 64) go(matmul_allreduce_kernel<B, true, 128, 64>); else go(matmul_allreduce_kernel<B, true, 128, 128>); }
             else if (tn == 64) { if (am == 64) go(matmul_allreduce_kernel<B, true, 64, 64>); else go(matmul_allreduce_kernel<B, true, 64, 128>); }
             else { if (am == 64) go(matmul_allreduce_kernel<B, true, 32, 64>); else go(matmul_allreduce_kernel<B, true, 32, 128>); }
         } else {
-            if (tn == 128) go(matmul_allreduce_kernel<B, false, 128, 128>);
+            if (tn == 128) { if (am == 64) go(matmul_allreduce_kernel<B, false, 128, 64>); else go(matmul_allreduce_kernel<B, false, 128, 128>); }
             else if (am == 64) go(matmul_allreduce_kernel<B, false, 64, 64>);
             else go(matmul_allreduce_kernel<B, false, 64, 128>);
         }

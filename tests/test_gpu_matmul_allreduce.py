@@ -98,6 +98,33 @@ def test_refusals(F):
     assert F.matmul_all_reduce(a[:0], b, None, "solo").shape == (0, 64)
 
 
+@pytest.mark.parametrize("kmajor", [False, True])
+@pytest.mark.parametrize("shape", [(64, 4096, 4096), (17, 1000, 2048), (64, 520, 640), (128, 2048, 1024)])
+def test_split_k_in_a_group_of_one(F, shape, kmajor):
+    """A group of one rank whose output has few 128-wide tiles splits K over several CTAs per tile (up to 8 slices, here
+    4, 4, 2 and 4); the slices are added in the staging area. Ragged K (the last 64-wide k block partly beyond the
+    matrix), bias added once, both layouts of x2, and two calls in a row (both halves of the staging area)."""
+    from diopi_b200 import tp_group
+    M, K, N = shape
+    tp_group.create("wide", max_tiles=256, rank=0, world=1)
+    try:
+        x1, b = rand((M, K), torch.bfloat16, 40 + M), rand((N,), torch.bfloat16, 41)
+        w = rand((N, K), torch.bfloat16, 42 + N, K ** -0.5)
+        x2 = w.t() if kmajor else w.t().contiguous()
+        want = golden.matmul_all_reduce([x1], [x2], [b])
+        x2d = w.cuda().t() if kmajor else x2.cuda()
+        got = F.matmul_all_reduce(x1.cuda(), x2d, b.cuda(), "wide")
+        torch.testing.assert_close(got.cpu().float(), want.float(), rtol=1e-2, atol=1e-2)
+        again = F.matmul_all_reduce(x1.cuda(), x2d, b.cuda(), "wide")
+        assert torch.equal(again, got)
+        # the narrow-tile form without split-K (forced tile width) gives the same numbers to rounding
+        tp_group.set_option("wide", "tile_width", 64)
+        narrow = F.matmul_all_reduce(x1.cuda(), x2d, b.cuda(), "wide")
+        torch.testing.assert_close(narrow.float(), got.float(), rtol=1e-2, atol=1e-2)
+    finally:
+        tp_group.destroy("wide")
+
+
 def test_group_options(F):
     from diopi_b200 import tp_group
     from diopi_b200.runtime import DiopiError
