@@ -320,7 +320,7 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_allreduce_kernel(const __g
         constexpr int RB = 8;   // accesses in flight per warp
         for (int vt = blockIdx.x; ok && vt < n_vt; vt += gridDim.x) {
             const int tile = vt / S;
-            if (vt - tile * S != 0) continue;   // the CTA with the first slice of a tile adds the sources up
+            if (vt - tile * S != 0) continue;   // the CTA with the first slice of a tile adds the sources up (sharing the adding among the S CTAs measured no faster)
             if (a.two_shot && tile % a.world != a.rank) continue;
             const int m0 = (tile / tiles_n) * TM, n0 = (tile % tiles_n) * TN;
             const int col = n0 + 4 * cl;

@@ -73,7 +73,8 @@ def main():
     dtype = torch.bfloat16 if args.dtype == "bf16" else torch.float16
     M, N, K = args.rows, args.cols, args.k_total // world
     tiles = ((M + 127) // 128) * ((N + 127) // 128)
-    tp_group.create("tp", max_tiles=tiles)
+    # a group of one may split K over up to eight CTAs per tile when its staging area has room for the slices
+    tp_group.create("tp", max_tiles=tiles * 8 if world == 1 else tiles)
     tp_group.set_option("tp", "form", args.form)
     ctx = Context()
     x1, x2, bias = inputs(rank, M, K, N, dtype, "cuda")
