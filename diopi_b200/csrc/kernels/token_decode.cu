@@ -789,7 +789,7 @@ cudaError_t static_scratch_address(void** out) {
 }  // namespace
 
 // Grouped K/V heads (kv_group query heads read one K/V head) whose shape the single-pass kernel of token_decode_gqa.cu
-// does not take (fp32, head dims other than 64 and 128, groups wider than 16): the call is run as kv_group passes,
+// does not take (fp32, head dims other than 64 and 128, groups wider than 128): the call is run as kv_group passes,
 // pass s taking query head s of every group. Each pass is an ordinary problem with as many query heads as K/V heads
 // (q and out are addressed with the group's stride), so the streaming kernel serves it unchanged. The K/V rows are
 // read once per pass; the plain kernel, which reads them once per query head with one CTA per (request, head),

@@ -12,13 +12,15 @@
 // accumulator fragment of S is the A fragment of the second product. Tried and dropped: blocks of 8 tokens (m16n8k8 for the
 // second product, six 33 KB stages instead of three 66 KB ones): 107 us where this form takes 97 us on 64 query heads
 // over 8 K/V heads, the per-stage hand-over costs more than the shorter chain wins; a 128-register cap, so that the
-// merge kernel's CTAs become resident beside this kernel's: 101 us.
+// merge kernel's CTAs become resident beside this kernel's: 101 us; separate accumulators for even and odd k steps of
+// Q K^T (shorter dependent chains): no change. Per stage the kernel pays about 0.24 us of hand-over on top of the bytes.
 //
 // Work split: the flattened (request, token) pairs are cut into equal ranges, one per CTA (as in token_decode.cu).
 // Per CTA four producer warps look up slots and issue one bulk copy per row part (the K/V heads of this CTA:
 // hg * D * 2 bytes) into a ring of shared-memory stages; rows are stored with a pitch of row bytes + 16, so that the
-// eight rows an ldmatrix reads fall into different banks. Eight consumer warps: warp = (token block g, K/V head hl);
-// a stage holds G = 8 / hg blocks of 16 tokens. Every consumer warp keeps (m, l, O) of its (head, token block) in
+// eight rows an ldmatrix reads fall into different banks. Eight consumer warps: warp = (token block g, M tile, K/V head hl),
+// one M tile of 16 query heads for groups up to 16 and 2, 4 or 8 tiles for groups up to 128 (they read the same rows in
+// shared memory); a stage holds G = 8 / (hg * M tiles) blocks of 16 tokens. Every consumer warp keeps (m, l, O) of its (head, token block) in
 // registers; at the end of a request's part the G token blocks are merged through shared memory and one partial per
 // (CTA, request, query head) goes to scratch, in the layout decode_combine_kernel reads.
 //
@@ -43,7 +45,8 @@ constexpr int kBlockTokens = 16;   // tokens one warp step covers: the K extent 
 struct GqaPlan {
     int hg;           // K/V heads per CTA (1, 2, 4 or 8)
     int n_hg;         // CTAs along the head axis
-    int G;            // token blocks per stage = consumer warps / hg
+    int MT;           // M tiles of 16 query heads per group: 1 for groups up to 16, 2, 4 or 8 for wider ones
+    int G;            // token blocks per stage = consumer warps / (hg * MT)
     int TT;           // tokens per stage = 16 * G
     int pitch;        // bytes between rows of a stage: hg * D * 2 + 16
     int stage_bytes;  // K rows then V rows: 2 * TT * pitch
@@ -51,7 +54,7 @@ struct GqaPlan {
     int n_cta;        // CTAs along the flattened token axis
     int smem_bytes;
     int off_bars, off_pre, off_red, off_flag;
-    int red_floats_per_warp;   // kv_group * (D + 2)
+    int red_floats_per_warp;   // rows a warp holds (kv_group, at most 16) * (D + 2)
 };
 
 __device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t (&r)[4]) {
@@ -215,11 +218,13 @@ __global__ void __launch_bounds__(kGqaThreads, 1) decode_gqa_kernel(const Decode
         }
     } else {
         // =========================== consumer warps ==============================
-        const int hl = warp % p.hg;        // K/V head inside this CTA's group
-        const int g = warp / p.hg;         // token block inside a stage
+        const int hl = warp % p.hg;                 // K/V head inside this CTA's group
+        const int mtile = (warp / p.hg) % p.MT;     // which 16 query heads of the group (groups wider than 16)
+        const int g = warp / (p.hg * p.MT);         // token block inside a stage
         const bool active = hl < heads_here;
         const int hkv = hg0 + hl;
-        const int r0 = lane >> 2;          // the two accumulator rows (query heads of the group) this thread holds
+        const int rb = mtile * 16;                  // first query head of this warp's M tile
+        const int r0 = rb + (lane >> 2);            // the two accumulator rows (query heads of the group) this thread holds
         const int r1 = r0 + 8;
         const int cq = (lane & 3) * 2;     // first of its two accumulator columns inside an 8-wide tile
         const float scale_log2 = kLog2e / sqrtf(static_cast<float>(HD));
@@ -383,7 +388,7 @@ __global__ void __launch_bounds__(kGqaThreads, 1) decode_gqa_kernel(const Decode
                         for (int half = 0; half < 2; ++half) {
                             const int r = half ? r1 : r0;
                             if (r < R) {
-                                float* dst = mine + r * (HD + 2);
+                                float* dst = mine + (r - rb) * (HD + 2);
                                 if ((lane & 3) == 0) {
                                     dst[0] = half ? m1 : m0;
                                     dst[1] = half ? l1 : l0;
@@ -396,18 +401,21 @@ __global__ void __launch_bounds__(kGqaThreads, 1) decode_gqa_kernel(const Decode
                     __syncwarp();
                     if (lane == 0) mbar_arrive(smem_u32(&bars[2 * p.nstages]));
                     if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&bars[2 * p.nstages]), red_phase, give_up) ? 1 : 0)) break;
-                    // warp (g, hl) merges rows g, g + G, ... of head hl over the G token blocks; a lane owns 4 columns (HD = 128) or 2 (HD = 64)
+                    // warp (g, M tile, hl) merges rows g, g + G, ... of its M tile over the G token blocks; a lane owns 4 columns (HD = 128) or 2 (HD = 64)
                     if (active) {
                         constexpr int CPL = HD / 32;   // columns per lane
-                        for (int r = g; r < R; r += p.G) {
+                        const int rows_here = min(16, R - rb);
+                        for (int rl = g; rl < rows_here; rl += p.G) {
+                            const int r = rb + rl;
                             float M = -INFINITY;
-                            for (int gg = 0; gg < p.G; ++gg) M = fmaxf(M, red[static_cast<size_t>(gg * p.hg + hl) * p.red_floats_per_warp + r * (HD + 2)]);
+                            for (int gg = 0; gg < p.G; ++gg)
+                                M = fmaxf(M, red[static_cast<size_t>((gg * p.MT + mtile) * p.hg + hl) * p.red_floats_per_warp + rl * (HD + 2)]);
                             const float Mr = (M == -INFINITY) ? 0.f : M;
                             float L = 0.f, acc[CPL];
 #pragma unroll
                             for (int e = 0; e < CPL; ++e) acc[e] = 0.f;
                             for (int gg = 0; gg < p.G; ++gg) {
-                                const float* src = red + static_cast<size_t>(gg * p.hg + hl) * p.red_floats_per_warp + r * (HD + 2);
+                                const float* src = red + static_cast<size_t>((gg * p.MT + mtile) * p.hg + hl) * p.red_floats_per_warp + rl * (HD + 2);
                                 const float w = exp2f(src[0] - Mr);   // a block that saw no token left m = -inf, l = 0, O = 0
                                 L = fmaf(src[1], w, L);
 #pragma unroll
@@ -441,7 +449,7 @@ __global__ void __launch_bounds__(kGqaThreads, 1) decode_gqa_kernel(const Decode
 bool make_gqa_plan(const DecodeArgs& a, int sm_count, int max_smem, GqaPlan& p) {
     if (a.force_plain || a.mode != DecodeMode::FUSED) return false;
     if (a.dt != Dt::F16 && a.dt != Dt::BF16) return false;
-    if (a.kv_group < 2 || a.kv_group > 16 || a.H % a.kv_group != 0) return false;
+    if (a.kv_group < 2 || a.kv_group > 128 || a.H % a.kv_group != 0) return false;
     if (a.D != 64 && a.D != 128) return false;
     if (a.B > kGqaMaxB || a.B <= 0) return false;
     if (static_cast<int64_t>(a.B) * a.max_input_len >= (1ll << 31)) return false;
@@ -453,15 +461,18 @@ bool make_gqa_plan(const DecodeArgs& a, int sm_count, int max_smem, GqaPlan& p) 
     // q is read with 32-bit loads
     if (a.q_s2 != 1 || a.q_s0 % 2 != 0 || a.q_s1 % 2 != 0 || reinterpret_cast<uintptr_t>(a.q) % 4 != 0) return false;
 
+    int mt = 1;
+    while (mt * 16 < a.kv_group) mt *= 2;   // 1, 2, 4 or 8 tiles of 16 query heads
+    p.MT = mt;
     int hg = 1;
-    while (hg * 2 <= std::min(Hkv, kGqaConsumerWarps)) hg *= 2;
+    while (hg * 2 <= std::min(Hkv, kGqaConsumerWarps / mt)) hg *= 2;
     p.hg = hg;
     p.n_hg = (Hkv + hg - 1) / hg;
-    p.G = kGqaConsumerWarps / hg;
+    p.G = kGqaConsumerWarps / (hg * mt);
     p.TT = kBlockTokens * p.G;
     p.pitch = hg * a.D * 2 + 16;
     p.stage_bytes = 2 * p.TT * p.pitch;
-    p.red_floats_per_warp = a.kv_group * (a.D + 2);
+    p.red_floats_per_warp = std::min(a.kv_group, 16) * (a.D + 2);
     const int red_bytes = p.G > 1 ? kGqaConsumerWarps * p.red_floats_per_warp * 4 : 0;
     int off = 0;
     auto take = [&](int bytes, int align) {

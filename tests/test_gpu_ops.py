@@ -889,11 +889,13 @@ def test_paged_attention_batches(F, dtype, heads, kv_heads, dim, block):
 # ------------------------------------------------------------------ grouped K/V heads: the single-pass kernel
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
 @pytest.mark.parametrize("heads,kv_heads,dim,block", [(16, 8, 128, 16), (32, 8, 128, 16), (64, 8, 128, 16), (16, 1, 128, 16), (12, 3, 128, 8), (40, 5, 64, 32),
-                                                      (32, 2, 64, 16), (24, 12, 128, 16), (7, 1, 64, 4), (48, 16, 128, 128)])
+                                                      (32, 2, 64, 16), (24, 12, 128, 16), (7, 1, 64, 4), (48, 16, 128, 128),
+                                                      (64, 2, 128, 16), (64, 1, 128, 16), (48, 2, 64, 16), (40, 1, 128, 8), (96, 3, 64, 16), (128, 1, 128, 16)])
 def test_paged_attention_grouped_heads(F, dtype, heads, kv_heads, dim, block):
-    """Query-head groups of 2 to 16 over 1 to 16 K/V heads (powers of two and not), head dims 64 and 128: every
-    shape of the tensor-core kernel (K/V heads per CTA 1, 2, 4, 8; 8 to 1 token blocks per stage; a second CTA row
-    for the heads beyond eight), with request lengths that leave ragged last blocks, an empty and a one-token request."""
+    """Query-head groups of 2 to 128 over 1 to 16 K/V heads (powers of two and not), head dims 64 and 128: every
+    shape of the tensor-core kernel (K/V heads per CTA 1, 2, 4, 8; 1, 2, 4 or 8 tiles of 16 query heads per group;
+    8 to 1 token blocks per stage; a second CTA row for the heads beyond eight), with request lengths that leave
+    ragged last blocks, an empty and a one-token request."""
     g = torch.Generator().manual_seed(heads * 131 + kv_heads * 7 + dim)
     lens = [1, 700, 0, 129, 16, 17, 333, 15, 1024, 31]
     B = len(lens)
