@@ -88,9 +88,11 @@ __global__ void __launch_bounds__(THREADS, (THREADS * VPT * Vec16<T>::N <= 4096 
         c = warp_sum_f(c);
         if (lane == 0) s_part[buf][warp] = c;
         __syncthreads();
-        float tot = 0.f;
+        // every warp adds the W partials in the same fixed order: one shared-memory load per lane and a butterfly,
+        // instead of W loads and adds per thread
+        float tot = lane < W ? s_part[buf][lane] : 0.f;
 #pragma unroll
-        for (int w = 0; w < W; ++w) tot += s_part[buf][w];
+        for (int o = 16; o > 0; o >>= 1) tot += __shfl_xor_sync(0xffffffffu, tot, o);
         buf ^= 1;  // the next row writes the other half: no second barrier per row
         const float coef = tot * inv_n2 * inv * inv * inv;
         uint4* o4 = reinterpret_cast<uint4*>(static_cast<T*>(a.dx) + row * a.n2);
