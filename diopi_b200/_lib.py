@@ -45,6 +45,7 @@ OPS = {
     "diopiRMSNorm": [c_void_p, c_void_p, c_void_p, diopiSize_t, c_void_p, c_void_p, c_double],
     "diopiRotaryEmbeddingCopyKV": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_bool],
     "diopiMatmulAllReduce": [c_void_p, c_void_p, c_void_p, c_void_p, c_char_p, c_char_p, c_int64, c_int64],
+    "diopiB200ContextRelease": [],
     "diopiRMSNormBackward": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, diopiSize_t, c_double],
 }
 INFO = ["diopiGetVendorName", "diopiGetImplVersion", "diopiGetLastErrorString"]

@@ -190,6 +190,17 @@ B200_EXPORT const char* diopiGetImplVersion() {
 }
 B200_EXPORT const char* diopiGetLastErrorString() { return last_error_cstr(); }
 
+// Extension: forget a context. With the fuse_token_attention switch on, diopiTokenAttentionInference may have recorded a
+// call on this context instead of launching it; the record holds raw tensor pointers and is keyed by the context handle.
+// This launches the recorded kernel (the logits get written) and drops the record, so that a context created later at
+// the same address cannot inherit it. Call it before destroying a context on which the pair of decode calls was used.
+B200_EXPORT diopiError_t diopiB200ContextRelease(diopiContextHandle_t ctx) {
+    return guard("diopiB200ContextRelease", [&] {
+        B200_REQUIRE(ctx != nullptr, "null context handle");
+        flush_pending(ctx);
+    });
+}
+
 // Extension: changes one of the process-wide switches of common.hpp (the environment gives only their start values).
 B200_EXPORT diopiError_t diopiB200SetOption(const char* name, int64_t value) {
     return guard("diopiB200SetOption", [&] {

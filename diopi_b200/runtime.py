@@ -110,6 +110,10 @@ class Context:
     def __del__(self):
         h, self.handle = getattr(self, "handle", None), None
         if h:
+            try:   # the backend may hold a recorded call for this handle (opt-in pair fusion): let it go first
+                _lib.load().impl.diopiB200ContextRelease(h)
+            except Exception:  # noqa: BLE001
+                pass
             self._rt.b200rt_context_destroy(h)
 
 

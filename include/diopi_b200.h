@@ -263,6 +263,12 @@ diopiError_t diopiB200GroupDestroy(const char* group);
  *   "tile_width"     0 chosen per call, or 128 / 64 / 32 output columns per tile. Must be the same on every rank. */
 diopiError_t diopiB200GroupSetOption(const char* group, const char* option, int64_t value);
 
+/* Forget a context: launches a decode-logits call that the fuse_token_attention switch has recorded on `ctx` (instead of
+ * launching it) and drops the record, which holds raw tensor pointers keyed by the context handle. Call it before a
+ * context on which diopiTokenAttentionInference ran with that switch on is destroyed; a no-op otherwise. No counterpart
+ * in the reference. */
+diopiError_t diopiB200ContextRelease(diopiContextHandle_t ctx);
+
 /* Process-wide switches; no counterpart in the reference. Each starts from an environment variable read once
  * (DIOPI_B200_LOG, DIOPI_B200_FUSE_TOKEN_ATTENTION, DIOPI_B200_DECODE_PLAIN, DIOPI_B200_PREFILL_SIMT) and is changed
  * here by name: "log", "fuse_token_attention", "decode_plain", "prefill_simt"; value 0 switches off, non-zero on. */

@@ -409,6 +409,35 @@ def test_token_attention_pair_runs_fused_when_asked(F, monkeypatch):
     assert torch.equal(att2, plain_att)
 
 
+def test_context_release_flushes_a_recorded_call(F):
+    """With the pair fusion on, the logits call is only recorded; releasing the context launches it and drops the
+    record, so that nothing stale is left behind for a context created later at the same address."""
+    from diopi_b200 import _lib
+    from diopi_b200.runtime import Context
+    c = make_decode_case(3, 8, 128, torch.float16, [40, 9, 200], seed=5)
+    d = {k: (v.cuda() if isinstance(v, torch.Tensor) else v) for k, v in c.items()}
+    idx = (d["b_loc"], d["b_start_loc"], d["b_seq_len"], d["max_input_len"])
+    total = int(c["b_seq_len"].sum())
+    plain = torch.zeros(8, total, dtype=torch.float16, device="cuda")
+    F.token_attention(d["q"], d["k"], plain, *idx)
+    ctx = Context()
+    att = torch.zeros_like(plain)
+    F.set_option("fuse_token_attention", 1)
+    try:
+        F.token_attention(d["q"], d["k"], att, *idx, ctx=ctx)
+        torch.cuda.synchronize()
+        assert torch.count_nonzero(att) == 0          # recorded, not launched
+        assert _lib.load().impl.diopiB200ContextRelease(ctx.handle) == 0
+        torch.cuda.synchronize()
+        assert torch.equal(att, plain)                # launched by the release
+        att.zero_()
+        assert _lib.load().impl.diopiB200ContextRelease(ctx.handle) == 0   # nothing left: a no-op
+        torch.cuda.synchronize()
+        assert torch.count_nonzero(att) == 0
+    finally:
+        F.set_option("fuse_token_attention", 0)
+
+
 # ------------------------------------------------------------------ status word, streams
 def test_out_of_range_slot_is_reported(F):
     c = make_decode_case(2, 8, 128, torch.float16, [20, 40], seed=2)
