@@ -241,17 +241,38 @@ int* async_status_device_ptr_if_ready() {
     return h ? h + current_device_index() * kStatusStrideInts : nullptr;
 }
 
+namespace {
+thread_local int t_handled_code = 0;
+}
+
+// An op that fails with an error of its own for the very event a status stands for (a group refused because a kernel gave
+// up) says so: neither the status its guard took nor one still in the word is reported a second time.
 void clear_async_status_if(int code) {
+    t_handled_code = code;
     int* h = async_status_device_ptr_if_ready();
     if (h && *reinterpret_cast<volatile int*>(h) == code) *reinterpret_cast<volatile int*>(h) = 0;
 }
 
-void check_async_status() {
+int drop_handled_status(int taken) {
+    const int handled = t_handled_code;
+    t_handled_code = 0;
+    return taken == handled ? 0 : taken;
+}
+
+int take_async_status() {
     int* h = async_status_device_ptr_if_ready();
-    if (!h) return;
-    int v = *reinterpret_cast<volatile int*>(h);
-    if (v == 0) return;
-    *reinterpret_cast<volatile int*>(h) = 0;
+    if (!h) return 0;
+    const int v = *reinterpret_cast<volatile int*>(h);
+    if (v != 0) *reinterpret_cast<volatile int*>(h) = 0;
+    return v;
+}
+
+void restore_async_status(int v) {
+    int* h = async_status_device_ptr_if_ready();
+    if (h && v != 0 && *reinterpret_cast<volatile int*>(h) == 0) *reinterpret_cast<volatile int*>(h) = v;
+}
+
+void fail_with_async_status(int v) {
     const char* what = "unknown";
     switch (v) {
         case 1: what = "a pool slot index read from b_loc or dest_loc was outside the pool; that row was skipped"; break;

@@ -98,27 +98,38 @@ struct DeviceInfo {
 const DeviceInfo& device_info();
 
 // One word per device in mapped pinned host memory that kernels write when they meet something they
-// must refuse (an index outside the pool, a wait that ran out). The word of the current device is read
-// at the end of every op at no cost; a non-zero value is reported once, as the return code of the op that
-// sees it. That op has already made its own launch by then: a status left by an earlier kernel never
-// keeps a later call from running (in a tensor-parallel layer a skipped call on one rank would leave
-// its peers waiting).
+// must refuse (an index outside the pool, a wait that ran out). Every op takes the word of the current
+// device (reads and clears it, at no cost) when it is entered, runs its body, and only then reports a
+// status it took, once, as its return code: a status left by an earlier kernel never keeps a later call
+// from running (in a tensor-parallel layer a skipped call on one rank would leave its peers waiting),
+// and a call never reports its own kernel, which may still be running.
 int* async_status_device_ptr();
 // The same word if an earlier call already set the block up, else null (kernels accept null). Never allocates.
 int* async_status_device_ptr_if_ready();
-void check_async_status();
+int take_async_status();              // reads and clears the current device's status
+void restore_async_status(int v);     // puts a taken status back (the op failed for a reason of its own)
+[[noreturn]] void fail_with_async_status(int v);
+int drop_handled_status(int taken);   // 0 when the op's body declared that status handled (clear_async_status_if), else `taken`
 // Drops the current device's status when it is `code`: for an op that reports the same event through its own error.
 void clear_async_status_if(int code);
 
 // Runs `body`, mapping exceptions to return codes; nothing escapes the C boundary.
+// `report_status` = false for housekeeping calls (options, context release): they must not use up a kernel's status, which
+// belongs to the next op call.
 template <typename F>
-diopiError_t guard(const char* op, F&& body) noexcept {
+diopiError_t guard(const char* op, F&& body, bool report_status = true) noexcept {
     void* rec = nullptr;
     if (diopiRecordStart) diopiRecordStart(op, &rec);
     diopiError_t rc = diopiSuccess;
+    int stale = 0;
     try {
+        if (report_status) stale = take_async_status();
         body();
-        check_async_status();   // after the launch: see the comment at async_status_device_ptr
+        if (stale != 0) {
+            const int v = stale;
+            stale = 0;
+            fail_with_async_status(v);   // after the launch: see the comment at async_status_device_ptr
+        }
     } catch (const OpError& e) {
         set_last_error(std::string(op) + ": " + e.msg);
         rc = e.code;
@@ -129,6 +140,8 @@ diopiError_t guard(const char* op, F&& body) noexcept {
         set_last_error(std::string(op) + ": unknown exception");
         rc = diopiErrorOccurred;
     }
+    stale = drop_handled_status(stale);
+    if (stale != 0) restore_async_status(stale);   // the body failed on its own: the status waits for the next call
     if (diopiRecordEnd && rec) diopiRecordEnd(&rec);
     return rc;
 }

@@ -198,7 +198,7 @@ B200_EXPORT diopiError_t diopiB200ContextRelease(diopiContextHandle_t ctx) {
     return guard("diopiB200ContextRelease", [&] {
         B200_REQUIRE(ctx != nullptr, "null context handle");
         flush_pending(ctx);
-    });
+    }, /*report_status=*/false);
 }
 
 // Extension: changes one of the process-wide switches of common.hpp (the environment gives only their start values).
@@ -206,7 +206,7 @@ B200_EXPORT diopiError_t diopiB200SetOption(const char* name, int64_t value) {
     return guard("diopiB200SetOption", [&] {
         if (!set_option(name, value))
             fail(diopiErrorOccurred, "unknown option '%s'; known: log, fuse_token_attention, decode_plain, prefill_simt", name ? name : "(null)");
-    });
+    }, /*report_status=*/false);
 }
 
 // ---------------------------------------------------------------------------------------------

@@ -442,13 +442,19 @@ def test_context_release_flushes_a_recorded_call(F):
 def test_out_of_range_slot_is_reported(F):
     c = make_decode_case(2, 8, 128, torch.float16, [20, 40], seed=2)
     bad = c["b_loc"].clone()
-    bad[1, -3] = c["k"].shape[0] + 5   # beyond the pool: the row is skipped, the next call reports it
+    bad[1, -3] = c["k"].shape[0] + 5   # beyond the pool: the row is skipped and a status is raised
     out = torch.empty(c["q"].shape, dtype=torch.float16, device="cuda")
+    from diopi_b200.runtime import DiopiError
+    # The kernel of the first call raises the status; the next call takes it when it is entered and reports it after
+    # making its own launch (a call never reports its own kernel).
     F.token_decode_attention(c["q"].cuda(), c["k"].cuda(), c["v"].cuda(), out, bad.cuda(), c["b_start_loc"].cuda(), c["b_seq_len"].cuda(), c["max_input_len"])
     torch.cuda.synchronize()
-    from diopi_b200.runtime import DiopiError
+    good = torch.empty_like(out)
     with pytest.raises(DiopiError, match="outside the pool"):
-        F.token_decode_attention(c["q"].cuda(), c["k"].cuda(), c["v"].cuda(), out, c["b_loc"].cuda(), c["b_start_loc"].cuda(), c["b_seq_len"].cuda(), c["max_input_len"])
+        F.token_decode_attention(c["q"].cuda(), c["k"].cuda(), c["v"].cuda(), good, c["b_loc"].cuda(), c["b_start_loc"].cuda(), c["b_seq_len"].cuda(), c["max_input_len"])
+    torch.cuda.synchronize()
+    want = golden.token_decode_attention(c["q"], c["k"], c["v"], torch.zeros(c["q"].shape), c["b_loc"], c["b_start_loc"], c["b_seq_len"], c["max_input_len"], upcast=True)
+    close(good, want, torch.float16)   # the call that reported the status did run
     # the status is reported once; the library keeps working
     check_decode_case(F, c)
 
