@@ -18,12 +18,20 @@
 // and held in shared memory once for both tiles. TMEM columns (512 allocated): score buffers at 64 * (2 t + j % 2),
 // O_t at 256 + t * HD.
 // What the measurements taught (benchmark config: 8 requests of 1024..8192 rows, 32 heads, D 128, fp16):
-//   one tile per CTA, two CTAs per SM, own K/V copies: 873 TFLOP/s; this form: 979 TFLOP/s. On the way: one thread
-//   issuing for both tiles was the limit (1.30 of the time of one issuing warp per tile with descriptors made once); key
-//   blocks of 128 with a single score buffer per tile (no room in TMEM for two) serialise Q K^T, soft-max and P V of a
-//   tile and reached 680 TFLOP/s; holding a row of 128 scores in registers spills; with the exponentials removed
-//   altogether the time does not change, so the special-function unit is not the limit: the soft-max warps
-//   (two per scheduler) are bound by instruction issue and dependent latencies, about 7 instructions per score.
+//   one tile per CTA, two CTAs per SM, own K/V copies: 873 TFLOP/s; this form: 950 to 980 TFLOP/s. On the way: one
+//   thread issuing for both tiles was the limit (1.30 of the time of one issuing warp per tile with descriptors made
+//   once). What bounds this form is the tensor pipe's instruction rate, not the soft-max: issued by itself, a
+//   tcgen05.mma M128 K16 takes about 98 cycles when it accumulates onto the one before it and about 72 when two chains
+//   alternate, whatever N <= 128 is (only N = 256 runs at the nominal 4096 MAC per cycle), so the products of a pair of
+//   64-key blocks (two Q K^T of 8 steps at N 64, two P V of 4 steps) take 1670 to 1830 cycles alone and the loop takes
+//   2010 per pair. That is why nothing done to the soft-max moved the time: more or fewer exponentials on the fma pipe,
+//   the two warps of a scheduler taking turns at the special-function unit (16 ex2 per cycle and SM, 1060 cycles per pair
+//   of blocks), 224 registers for the soft-max threads by setmaxnreg. Key blocks of 128 halve the Q K^T instructions,
+//   but TMEM (512 columns: 2 x 128 for O) then holds one score buffer per tile: with P written over the scores 754 to
+//   795 TFLOP/s (Q K^T, soft-max and P V of a tile in series), with P handed over through shared memory (the buffer is
+//   free once the scores are in registers) 900 against 952 for this form in the same run: the soft-max threads then
+//   wait for the shared P piece and run 1800 cycles per 64 keys. A CTA spends 3.5 us before its first scores, 47 us
+//   in the loop and 1.9 us storing O on average; the SMs are busy 94 % of the kernel's span.
 // The L x L score and mask tensors of the reference never exist; FLOPs counted = 4*D*L*(L+1)/2 per head.
 //
 // All waits are bounded (2 s); a wait that runs out sets a flag, every role leaves its loop, TMEM is
@@ -177,28 +185,47 @@ __global__ void __launch_bounds__(Cfg<HD, BN, NT>::kThreads, 1)
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int h = blockIdx.y;
+    if (tid == 0) {
+        asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_q)) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_k)) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_v)) : "memory");
+    }
     const int hkv = h / p.kv_group;   // grouped-query attention: several query heads share one K/V head
 
     // ---- which (request, group of NT row tiles) is this CTA? Heaviest groups (late rows) are handed out first. ----
     int req = -1;
     int64_t L = 0, start = 0, r0 = 0;
     {
+        // Every warp does the same search, 32 requests at a time: lane i loads request i's length and start (one round of
+        // loads in flight instead of a chain of dependent ones), a warp scan gives the groups before it.
         const int64_t flat = static_cast<int64_t>(p.n_groups_max) - 1 - blockIdx.x;
         int64_t before = 0;
-        for (int i = 0; i < p.B; ++i) {
-            int64_t Li = p.uniform_len > 0 ? p.uniform_len : load_index(p.b_len, i);
-            const int64_t si = p.uniform_len > 0 ? i * p.uniform_len : load_index(p.b_start, i);
-            if (Li <= 0 || si < 0 || si >= p.total_rows) continue;
-            Li = imin64(Li, p.total_rows - si);
-            const int64_t ng = (Li + BM * NT - 1) / (BM * NT);
-            if (flat < before + ng) {
-                req = i;
-                L = Li;
-                start = si;
-                r0 = (flat - before) * (BM * NT);
-                break;
+        for (int base = 0; base < p.B && req < 0; base += 32) {
+            const int i = base + lane;
+            int64_t Li = 0, si = 0;
+            if (i < p.B) {
+                Li = p.uniform_len > 0 ? p.uniform_len : load_index(p.b_len, i);
+                si = p.uniform_len > 0 ? i * p.uniform_len : load_index(p.b_start, i);
+                if (Li <= 0 || si < 0 || si >= p.total_rows) Li = 0;
+                else Li = imin64(Li, p.total_rows - si);
             }
-            before += ng;
+            const int ng = static_cast<int>((Li + BM * NT - 1) / (BM * NT));
+            int incl = ng;
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) {
+                const int up = __shfl_up_sync(0xffffffffu, incl, d);
+                if (lane >= d) incl += up;
+            }
+            const unsigned hit = __ballot_sync(0xffffffffu, ng > 0 && flat < before + incl);
+            if (hit != 0) {
+                const int src = __ffs(hit) - 1;
+                req = base + src;
+                L = __shfl_sync(0xffffffffu, Li, src);
+                start = __shfl_sync(0xffffffffu, si, src);
+                r0 = (flat - before - __shfl_sync(0xffffffffu, incl - ng, src)) * (BM * NT);
+            } else {
+                before += __shfl_sync(0xffffffffu, incl, 31);
+            }
         }
     }
     if (req < 0) return;  // the whole CTA leaves together, before any barrier or TMEM use
@@ -303,6 +330,7 @@ __global__ void __launch_bounds__(Cfg<HD, BN, NT>::kThreads, 1)
             // inputs become ready; P V first, because it is what frees a score buffer.
             int nqk = 0, npv = 0;
             unsigned long long idle_since = 0;
+            uint32_t idle_probes = 0;
             while (ok && npv < my_blocks) {
                 bool progressed = false;
                 if (npv < nqk) {
@@ -347,7 +375,9 @@ __global__ void __launch_bounds__(Cfg<HD, BN, NT>::kThreads, 1)
                 }
                 if (progressed) {
                     idle_since = 0;
-                } else {
+                    idle_probes = 0;
+                } else if ((++idle_probes & 0xffu) == 0) {
+                    // The clock and the flag are looked at once in 256 idle rounds (a round is a handful of barrier probes).
                     if (*give_up) break;
                     const unsigned long long now = global_ns();
                     if (idle_since == 0) idle_since = now;
