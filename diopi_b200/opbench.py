@@ -99,7 +99,59 @@ def paged_case(kv_heads: int, q_heads: int = 64, B: int = 64, D: int = 128, bloc
     return dict(q=q, k=k, v=v, table=table.cuda(), lens=lens.tolist(), sum_len=int(lens.sum()), q_heads=q_heads, kv_heads=kv_heads, D=D, block=block)
 
 
-def run_op(op: str, size: str = "full", iters: int = 10, warmup: int = 3, kv_heads: int = 8, head_dim: int = 128, ctx: Context | None = None) -> dict:
+def library_prefill(pf, out, fn, rounds):
+    """The same prefill batch on attention kernels of libraries that happen to be installed, timed the same way (queued
+    back to back) and compared with this library's output: flash_attn's varlen kernel (mma.sync code built for earlier
+    GPUs) and torch's scaled_dot_product_attention, one call per request on contiguous copies made beforehand. They are
+    yardsticks printed beside the measurement, not part of the library and never on its call path."""
+    res = {}
+    lens = pf["lens"]
+    fn()
+    torch.cuda.synchronize()
+    try:
+        from flash_attn import flash_attn_varlen_func
+        cu = torch.cat([torch.zeros(1, dtype=torch.int32), lens.cumsum(0).to(torch.int32)]).cuda()
+        mx = int(lens.max())
+        fa = lambda: flash_attn_varlen_func(pf["q"], pf["k"], pf["v"], cu, cu, mx, mx, causal=True)  # noqa: E731
+        o = fa()
+        ms = time_rotating([fa], rounds=rounds, warmup=1)
+        res["flash_attn_varlen"] = {"ms": ms, "tflops": pf["flops"] / ms / 1e9, "max_abs_diff": (o.float() - out.float()).abs().max().item()}
+    except Exception as e:  # noqa: BLE001
+        res["flash_attn_varlen"] = {"error": repr(e)[:200]}
+    try:
+        import torch.nn.functional as TF
+        starts = pf["b_start_loc"].tolist()
+        per = []
+        for s0, L in zip(starts, lens.tolist()):
+            per.append(tuple(t[s0:s0 + L].transpose(0, 1).unsqueeze(0).contiguous() for t in (pf["q"], pf["k"], pf["v"])))
+        def sd():
+            return [TF.scaled_dot_product_attention(q, k, v, is_causal=True) for q, k, v in per]
+        outs = sd()
+        ms = time_rotating([sd], rounds=rounds, warmup=1)
+        diff = max((o[0].transpose(0, 1).float() - out[s0:s0 + L].float()).abs().max().item() for o, s0, L in zip(outs, starts, lens.tolist()))
+        res["torch_sdpa_per_request"] = {"ms": ms, "tflops": pf["flops"] / ms / 1e9, "max_abs_diff": diff, "calls": len(per)}
+        # the longest request alone, on both
+        i = int(lens.argmax())
+        s0, L = starts[i], int(lens[i])
+        H, D = pf["q"].shape[1], pf["q"].shape[2]
+        fl = H * 4 * D * L * (L + 1) // 2
+        q, k, v = per[i]
+        one = lambda: TF.scaled_dot_product_attention(q, k, v, is_causal=True)  # noqa: E731
+        ms1 = time_rotating([one], rounds=rounds, warmup=1)
+        q1, k1, v1 = (t[s0:s0 + L].contiguous() for t in (pf["q"], pf["k"], pf["v"]))
+        o1 = torch.empty_like(q1)
+        st1 = torch.zeros(1, dtype=torch.int32, device="cuda")
+        ln1 = torch.full((1,), L, dtype=torch.int32, device="cuda")
+        mine = lambda: F.context_attention(q1, k1, v1, o1, st1, ln1, L)  # noqa: E731
+        ms2 = time_rotating([mine], rounds=rounds, warmup=1)
+        res["longest_request_alone"] = {"rows": L, "torch_sdpa_ms": ms1, "torch_sdpa_tflops": fl / ms1 / 1e9, "this_library_ms": ms2, "this_library_tflops": fl / ms2 / 1e9}
+    except Exception as e:  # noqa: BLE001
+        res["torch_sdpa_per_request"] = {"error": repr(e)[:200]}
+    return res
+
+
+def run_op(op: str, size: str = "full", iters: int = 10, warmup: int = 3, kv_heads: int = 8, head_dim: int = 128, ctx: Context | None = None,
+           compare: bool = False) -> dict:
     """Runs one op's benchmark on the current device and returns its record (with a `clocks` entry)."""
     hbm, tf_burst, tf_sust, kind = peaks()
     ctx = ctx or Context()
@@ -118,6 +170,8 @@ def run_op(op: str, size: str = "full", iters: int = 10, warmup: int = 3, kv_hea
         rec.update(ms=back, ms_single_launch_median=med, ms_single_launch_best=best, flops=pf["flops"], tflops=tf, frac_of_burst_peak=tf / tf_burst,
                    frac_of_sustained_peak=tf / tf_sust, head_dim=head_dim, heads=kw["H"], lens=pf["lens"].tolist(),
                    unit="TFLOP/s (causal-only FLOPs, fp16)", timing="launches queued back to back, average per call")
+        if compare:
+            rec["library_comparators"] = library_prefill(pf, out, fn, max(5, iters))
     elif op in ("rms_norm", "rms_norm_bwd", "rotary", "rope_copy_kv"):
         tokens = 8192 if size == "full" else 1024
         p = workloads.prenorm(tokens=tokens)
@@ -268,8 +322,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--kv-heads", type=int, default=8, help="paged: K/V heads under 64 query heads")
     ap.add_argument("--head-dim", type=int, default=128, help="prefill: head dimension (heads = 4096 / head_dim)")
+    ap.add_argument("--compare", action="store_true", help="prefill: also time installed library attention kernels on the same batch")
     args = ap.parse_args()
-    print(json.dumps(run_op(args.op, args.size, args.iters, args.warmup, args.kv_heads, args.head_dim)), flush=True)
+    print(json.dumps(run_op(args.op, args.size, args.iters, args.warmup, args.kv_heads, args.head_dim, compare=args.compare)), flush=True)
 
 
 if __name__ == "__main__":
