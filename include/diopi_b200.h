@@ -281,7 +281,9 @@ diopiError_t diopiB200SetOption(const char* name, int64_t value);
  * the library's device image, held by every GPU that loads the library. Refuses, with an error,
  * problems whose partials ((148 + batch) * head_num * (head_dim + 2) * 4 bytes) exceed it. The first
  * call on a device looks up the array's address: make it before any stream capture. Calls that may
- * overlap on one GPU share the array and race; keep them on one stream. */
+ * overlap on one GPU share the array and race; keep them on one stream. With the fuse_token_attention
+ * switch on, a logits call recorded on `ctx` is NOT launched by this entry point (launching it needs
+ * scratch): call diopiB200ContextRelease(ctx) first if one may be pending. */
 diopiError_t diopiTokenDecodeAttentionInferenceNoAlloc(diopiContextHandle_t ctx, diopiTensorHandle_t out, diopiConstTensorHandle_t q,
                                                        diopiConstTensorHandle_t k, diopiConstTensorHandle_t v, diopiConstTensorHandle_t b_loc,
                                                        diopiConstTensorHandle_t b_start_loc, diopiConstTensorHandle_t b_seq_len, int max_input_len);
